@@ -1,0 +1,78 @@
+// Internal description of one GEMM call, shared by the dispatch layer and every kernel family.
+//
+// The public entry points (cublasSgemm_v2, cublasGemmEx, cublasGemmStridedBatchedEx, cublasLtMatmul, ...)
+// fold their arguments into a Problem the way k0zi/Vulkanizer folds them into `struct Gemm`
+// (src/cublas/cublas.cpp:260-281); the kernels read it through EpilogueArgs / ScalarArgs below.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace vkzb {
+
+// Storage types a matrix can have. The numeric codes index small tables in the kernels.
+enum DType : int { kF32 = 0, kF16 = 1, kBF16 = 2, kS8 = 3, kS32 = 4, kF64 = 5, kBadType = -1 };
+
+// Type of alpha and beta: fixed by the compute type (cublas.cpp:235-258 reads 2, 4 or 8 bytes).
+enum ScalarType : int { kScalarF32 = 0, kScalarF16 = 1, kScalarS32 = 2, kScalarF64 = 3 };
+
+enum Activation : int { kActNone = 0, kActRelu = 1, kActGelu = 2 };
+
+__host__ __device__ inline int dtypeSize(int t) {
+    return t == kF32 || t == kS32 ? 4 : t == kF64 ? 8 : t == kS8 ? 1 : 2;
+}
+
+// alpha and beta as the kernels see them. In host pointer mode the values were read on the host and
+// travel by value; in device pointer mode the kernel dereferences the pointers itself, so no call
+// ever blocks on a device-to-host copy (the reference does one per scalar, cublas.cpp:241-243).
+struct ScalarArgs {
+    double alphaHost, betaHost;  // exact for every scalar type (f16, f32, s32, f64)
+    const void* alphaDev;        // non-null: device pointer mode
+    const void* betaDev;
+    int type;                    // ScalarType
+};
+
+// Where and how results are written: D = act(alpha * acc + beta * C + bias).
+struct EpilogueArgs {
+    void* D;              // matrix, or device array of matrix pointers when pointerArrays
+    const void* C;        // read only when beta != 0; equals D for the cuBLAS entry points
+    long long ldd, ldc;
+    long long strideD, strideC;  // elements, per batch entry
+    int typeD, typeC;     // DType
+    const void* bias;     // per-row vector of length m, or null
+    long long biasStride; // elements, per batch entry
+    int typeBias;
+    int activation;       // Activation
+    int roundBeforeBias;  // 1: round alpha*acc+beta*C to D's type before bias/activation, as a second pass over D would
+    int pointerArrays;    // D (and C) are arrays of pointers indexed by the batch entry
+    ScalarArgs scalars;
+};
+
+struct Problem {
+    bool transA = false, transB = false;
+    int m = 0, n = 0, k = 0, batch = 1;
+    const void* A = nullptr;
+    const void* B = nullptr;
+    int typeA = kF32, typeB = kF32;
+    long long lda = 0, ldb = 0;
+    long long strideA = 0, strideB = 0;
+    bool pointerArrays = false;  // A, B, D are device arrays of pointers
+    int accType = kF32;          // kF32, kS32 or kF64: the accumulator
+    bool allowTf32 = false;      // handle asked for CUBLAS_TF32_TENSOR_OP_MATH or compute type FAST_TF32
+    EpilogueArgs epi{};
+    cudaStream_t stream = nullptr;
+};
+
+// Kernel families (launchers return cudaError_t; the dispatch layer maps it to a cuBLAS status).
+cudaError_t launchScale(const Problem& p);    // k = 0: D = act(beta * C + bias)
+cudaError_t launchGeneric(const Problem& p);  // any types / leading dimensions / pointer arrays
+cudaError_t launchGemv(const Problem& p);     // m = 1 or n = 1
+bool sgemmEligible(const Problem& p);
+cudaError_t launchSgemm(const Problem& p);    // fp32 FFMA
+bool ummaEligible(const Problem& p);
+cudaError_t launchUmma(const Problem& p);     // tcgen05 tensor cores
+int ummaDeviceStatus();
+
+void countLaunch(int n = 1);
+
+}  // namespace vkzb

@@ -1,0 +1,532 @@
+// Tensor-core GEMM for Blackwell (sm_100a): TMA -> shared memory -> tcgen05.mma -> TMEM -> fused epilogue.
+//
+// This is the B200 counterpart of k0zi/Vulkanizer's cooperative-matrix shader (src/cublas/shaders/gemm_coopmat.comp:349-464,
+// chosen at src/cublas/cublas.cpp:791-901) and of its f16 A^T B shader (gemm_f16_tn.comp:183-223): f16 or bf16
+// operands with fp32 accumulation in every transpose combination, C in f32 / f16 / bf16, alpha and beta fused into
+// the store. Beyond the reference it also covers int8 operands with exact int32 accumulation (kind::i8) and fp32
+// operands on TF32 tensor cores (kind::tf32, only when the caller asked for TF32 math).
+//
+// One persistent CTA per SM walks output tiles of 128 x BN (BN = 256, 128 or 64) in a grouped order that keeps a
+// band of A panels and the B panels they meet resident in L2 (the same idea as gemm_coopmat.comp:353-360). Warps
+// are specialised:
+//   warp 0    one lane issues the TMA loads of A and B k-slices into a ring of shared-memory stages
+//   warp 1    one lane issues tcgen05.mma for each filled stage; accumulators live in TMEM, two of them,
+//             so the next tile's products start while the previous tile is still being written out
+//   warps 2-5 read their 32 TMEM lanes (= 32 rows of the tile) with tcgen05.ld and store
+//             D = act(alpha * acc + beta * C + bias) straight to column-major global memory: for a fixed
+//             column the 32 lanes of a warp touch 32 consecutive rows, i.e. one full 128-byte line
+// A k-slice is 128 bytes per row (64 halves, 32 floats or 128 int8) so that TMA's 128-byte swizzle and the
+// matrix descriptors' SWIZZLE_128B layout agree. Operands that are contiguous along k ("K-major": op(A) = A^T,
+// op(B) = B) arrive as one box of rows x 128 bytes; operands contiguous along m or n ("MN-major") arrive as
+// boxes of 128 bytes (of m or n) x slice-length rows, and the descriptor's leading-dimension byte offset steps
+// between those boxes. Rows, columns and the k tail that fall outside the matrices are zero-filled by TMA.
+//
+// Every wait on an mbarrier is bounded in time: when one gives up it records a code in a device status
+// word, raises a CTA-wide abort flag, and all roles fall through to the common exit, which frees TMEM.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "epilogue.cuh"
+
+namespace vkzb {
+namespace {
+
+constexpr int kBM = 128;                    // tile rows = TMEM lanes
+constexpr int kSliceBytes = 128;            // bytes of k per row and stage (one swizzle span)
+constexpr int kStageABytes = kBM * kSliceBytes;
+constexpr int kMmasPerStage = 4;            // 128 bytes / 32 bytes of k per tcgen05.mma
+constexpr int kEpilogueWarps = 4;
+constexpr int kThreads = 32 * (2 + kEpilogueWarps);
+constexpr int kSmemBudget = 200 * 1024;     // ring of stages; leaves room for barriers and alignment slack
+constexpr unsigned long long kWaitLimitNs = 4000000000ull;  // a wait longer than this is a lost signal
+
+enum UmmaKind : int { kKindF16 = 0, kKindTf32 = 1, kKindI8 = 2 };
+
+// Codes left in the device status word by the wait that gave up.
+enum : unsigned { kStatusOk = 0, kStatusProducerWait = 1, kStatusMmaFullWait = 2, kStatusMmaTmemWait = 3, kStatusEpilogueWait = 4 };
+
+__device__ unsigned g_ummaStatus;
+
+struct UmmaArgs {
+    int m, n, k, batch;
+    int tilesM, tilesN, groupM;
+    long long totalTiles;
+    int numKSlices;   // ceil(k / sliceElems)
+    int sliceElems;   // elements of k per stage: 128 bytes / element size
+    int kind;         // UmmaKind
+    unsigned idesc;   // tcgen05 instruction descriptor
+    unsigned descHi;  // upper half of both shared-memory descriptors: stride offset, version, swizzle mode
+    unsigned lboA, lboB;            // leading-dimension byte offset >> 4
+    unsigned kStepA, kStepB;        // descriptor start-address advance per MMA, in 16-byte units
+    int mnMajorA, mnMajorB;
+    int boxesA, boxesB;             // TMA boxes per stage
+    int boxBytesA, boxBytesB;
+    int boxElemsA, boxElemsB;       // elements of m / n per box when MN-major
+    int batchMulA, batchMulB;       // 0: the operand is shared by every batch entry
+    EpilogueArgs epi;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ unsigned smemAddr(const void* p) { return unsigned(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbarInit(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbarArriveExpectTx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbarArrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbarTryWait(unsigned bar, unsigned parity) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ unsigned long long globalTimerNs() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits for the phase with `parity` to complete. Returns false when the CTA is aborting or the wait ran out
+// of time; in the latter case the code is recorded and the abort flag raised for the other roles.
+__device__ __noinline__ bool mbarWaitSlow(unsigned bar, unsigned parity, volatile int* abortFlag, unsigned code) {
+    const unsigned long long start = globalTimerNs();
+    for (unsigned spins = 0;; ++spins) {
+        if (mbarTryWait(bar, parity)) return true;
+        if ((spins & 63u) == 63u) {
+            if (*abortFlag) return false;
+            if (globalTimerNs() - start > kWaitLimitNs) {
+                atomicCAS(&g_ummaStatus, kStatusOk, code);
+                *abortFlag = 1;
+                __threadfence_block();
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbarWait(unsigned bar, unsigned parity, volatile int* abortFlag, unsigned code) {
+    if (mbarTryWait(bar, parity)) return true;
+    return mbarWaitSlow(bar, parity, abortFlag, code);
+}
+
+__device__ __forceinline__ void tmaLoad3d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05FenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05FenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void tcgen05Commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void ummaIssue(int kind, unsigned tmemD, unsigned long long descA, unsigned long long descB,
+                                          unsigned idesc, unsigned accumulate) {
+    if (kind == kKindF16) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else if (kind == kKindI8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// 32 lanes x 32 columns of 32-bit accumulators: thread i of the warp receives row i, columns c .. c + 31.
+__device__ __forceinline__ void tmemLoad32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Tile number -> (batch entry, tile row, tile column). Tiles are numbered so that consecutive numbers, which run
+// at the same time on neighbouring SMs, cover `groupM` tile rows by a few tile columns: their A and B panels
+// are then fetched from HBM once and served from L2 to the other CTAs that need them.
+struct TileCoord {
+    int batch, row, col;
+};
+__device__ __forceinline__ TileCoord tileCoord(const UmmaArgs& g, long long tile) {
+    const int perEntry = g.tilesM * g.tilesN;
+    const int batch = int(tile / perEntry), r = int(tile % perEntry);
+    const int groupSize = g.groupM * g.tilesN;
+    const int group = r / groupSize, firstRow = group * g.groupM;
+    const int rowsInGroup = min(g.tilesM - firstRow, g.groupM);
+    const int inGroup = r % groupSize;
+    return {batch, firstRow + inGroup % rowsInGroup, inGroup / rowsInGroup};
+}
+
+template <int BN>
+struct SmemPlan {
+    static constexpr int kStageBBytes = BN * kSliceBytes;
+    static constexpr int kStageBytes = kStageABytes + kStageBBytes;
+    static constexpr int kStages = kSmemBudget / kStageBytes;
+    static constexpr int kTmemCols = 2 * BN;  // two accumulators
+    static constexpr int kDynamicBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+    static_assert(kStages >= 3, "ring too short");
+    static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols >= 32 && kTmemCols <= 512, "TMEM allocation size");
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB) {
+    using Plan = SmemPlan<BN>;
+    constexpr int kStages = Plan::kStages;
+    extern __shared__ unsigned char smemRaw[];
+    // the swizzled layout is defined on 1024-byte aligned addresses
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + kStages * Plan::kStageBytes);
+    // bars[0 .. S): stage filled; [S .. 2S): stage drained; [2S, 2S+2): accumulator ready; [2S+2, 2S+4): accumulator drained
+    unsigned* tmemSlot = reinterpret_cast<unsigned*>(bars + 2 * kStages + 4);
+    volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const unsigned smemBase = smemAddr(smem);
+    const unsigned fullBar = smemAddr(bars), emptyBar = fullBar + 8 * kStages;
+    const unsigned accFullBar = emptyBar + 8 * kStages, accEmptyBar = accFullBar + 16;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbarInit(fullBar + 8 * s, 1);
+            mbarInit(emptyBar + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbarInit(accFullBar + 8 * a, 1);
+            mbarInit(accEmptyBar + 8 * a, kEpilogueWarps);
+        }
+        *abortFlag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(tmemSlot)),
+                     "r"(unsigned(Plan::kTmemCols))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05FenceBefore();
+    __syncthreads();
+    tcgen05FenceAfter();
+    const unsigned tmemBase = *tmemSlot;
+
+    if (warp == 0) {
+        // ---- TMA producer ----
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; ok && tile < g.totalTiles; tile += gridDim.x) {
+                const TileCoord t = tileCoord(g, tile);
+                const int row0 = t.row * kBM, col0 = t.col * BN;
+                for (int ks = 0; ks < g.numKSlices; ++ks) {
+                    if (!(ok = mbarWait(emptyBar + 8 * stage, phase ^ 1, abortFlag, kStatusProducerWait))) break;
+                    const unsigned bar = fullBar + 8 * stage;
+                    mbarArriveExpectTx(bar, unsigned(Plan::kStageBytes));
+                    const unsigned dstA = smemBase + stage * Plan::kStageBytes, dstB = dstA + kStageABytes;
+                    const int k0 = ks * g.sliceElems;
+                    if (g.mnMajorA) {
+                        for (int b = 0; b < g.boxesA; ++b)
+                            tmaLoad3d(dstA + b * g.boxBytesA, &mapA, bar, row0 + b * g.boxElemsA, k0, t.batch * g.batchMulA);
+                    } else {
+                        tmaLoad3d(dstA, &mapA, bar, k0, row0, t.batch * g.batchMulA);
+                    }
+                    if (g.mnMajorB) {
+                        for (int b = 0; b < g.boxesB; ++b)
+                            tmaLoad3d(dstB + b * g.boxBytesB, &mapB, bar, col0 + b * g.boxElemsB, k0, t.batch * g.batchMulB);
+                    } else {
+                        tmaLoad3d(dstB, &mapB, bar, k0, col0, t.batch * g.batchMulB);
+                    }
+                    if (++stage == kStages) stage = 0, phase ^= 1;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 0, tileCount = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; ok && tile < g.totalTiles; tile += gridDim.x, ++tileCount) {
+                const unsigned acc = tileCount & 1, accPhase = (tileCount >> 1) & 1;
+                if (!(ok = mbarWait(accEmptyBar + 8 * acc, accPhase ^ 1, abortFlag, kStatusMmaTmemWait))) break;
+                tcgen05FenceAfter();
+                const unsigned tmemD = tmemBase + acc * BN;
+                for (int ks = 0; ks < g.numKSlices; ++ks) {
+                    if (!(ok = mbarWait(fullBar + 8 * stage, phase, abortFlag, kStatusMmaFullWait))) break;
+                    tcgen05FenceAfter();
+                    const unsigned addrA = smemBase + stage * Plan::kStageBytes, addrB = addrA + kStageABytes;
+                    const unsigned loA = ((addrA & 0x3FFFFu) >> 4) | (g.lboA << 16);
+                    const unsigned loB = ((addrB & 0x3FFFFu) >> 4) | (g.lboB << 16);
+#pragma unroll
+                    for (int j = 0; j < kMmasPerStage; ++j) {
+                        const unsigned long long descA = (static_cast<unsigned long long>(g.descHi) << 32) | (loA + j * g.kStepA);
+                        const unsigned long long descB = (static_cast<unsigned long long>(g.descHi) << 32) | (loB + j * g.kStepB);
+                        ummaIssue(g.kind, tmemD, descA, descB, g.idesc, (ks | j) != 0 ? 1u : 0u);
+                    }
+                    tcgen05Commit(emptyBar + 8 * stage);  // the stage may be refilled once these MMAs have read it
+                    if (++stage == kStages) stage = 0, phase ^= 1;
+                }
+                if (ok) tcgen05Commit(accFullBar + 8 * acc);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---- epilogue: TMEM -> registers -> global ----
+        const int quarter = warp % 4;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31
+        unsigned tileCount = 0;
+        bool ok = true;
+        for (long long tile = blockIdx.x; ok && tile < g.totalTiles; tile += gridDim.x, ++tileCount) {
+            const TileCoord t = tileCoord(g, tile);
+            const unsigned acc = tileCount & 1, accPhase = (tileCount >> 1) & 1;
+            ok = mbarWait(accFullBar + 8 * acc, accPhase, abortFlag, kStatusEpilogueWait);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tcgen05FenceAfter();
+            const int row = t.row * kBM + quarter * 32 + lane;
+            const int col0 = t.col * BN;
+            const unsigned taddr = tmemBase + acc * BN + (unsigned(quarter * 32) << 16);
+            const bool rowOk = row < g.m;
+            if (g.kind == kKindI8) {
+                Epilogue<int> epi;
+                epi.init(g.epi, t.batch);
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    if (col0 + c >= g.n) break;
+                    unsigned v[32];
+                    tmemLoad32(taddr + c, v);
+                    if (rowOk) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + c + j < g.n) epi.store(row, col0 + c + j, int(v[j]));
+                    }
+                }
+            } else {
+                Epilogue<float> epi;
+                epi.init(g.epi, t.batch);
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    if (col0 + c >= g.n) break;
+                    unsigned v[32];
+                    tmemLoad32(taddr + c, v);
+                    if (rowOk) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + c + j < g.n) epi.store(row, col0 + c + j, __uint_as_float(v[j]));
+                    }
+                }
+            }
+            tcgen05FenceBefore();
+            __syncwarp();
+            if (lane == 0) mbarArrive(accEmptyBar + 8 * acc);
+        }
+    }
+
+    // ---- common exit ----
+    if (*abortFlag) __nanosleep(20000);  // let copies still in flight land before the shared memory is released
+    tcgen05FenceBefore();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05FenceAfter();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(unsigned(Plan::kTmemCols))
+                     : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encodeTiled() {
+    static const EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+struct DeviceInfo {
+    int sms = 0;
+    bool sm100 = false;
+    bool attrSet[3] = {};
+};
+
+DeviceInfo& deviceInfo() {
+    static std::mutex mutex;
+    static DeviceInfo info[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev = dev < 0 || dev >= 64 ? 0 : dev;
+    std::lock_guard<std::mutex> lock(mutex);
+    DeviceInfo& d = info[dev];
+    if (!d.sms) {
+        int major = 0;
+        cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        d.sm100 = major == 10;
+        if (d.sms <= 0) d.sms = 1;
+    }
+    return d;
+}
+
+int elemSizeOf(int type) { return type == kF32 ? 4 : type == kS8 ? 1 : 2; }
+
+// A 3-d map over one operand: (contiguous dimension, strided dimension, batch entry).
+bool encodeOperand(CUtensorMap* map, const void* base, int type, long long inner, long long outer, long long ld,
+                   long long batch, long long batchStride, unsigned boxInner, unsigned boxOuter) {
+    const int es = elemSizeOf(type);
+    const CUtensorMapDataType dt = type == kF16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                   : type == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                   : type == kF32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                   : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const cuuint64_t dims[3] = {cuuint64_t(inner), cuuint64_t(outer), cuuint64_t(batch)};
+    // a batch dimension of extent 1 still needs a legal stride
+    const cuuint64_t strides[2] = {cuuint64_t(ld) * es, batch > 1 ? cuuint64_t(batchStride) * es : cuuint64_t(ld) * es * cuuint64_t(outer)};
+    const cuuint32_t box[3] = {boxInner, boxOuter, 1};
+    const cuuint32_t elemStrides[3] = {1, 1, 1};
+    return encodeTiled()(map, dt, 3, const_cast<void*>(base), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int ummaKindOf(const Problem& p) {
+    if (p.typeA != p.typeB) return -1;
+    if ((p.typeA == kF16 || p.typeA == kBF16) && p.accType == kF32) return kKindF16;
+    if (p.typeA == kS8 && p.accType == kS32) return kKindI8;
+    if (p.typeA == kF32 && p.accType == kF32 && p.allowTf32) return kKindTf32;
+    return -1;
+}
+
+template <int BN>
+cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtensorMap& mapB, int slot, cudaStream_t stream) {
+    using Plan = SmemPlan<BN>;
+    DeviceInfo& d = deviceInfo();
+    if (!d.attrSet[slot]) {
+        if (cudaError_t e = cudaFuncSetAttribute(ummaGemmKernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kDynamicBytes);
+            e != cudaSuccess)
+            return e;
+        d.attrSet[slot] = true;
+    }
+    const unsigned grid = unsigned(std::min<long long>(g.totalTiles, d.sms));
+    ummaGemmKernel<BN><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(g, mapA, mapB);
+    countLaunch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool ummaEligible(const Problem& p) {
+    if (p.pointerArrays || p.k <= 0 || ummaKindOf(p) < 0) return false;
+    if (!deviceInfo().sm100 || !encodeTiled()) return false;
+    const int es = elemSizeOf(p.typeA);
+    const auto ok = [&](const void* ptr, long long ld, long long stride) {
+        return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && (ld * es) % 16 == 0 &&
+               (p.batch == 1 || stride == 0 || (stride * es) % 16 == 0);
+    };
+    return ok(p.A, p.lda, p.strideA) && ok(p.B, p.ldb, p.strideB);
+}
+
+cudaError_t launchUmma(const Problem& p) {
+    const int kind = ummaKindOf(p);
+    const int es = elemSizeOf(p.typeA);
+    DeviceInfo& d = deviceInfo();
+
+    // Tile width: the candidate that needs the least time by a simple model, waves of tiles times a cost
+    // per tile that grows with the tile's width plus a fixed part.
+    const int tilesM = (p.m + kBM - 1) / kBM;
+    int bn = 256;
+    long long best = -1;
+    for (int cand : {256, 128, 64}) {
+        const long long tiles = (long long)tilesM * ((p.n + cand - 1) / cand) * p.batch;
+        const long long cost = (tiles + d.sms - 1) / d.sms * (cand + 32);
+        if (best < 0 || cost < best) best = cost, bn = cand;
+    }
+
+    UmmaArgs g{};
+    g.m = p.m, g.n = p.n, g.k = p.k, g.batch = p.batch;
+    g.tilesM = tilesM, g.tilesN = (p.n + bn - 1) / bn;
+    g.groupM = 16;
+    g.totalTiles = (long long)g.tilesM * g.tilesN * p.batch;
+    g.sliceElems = kSliceBytes / es;
+    g.numKSlices = (p.k + g.sliceElems - 1) / g.sliceElems;
+    g.kind = kind;
+    g.mnMajorA = !p.transA;  // op(A) = A: stored m x k, m contiguous
+    g.mnMajorB = p.transB;   // op(B) = B^T: stored n x k, n contiguous
+    const unsigned format = kind == kKindF16 ? (p.typeA == kBF16 ? 1u : 0u) : kind == kKindTf32 ? 2u : 1u /* signed 8-bit */;
+    const unsigned cFormat = kind == kKindI8 ? 2u : 1u;  // s32 : f32
+    g.idesc = cFormat << 4 | format << 7 | format << 10 | unsigned(g.mnMajorA) << 15 | unsigned(g.mnMajorB) << 16 |
+              unsigned(bn >> 3) << 17 | unsigned(kBM >> 4) << 24;
+    // stride offset 1024 bytes (8 rows of 128 bytes), descriptor version 1, 128-byte swizzle
+    g.descHi = (1024u >> 4) | 1u << 14 | 2u << 29;
+    const unsigned mnBoxBytes = unsigned(g.sliceElems) * kSliceBytes;  // slice-length rows of 128 bytes
+    const unsigned mnKStep = (32u / es / 8u) * (1024u >> 4);          // k groups of 8 rows per MMA
+    g.lboA = g.mnMajorA ? mnBoxBytes >> 4 : 1u;
+    g.lboB = g.mnMajorB ? mnBoxBytes >> 4 : 1u;
+    g.kStepA = g.mnMajorA ? mnKStep : 32u >> 4;
+    g.kStepB = g.mnMajorB ? mnKStep : 32u >> 4;
+    g.boxElemsA = g.boxElemsB = kSliceBytes / es;
+    g.boxBytesA = g.boxBytesB = int(mnBoxBytes);
+    g.boxesA = g.mnMajorA ? kBM / g.boxElemsA : 1;
+    g.boxesB = g.mnMajorB ? bn / g.boxElemsB : 1;
+    g.batchMulA = p.batch > 1 && p.strideA != 0;
+    g.batchMulB = p.batch > 1 && p.strideB != 0;
+    g.epi = p.epi;
+
+    CUtensorMap mapA, mapB;
+    const long long batchA = g.batchMulA ? p.batch : 1, batchB = g.batchMulB ? p.batch : 1;
+    const bool okA = g.mnMajorA ? encodeOperand(&mapA, p.A, p.typeA, p.m, p.k, p.lda, batchA, p.strideA, g.boxElemsA, g.sliceElems)
+                                : encodeOperand(&mapA, p.A, p.typeA, p.k, p.m, p.lda, batchA, p.strideA, g.sliceElems, kBM);
+    const bool okB = g.mnMajorB ? encodeOperand(&mapB, p.B, p.typeB, p.n, p.k, p.ldb, batchB, p.strideB, g.boxElemsB, g.sliceElems)
+                                : encodeOperand(&mapB, p.B, p.typeB, p.k, p.n, p.ldb, batchB, p.strideB, g.sliceElems, bn);
+    if (!okA || !okB) return cudaErrorInvalidValue;
+
+    if (bn == 256) return launchWith<256>(g, mapA, mapB, 0, p.stream);
+    if (bn == 128) return launchWith<128>(g, mapA, mapB, 1, p.stream);
+    return launchWith<64>(g, mapA, mapB, 2, p.stream);
+}
+
+int ummaDeviceStatus() {
+    unsigned status = 0;
+    if (cudaMemcpyFromSymbol(&status, g_ummaStatus, sizeof status) != cudaSuccess) return -1;
+    return int(status);
+}
+
+}  // namespace vkzb
