@@ -1,0 +1,398 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path through the drop-in C ABI (libcublas.so.12 / libcublasLt.so.12 / libnccl.so.2).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One JSON line on stdout (rank 0). A "step" is one GEMM call of the workload:
+
+  N = 1   cfg2_f16_tn_8192: cublasGemmEx, fp16 A/B (opA = T, opB = N), fp32 C, M = N = K = 8192, alpha = 1, beta = 0,
+          operands normal(0, 0.02) rounded to fp16, seed 1. The three matrices hold 512 MiB, four times the L2, so every
+          step streams its operands from HBM (no flush needed between steps).
+  N > 1   cfg5b_bf16_32768_nsharded: the 32768^3 bf16 -> fp32 product split along N, rank r computing the column block
+          C[:, r*32768/N : (r+1)*32768/N] with cublasLtMatmul in column chunks whose results are all-gathered over NVLink
+          through this repository's libnccl.so.2 while the next chunk is multiplied (strong scaling: total work fixed).
+
+`value` is the whole-job rate with operands resident in HBM; `e2e` is the same metric through the same C-ABI call but from
+pinned HOST buffers, the host-to-device copies of A and B and the device-to-host copy of C inside the timed region.
+`--impl reference` times k0zi/Vulkanizer's own CPU GEMM for this path (oracle/_ref, compiled from its sources) on the host
+cores, on a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            d = json.loads(path.read_text())
+            return d, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0: float, t1: float):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        rows = [r for (t, r) in self.rows if t0 - 0.05 <= t <= t1 + 0.15 and len(r) >= 7] or [r for (_, r) in self.rows if len(r) >= 7]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        mhz = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i] == "Active" for r in rows)]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": float(rows[0][1]) if rows[0][1].isdigit() else None,
+                "reasons": reasons, "samples": len(rows), "power_w_max": max(float(r[2]) for r in rows if r[2].replace(".", "").isdigit())}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# CPU arm: the reference's own code for this path on the host cores
+# ---------------------------------------------------------------------------------------------------------------------
+
+def cpu_reference_sample(size: int = 2048, reps: int = 3):
+    """fp16 TN size^3 through the reference's staged CPU GEMM (packTransposed -> hostGemm on all cores -> epilogue),
+    or through the C restatement when the compiled reference is absent. Returns (tflops, cores, kind, sample)."""
+    import numpy as np
+    from oracle import pyoracle as orc
+    from vulkanizer_b200 import synth
+
+    a = orc.to_storage(synth.normal(1, size * size, 0.02), "f16")
+    b = orc.to_storage(synth.normal(1, size * size, 0.02, first=size * size), "f16")
+    c = np.zeros(size * size, dtype=np.float32)
+    ref = orc.reference()
+    times = []
+    if ref is not None:
+        cores = ref.vkref_hardware_threads()
+        for _ in range(reps + 1):
+            t = time.perf_counter()
+            used = ref.vkref_staged_gemm(1, 0, size, size, size, 1.0, a.ctypes.data, 1, size, b.ctypes.data, 1, size, 0.0, c.ctypes.data, 0, size)
+            times.append(time.perf_counter() - t)
+        kind, cores = "reference", used or cores
+    else:
+        size = min(size, 512)
+        a, b, c = a[:size * size], b[:size * size], c[:size * size]
+        for _ in range(2):
+            t = time.perf_counter()
+            orc.gemm_f32(True, False, size, size, size, 1, 1.0, a, "f16", size, 0, b, "f16", size, 0, 0.0, c, "f32", size, 0)
+            times.append(time.perf_counter() - t)
+        kind, cores = "port", 1
+    best = statistics.median(times[1:])
+    return 2.0 * size ** 3 / best / 1e12, cores, kind, f"fp16 TN {size}^3, alpha=1 beta=0, median of {len(times) - 1} runs after one warm-up"
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    times = []
+    tf = cores = kind = sample = None
+    for _ in range(max(1, args.warmup // 3)):
+        cpu_reference_sample(1024, 1)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tf, cores, kind, sample = cpu_reference_sample(2048, 1)
+        times.append(tf)
+        if time.perf_counter() - t0 > 120:
+            break
+    value = statistics.median(times)
+    line = {"impl": "reference", "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": len(times),
+            "warmup": args.warmup, "ms_per_step": 2.0 * 2048 ** 3 / value / 1e9, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "cfg2_f16_tn_8192 (bounded sample: 2048^3 per step on the host cores)", "m": 2048, "n": 2048, "k": 2048},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# GPU arm, one GPU: configuration 2
+# ---------------------------------------------------------------------------------------------------------------------
+
+WORKLOADS = {
+    # name: call, A/B type, C type, opA, opB, m, n, k, batch, alpha, beta, distribution, seed, bound
+    "cfg1_sgemm_nn_512": dict(call="sgemm", ab="f32", c="f32", ta="N", tb="N", m=512, n=512, k=512, batch=1, alpha=1.0, beta=0.5,
+                              dist=("uniform", 1.0), seed=0, bound="ffma"),
+    "cfg2_f16_tn_8192": dict(call="gemmex", ab="f16", c="f32", ta="T", tb="N", m=8192, n=8192, k=8192, batch=1, alpha=1.0, beta=0.0,
+                             dist=("normal", 0.02), seed=1, bound="tensor"),
+    "cfg2_bf16_tn_8192": dict(call="gemmex", ab="bf16", c="f32", ta="T", tb="N", m=8192, n=8192, k=8192, batch=1, alpha=1.0, beta=0.0,
+                              dist=("normal", 0.02), seed=1, bound="tensor"),
+    "cfg3_s8_tn_11008x512x4096": dict(call="gemmex", ab="s8", c="s32", ta="T", tb="N", m=11008, n=512, k=4096, batch=1, alpha=1, beta=0,
+                                      dist=("int8", 127), seed=2, bound="tensor"),
+    "cfg3_s8_tn_4096x512x11008": dict(call="gemmex", ab="s8", c="s32", ta="T", tb="N", m=4096, n=512, k=11008, batch=1, alpha=1, beta=0,
+                                      dist=("int8", 127), seed=2, bound="tensor"),
+    "cfg4_f16_tn_batched_qk": dict(call="strided", ab="f16", c="f32", ta="T", tb="N", m=1024, n=1024, k=128, batch=256,
+                                   alpha=128 ** -0.5, beta=0.0, dist=("normal", 1.0), seed=3, bound="hbm"),
+    "cfg5a_f16_gemv_4096": dict(call="gemmex", ab="f16", c="f32", ta="T", tb="N", m=4096, n=1, k=4096, batch=1, alpha=1.0, beta=0.0,
+                                dist=("normal", 0.02), seed=4, bound="hbm"),
+    "cfg5a_f16_gemv_11008": dict(call="gemmex", ab="f16", c="f32", ta="T", tb="N", m=11008, n=1, k=4096, batch=1, alpha=1.0, beta=0.0,
+                                 dist=("normal", 0.02), seed=4, bound="hbm"),
+    # a smaller sibling of cfg2 for profiler captures (operands 96 MiB + C 64 MiB)
+    "profile_f16_tn_4096": dict(call="gemmex", ab="f16", c="f32", ta="T", tb="N", m=4096, n=4096, k=4096, batch=1, alpha=1.0, beta=0.0,
+                                dist=("normal", 0.02), seed=1, bound="tensor"),
+    "profile_s8_tn_4096": dict(call="gemmex", ab="s8", c="s32", ta="T", tb="N", m=4096, n=4096, k=4096, batch=1, alpha=1, beta=0,
+                               dist=("int8", 127), seed=2, bound="tensor"),
+}
+ELEM = {"f32": 4, "f16": 2, "bf16": 2, "s8": 1, "s32": 4}
+L2_BYTES = 126 * 1024 * 1024
+
+
+def host_operand(torch, spec, count: int, first: int):
+    """Pinned host tensor with `count` elements of the workload's distribution (element i depends on seed and i only)."""
+    import numpy as np
+    from vulkanizer_b200 import synth
+
+    kind, (dist, scale), seed = spec["ab"], spec["dist"], spec["seed"]
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16, "s8": torch.int8}[kind]
+    host = torch.empty(count, dtype=tdt).pin_memory()
+    raw = host.view(torch.int16).numpy().view(np.uint16) if kind in ("f16", "bf16") else host.numpy()
+    for start, n in synth.blocks(count):
+        if dist == "int8":
+            raw[start:start + n] = synth.int8_uniform(seed, n, first=first + start)
+            continue
+        v = synth.normal(seed, n, scale, first=first + start) if dist == "normal" else synth.uniform(seed, n, -scale, scale, first=first + start)
+        if kind == "f32":
+            raw[start:start + n] = v
+        elif kind == "f16":
+            raw[start:start + n] = v.astype(np.float16).view(np.uint16)
+        else:
+            u = v.view(np.uint32).astype(np.uint64)
+            raw[start:start + n] = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return host
+
+
+def run_single_gpu(args):
+    import torch
+    from vulkanizer_b200 import capi
+
+    name = args.workload or "cfg2_f16_tn_8192"
+    spec = WORKLOADS[name]
+    torch.cuda.set_device(0)
+    torch.zeros(1, device="cuda")
+    m, n, k, batch = spec["m"], spec["n"], spec["k"], spec["batch"]
+    ab, ct = spec["ab"], spec["c"]
+    ta = capi.OP_T if spec["ta"] == "T" else capi.OP_N
+    tb = capi.OP_T if spec["tb"] == "T" else capi.OP_N
+    rows_a, cols_a = (k, m) if ta == capi.OP_T else (m, k)
+    rows_b, cols_b = (n, k) if tb == capi.OP_T else (k, n)
+    lda, ldb, ldc = rows_a, rows_b, m
+    sA, sB, sC = rows_a * cols_a, rows_b * cols_b, m * n
+    cuda_type = {"f32": capi.CUDA_R_32F, "f16": capi.CUDA_R_16F, "bf16": capi.CUDA_R_16BF, "s8": capi.CUDA_R_8I, "s32": capi.CUDA_R_32I}
+    compute = capi.COMPUTE_32I if ab == "s8" else capi.COMPUTE_32F
+    ctorch = torch.int32 if ct == "s32" else torch.float32
+    bytes_in = (sA + sB) * batch * ELEM[ab]
+    bytes_out = sC * batch * ELEM[ct]
+    algorithmic_bytes = bytes_in + bytes_out * (2 if spec["beta"] != 0 else 1)
+
+    hostA = host_operand(torch, spec, sA * batch, 0)
+    hostB = host_operand(torch, spec, sB * batch, sA * batch)
+    hostC = torch.empty(sC * batch, dtype=ctorch).pin_memory()
+    # Small workloads would be served from L2 if the same buffers were reused: rotate through enough copies of
+    # the operands that a step never finds its inputs cached.
+    copies = 1 if algorithmic_bytes > 2 * L2_BYTES else int(2 * L2_BYTES // algorithmic_bytes) + 2
+    dAs = [hostA.cuda() for _ in range(copies)]
+    dBs = [hostB.cuda() for _ in range(copies)]
+    dCs = [torch.zeros(sC * batch, dtype=ctorch, device="cuda") for _ in range(copies)]
+    if spec["beta"] != 0:
+        for c in dCs:
+            c.copy_(torch.from_numpy(__import__("vulkanizer_b200.synth", fromlist=["x"]).uniform(spec["seed"] + 100, sC * batch)).to(ctorch))
+    blas = capi.Cublas()
+    stream = torch.cuda.Stream()
+    blas.set_stream(stream.cuda_stream)
+    counter = [0]
+
+    def call(i):
+        A, B, Cd = dAs[i % copies].data_ptr(), dBs[i % copies].data_ptr(), dCs[i % copies].data_ptr()
+        if spec["call"] == "sgemm":
+            blas.sgemm(ta, tb, m, n, k, spec["alpha"], A, lda, B, ldb, spec["beta"], Cd, ldc)
+        elif spec["call"] == "strided":
+            blas.gemm_strided_batched_ex(ta, tb, m, n, k, spec["alpha"], A, cuda_type[ab], lda, sA, B, cuda_type[ab], ldb, sB, spec["beta"],
+                                         Cd, cuda_type[ct], ldc, sC, batch, compute)
+        else:
+            blas.gemm_ex(ta, tb, m, n, k, spec["alpha"], A, cuda_type[ab], lda, B, cuda_type[ab], ldb, spec["beta"], Cd, cuda_type[ct], ldc,
+                         compute, capi.GEMM_DEFAULT_TENSOR_OP)
+
+    def step():
+        call(counter[0])
+        counter[0] += 1
+
+    # Launch-bound workloads (a few microseconds of kernel) are replayed from a CUDA graph holding one pass over the
+    # rotating buffers, so that the device time per step is the kernel's and not the host's call overhead.
+    flops = 2.0 * m * n * k * batch
+    use_graph = flops < 2e11
+    graph = None
+    with torch.cuda.stream(stream):
+        for _ in range(max(3, args.warmup)):
+            step()
+        stream.synchronize()
+        path = blas.last_path()
+        if use_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(copies):
+                    call(i)
+            graph.replay()
+            stream.synchronize()
+    launches0 = blas.launch_count()
+    sampler = ClockSampler(physical_gpu_index(0))
+    time.sleep(0.3)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    with torch.cuda.stream(stream):
+        stream.synchronize()
+        if use_graph:
+            replays = max(1, -(-args.steps // copies))
+            steps_done = replays * copies
+            start.record(stream)
+            for _ in range(replays):
+                graph.replay()
+            stop.record(stream)
+            graph_launches = steps_done
+        else:
+            steps_done = args.steps
+            start.record(stream)
+            for _ in range(steps_done):
+                step()
+            stop.record(stream)
+            graph_launches = 0
+        stream.synchronize()
+    t1 = time.time()
+    clocks = sampler.stop(t0, t1)
+    launches = blas.launch_count() - launches0 + graph_launches
+    total_ms = start.elapsed_time(stop)
+    kernel_ms = total_ms / steps_done
+    value_tf = flops * steps_done / (total_ms * 1e-3) / 1e12
+    assert blas.device_status() == 0, "a bounded wait in the tcgen05 kernel gave up"
+
+    # end to end through the same C-ABI call from pinned host buffers: copy A and B in, multiply, copy C out
+    def step_e2e():
+        dAs[0].copy_(hostA, non_blocking=True)
+        dBs[0].copy_(hostB, non_blocking=True)
+        call(0)
+        hostC.copy_(dCs[0], non_blocking=True)
+
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            step_e2e()
+        stream.synchronize()
+        e2e_steps = max(3, min(args.steps, 10))
+        start.record(stream)
+        for _ in range(e2e_steps):
+            step_e2e()
+        stop.record(stream)
+        stream.synchronize()
+    e2e_tf = flops * e2e_steps / (start.elapsed_time(stop) * 1e-3) / 1e12
+
+    peaks, peak_kind = measured_peaks()
+    bound = spec["bound"]
+    if bound == "hbm":
+        peak = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+        achieved, unit, source = algorithmic_bytes / (kernel_ms * 1e-3) / 1e9, "GB/s", f"{peak_kind}: device copy bandwidth"
+    elif bound == "ffma":
+        # no measured fp32 peak on record: nominal 148 SMs x 128 FMA x 2 x 1.965 GHz
+        peak, bound = 148 * 128 * 2 * 1.965e9 / 1e12, "tensor"
+        achieved, unit, source = flops / (kernel_ms * 1e-3) / 1e12, "TFLOP/s", "nominal fp32 FFMA rate at the maximum SM clock (CUDA cores, not tensor cores)"
+    else:
+        peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])) * (2.0 if ab == "s8" else 1.0)
+        achieved, unit = flops / (kernel_ms * 1e-3) / 1e12, "TFLOP/s"
+        source = f"{peak_kind}: cuBLAS bf16 8192^3 burst" + (" x 2 (int8 issues at twice the bf16 rate; no int8 measurement on record)" if ab == "s8" else "")
+    traffic = None
+    traffic_file = ROOT / "profiles" / "traffic.json"
+    if traffic_file.exists():
+        try:
+            traffic = json.loads(traffic_file.read_text()).get(name)
+        except Exception:
+            traffic = None
+
+    headline = name == "cfg2_f16_tn_8192"
+    cpu_tf, cores, cpu_kind, sample = cpu_reference_sample(2048, 3) if headline else (None, None, None, None)
+    path_names = {capi.PATH_GEMV: "gemvRowsVec16", capi.PATH_SGEMM: "sgemmKernel", capi.PATH_UMMA: "ummaGemmKernel", capi.PATH_GENERIC: "genericGemmKernel"}
+    line = {
+        "metric": "gemm_tflops", "value": value_tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps_done, "warmup": max(3, args.warmup),
+        "ms_per_step": kernel_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": ab, "data": "synthetic",
+        "config": {"workload": name, "call": {"sgemm": "cublasSgemm_v2", "strided": "cublasGemmStridedBatchedEx", "gemmex": "cublasGemmEx"}[spec["call"]],
+                   "opA": spec["ta"], "opB": spec["tb"], "m": m, "n": n, "k": k, "batch": batch, "a_b_type": ab, "c_type": ct,
+                   "alpha": spec["alpha"], "beta": spec["beta"], "seed": spec["seed"], "distribution": list(spec["dist"]),
+                   "l2": (f"{copies} rotating operand sets, {copies * algorithmic_bytes >> 20} MiB > L2" if copies > 1 else
+                          f"operands of one step hold {algorithmic_bytes >> 20} MiB > L2") + ", no flush",
+                   "timing": "CUDA graph replay of one pass over the operand sets" if use_graph else "back-to-back calls on one stream"},
+        "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "traffic": traffic,
+                     "peak_source": source, "kernel": path_names.get(path, str(path)), "kernel_ms": kernel_ms,
+                     "algorithmic_bytes": algorithmic_bytes, "algorithmic_flop": flops},
+        "e2e": {"value": e2e_tf, "unit": "TFLOP/s", "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out},
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    if cpu_tf is not None:
+        line["cpu_baseline"] = {"value": cpu_tf, "unit": "TFLOP/s", "cores": cores, "kind": cpu_kind, "sample": sample}
+    print(json.dumps(line), flush=True)
+    blas.destroy()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, help="one of the names in WORKLOADS (default: the headline configuration)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 or args.gpus > 1:
+        from vulkanizer_b200 import multi_gpu_bench
+        return multi_gpu_bench.run(args)
+    return run_single_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

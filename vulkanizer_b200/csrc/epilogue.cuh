@@ -72,6 +72,14 @@ __device__ __forceinline__ double readScalar(const void* dev, double host, int t
 }
 
 // Per-thread view of the epilogue for one batch entry. Acc is float, int or double.
+//
+// Kernels call store() once per result from fully unrolled loops, so its inlined body must stay a handful of
+// instructions or the unrolled code outgrows the instruction cache (measured: a 128 x 256 tile took 34 us to
+// write with the whole type switch inlined 32 times over, against under 2 us of arithmetic). The common cases,
+// a plain f32 / f16 / bf16 / s32 store with or without beta * C of the same type, are inlined; everything else
+// (mixed C and D types, bias, activation, the extra rounding) goes through one out-of-line function.
+enum StoreMode : int { kStoreSlow = 0, kStoreF32 = 1, kStoreF16 = 2, kStoreBF16 = 3, kStoreS32 = 4, kStoreF64 = 5 };
+
 template <typename Acc>
 struct Epilogue {
     char* D;
@@ -80,6 +88,7 @@ struct Epilogue {
     long long ldd, ldc;
     Acc alpha, beta;
     int typeD, typeC, typeBias, activation, roundBeforeBias;
+    int mode;  // StoreMode
     bool readC;
 
     __device__ __forceinline__ void init(const EpilogueArgs& e, long long batchEntry) {
@@ -99,20 +108,21 @@ struct Epilogue {
             C = static_cast<const char*>(e.C) + batchEntry * e.strideC * dtypeSize(e.typeC);
         }
         bias = e.bias ? static_cast<const char*>(e.bias) + batchEntry * e.biasStride * dtypeSize(e.typeBias) : nullptr;
+        const bool extras = bias || activation != kActNone || roundBeforeBias || (readC && typeC != typeD);
+        if constexpr (std::is_same_v<Acc, double>) mode = kStoreF64;
+        else if constexpr (std::is_same_v<Acc, int>) mode = typeD == kS32 && !extras ? kStoreS32 : kStoreSlow;
+        else mode = extras ? kStoreSlow : typeD == kF32 ? kStoreF32 : typeD == kF16 ? kStoreF16 : typeD == kBF16 ? kStoreBF16 : kStoreSlow;
     }
 
-    __device__ __forceinline__ void store(int row, int col, Acc acc) const {
+    // The general form: any C / D / bias types, bias, activation.
+    __device__ __noinline__ void storeSlow(int row, int col, Acc acc) const {
         const long long di = row + col * ldd;
-        if constexpr (std::is_same_v<Acc, double>) {
-            double v = alpha * acc;
-            if (readC) v += beta * static_cast<const double*>(static_cast<const void*>(C))[row + col * ldc];
-            static_cast<double*>(static_cast<void*>(D))[di] = v;
-        } else if constexpr (std::is_same_v<Acc, int>) {
+        if constexpr (std::is_same_v<Acc, int>) {
             int v = alpha * acc;
             if (readC) v += beta * loadAs<int>(C, row + col * ldc, typeC);
             if (typeD == kS32) static_cast<int*>(static_cast<void*>(D))[di] = v;
             else storeFloat(D, di, typeD, float(v));
-        } else {
+        } else if constexpr (std::is_same_v<Acc, float>) {
             float v = alpha * acc;
             if (readC) v += beta * loadAs<float>(C, row + col * ldc, typeC);
             if (roundBeforeBias) v = roundTo(v, typeD);
@@ -120,6 +130,48 @@ struct Epilogue {
             if (activation == kActRelu) v = fmaxf(v, 0.0f);
             else if (activation == kActGelu) v = geluTanh(v);
             storeFloat(D, di, typeD, v);
+        }
+    }
+
+    // One result, storage type fixed at compile time (MODE is a StoreMode other than kStoreSlow).
+    template <int MODE>
+    __device__ __forceinline__ void storeAs(int row, int col, Acc acc) const {
+        const long long di = row + col * ldd, ci = row + col * ldc;
+        if constexpr (MODE == kStoreF64) {
+            double v = alpha * acc;
+            if (readC) v += beta * reinterpret_cast<const double*>(C)[ci];
+            reinterpret_cast<double*>(D)[di] = v;
+        } else if constexpr (MODE == kStoreS32) {
+            int v = alpha * acc;
+            if (readC) v += beta * reinterpret_cast<const int*>(C)[ci];
+            reinterpret_cast<int*>(D)[di] = v;
+        } else if constexpr (MODE == kStoreF32) {
+            float v = alpha * acc;
+            if (readC) v += beta * reinterpret_cast<const float*>(C)[ci];
+            reinterpret_cast<float*>(D)[di] = v;
+        } else if constexpr (MODE == kStoreF16) {
+            float v = alpha * acc;
+            if (readC) v += beta * __half2float(reinterpret_cast<const __half*>(C)[ci]);
+            reinterpret_cast<__half*>(D)[di] = __float2half_rn(v);
+        } else {
+            float v = alpha * acc;
+            if (readC) v += beta * __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(C)[ci]);
+            reinterpret_cast<__nv_bfloat16*>(D)[di] = __float2bfloat16_rn(v);
+        }
+    }
+
+    // For kernels with few results per thread: the plain fp32 (or s32 / f64) store inline, the rest out of line.
+    __device__ __forceinline__ void store(int row, int col, Acc acc) const {
+        if constexpr (std::is_same_v<Acc, double>) {
+            storeAs<kStoreF64>(row, col, acc);
+        } else if constexpr (std::is_same_v<Acc, int>) {
+            if (mode == kStoreS32) storeAs<kStoreS32>(row, col, acc);
+            else storeSlow(row, col, acc);
+        } else {
+            if (mode == kStoreF32) storeAs<kStoreF32>(row, col, acc);
+            else if (mode == kStoreF16) storeAs<kStoreF16>(row, col, acc);
+            else if (mode == kStoreBF16) storeAs<kStoreBF16>(row, col, acc);
+            else storeSlow(row, col, acc);
         }
     }
 };

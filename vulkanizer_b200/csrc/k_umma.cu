@@ -12,9 +12,10 @@
 //   warp 0    one lane issues the TMA loads of A and B k-slices into a ring of shared-memory stages
 //   warp 1    one lane issues tcgen05.mma for each filled stage; accumulators live in TMEM, two of them,
 //             so the next tile's products start while the previous tile is still being written out
-//   warps 2-5 read their 32 TMEM lanes (= 32 rows of the tile) with tcgen05.ld and store
-//             D = act(alpha * acc + beta * C + bias) straight to column-major global memory: for a fixed
-//             column the 32 lanes of a warp touch 32 consecutive rows, i.e. one full 128-byte line
+//   warps 2-9 two groups of four; each warp reads its 32 TMEM lanes (= 32 rows of the tile) with tcgen05.ld, the
+//             groups taking alternate column steps, and D = act(alpha * acc + beta * C + bias) leaves either through
+//             a shared-memory buffer and a TMA bulk store (16-byte aligned D) or as direct column-major stores: for
+//             a fixed column the 32 lanes of a warp touch 32 consecutive rows, i.e. one full 128-byte line
 // A k-slice is 128 bytes per row (64 halves, 32 floats or 128 int8) so that TMA's 128-byte swizzle and the
 // matrix descriptors' SWIZZLE_128B layout agree. Operands that are contiguous along k ("K-major": op(A) = A^T,
 // op(B) = B) arrive as one box of rows x 128 bytes; operands contiguous along m or n ("MN-major") arrive as
@@ -25,6 +26,7 @@
 // word, raises a CTA-wide abort flag, and all roles fall through to the common exit, which frees TMEM.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "epilogue.cuh"
@@ -36,9 +38,13 @@ constexpr int kBM = 128;                    // tile rows = TMEM lanes
 constexpr int kSliceBytes = 128;            // bytes of k per row and stage (one swizzle span)
 constexpr int kStageABytes = kBM * kSliceBytes;
 constexpr int kMmasPerStage = 4;            // 128 bytes / 32 bytes of k per tcgen05.mma
-constexpr int kEpilogueWarps = 4;
+constexpr int kEpilogueGroups = 2;             // each group of 4 warps covers the 128 TMEM lanes and takes every other column step
+constexpr int kEpilogueWarps = 4 * kEpilogueGroups;
 constexpr int kThreads = 32 * (2 + kEpilogueWarps);
 constexpr int kSmemBudget = 200 * 1024;     // ring of stages; leaves room for barriers and alignment slack
+constexpr int kStoreCols = 16;                // columns per staged epilogue step
+constexpr int kStagingBufferBytes = kBM * kStoreCols * 4;             // 128 rows x 16 columns of 4 bytes
+constexpr int kStagingBytes = kEpilogueGroups * 2 * kStagingBufferBytes;  // two buffers per group
 constexpr unsigned long long kWaitLimitNs = 4000000000ull;  // a wait longer than this is a lost signal
 
 enum UmmaKind : int { kKindF16 = 0, kKindTf32 = 1, kKindI8 = 2 };
@@ -64,6 +70,8 @@ struct UmmaArgs {
     int boxBytesA, boxBytesB;
     int boxElemsA, boxElemsB;       // elements of m / n per box when MN-major
     int batchMulA, batchMulB;       // 0: the operand is shared by every batch entry
+    int debugSkipStore;             // measurement aid: run everything but the global stores
+    int tmaStore;                   // D is 16-byte aligned in every dimension: results leave through shared memory and TMA
     EpilogueArgs epi;
 };
 
@@ -126,6 +134,22 @@ __device__ __forceinline__ void tmaLoad3d(unsigned dst, const CUtensorMap* map, 
         : "memory");
 }
 
+// Shared memory -> global, asynchronous; elements outside the tensor are clipped by the hardware.
+__device__ __forceinline__ void tmaStore3d(const CUtensorMap* map, unsigned src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<unsigned long long>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Until at most `Pending` of this thread's bulk stores are still reading their shared-memory source.
+template <int Pending>
+__device__ __forceinline__ void tmaStoreWaitRead() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(Pending) : "memory");
+}
+__device__ __forceinline__ void tmaStoreWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Barrier among the four warps of one epilogue group (hardware barriers 1 and 2; 0 is __syncthreads).
+__device__ __forceinline__ void epilogueBarrier(int group) { asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory"); }
+
 __device__ __forceinline__ void tcgen05FenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05FenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -172,6 +196,119 @@ __device__ __forceinline__ void tmemLoad32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmemLoad16(unsigned taddr, unsigned (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <typename Acc>
+__device__ __forceinline__ Acc accumulatorValue(unsigned bits) {
+    if constexpr (std::is_same_v<Acc, int>) return int(bits);
+    else return __uint_as_float(bits);
+}
+
+// 32 results of one row, consecutive columns, with the store form fixed at compile time. The addresses advance
+// by one leading dimension per column, so each result costs an add, a multiply (plus a load and a fused
+// multiply-add when beta != 0) and a store. `count` < 32 only in a tile's last, ragged chunk.
+template <int MODE, typename Acc>
+__device__ __forceinline__ void storeChunk(const Epilogue<Acc>& epi, const unsigned (&v)[32], int row, int col, int count) {
+    using Elem = std::conditional_t<MODE == kStoreF32, float, std::conditional_t<MODE == kStoreS32, int,
+                 std::conditional_t<MODE == kStoreF16, __half, __nv_bfloat16>>>;
+    Elem* d = reinterpret_cast<Elem*>(epi.D) + (row + col * epi.ldd);
+    const Elem* c = reinterpret_cast<const Elem*>(epi.C) + (row + col * epi.ldc);
+    const Acc alpha = epi.alpha, beta = epi.beta;
+    const long long ldd = epi.ldd, ldc = epi.ldc;
+    const bool readC = epi.readC;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        if (j < count) {
+            Acc r = alpha * accumulatorValue<Acc>(v[j]);
+            if (readC) {
+                if constexpr (MODE == kStoreF32 || MODE == kStoreS32) r += beta * Acc(*c);
+                else if constexpr (MODE == kStoreF16) r += beta * __half2float(*c);
+                else r += beta * __bfloat162float(*c);
+                c += ldc;
+            }
+            if constexpr (MODE == kStoreF32 || MODE == kStoreS32) *d = r;
+            else if constexpr (MODE == kStoreF16) *d = __float2half_rn(r);
+            else *d = __float2bfloat16_rn(r);
+            d += ldd;
+        }
+    }
+}
+
+// One accumulator (this warp's 32 rows; its group's share of the BN columns) from TMEM to global memory, 32 columns at a time.
+template <int BN, typename Acc>
+__device__ __forceinline__ void drainAccumulator(const Epilogue<Acc>& epi, unsigned taddr, int row, bool rowOk, int col0, int n, int group) {
+#pragma unroll 1
+    for (int c = group * 32; c < BN; c += 32 * kEpilogueGroups) {
+        const int count = n - (col0 + c);
+        if (count <= 0) break;
+        unsigned v[32];
+        tmemLoad32(taddr + c, v);
+        if (!rowOk) continue;
+        switch (epi.mode) {
+        case kStoreF32: if constexpr (std::is_same_v<Acc, float>) storeChunk<kStoreF32>(epi, v, row, col0 + c, count); break;
+        case kStoreF16: if constexpr (std::is_same_v<Acc, float>) storeChunk<kStoreF16>(epi, v, row, col0 + c, count); break;
+        case kStoreBF16: if constexpr (std::is_same_v<Acc, float>) storeChunk<kStoreBF16>(epi, v, row, col0 + c, count); break;
+        case kStoreS32: if constexpr (std::is_same_v<Acc, int>) storeChunk<kStoreS32>(epi, v, row, col0 + c, count); break;
+        default:
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < count) epi.storeSlow(row, col0 + c + j, accumulatorValue<Acc>(v[j]));
+            break;
+        }
+    }
+}
+
+// The same through shared memory: each step's 128 x 16 block is laid out like the column-major D tile it belongs to
+// (column pitch 128 elements; lane = row, so the writes are conflict-free), then one thread hands it to TMA, which
+// writes full lines, clips rows and columns outside D, and keeps many stores in flight where four warps of scalar
+// stores cannot. Two buffers per group alternate: a buffer is rewritten only after the bulk store that read it two steps
+// earlier has finished reading.
+template <int BN, int MODE, typename Acc>
+__device__ __forceinline__ void drainAccumulatorStaged(const Epilogue<Acc>& epi, unsigned taddr, int rowInTile, int row, bool rowOk,
+                                                       int row0, int col0, int n, int batchEntry, const CUtensorMap* mapD,
+                                                       unsigned char* staging, unsigned& step, bool issuer, int group) {
+    using Elem = std::conditional_t<MODE == kStoreF32, float, std::conditional_t<MODE == kStoreS32, int,
+                 std::conditional_t<MODE == kStoreF16, __half, __nv_bfloat16>>>;
+    const Acc alpha = epi.alpha, beta = epi.beta;
+    const bool readC = epi.readC;
+#pragma unroll 1
+    for (int c = group * kStoreCols; c < BN; c += kStoreCols * kEpilogueGroups) {
+        const int count = n - (col0 + c);
+        if (count <= 0) break;
+        unsigned v[kStoreCols];
+        tmemLoad16(taddr + c, v);
+        Elem* buf = reinterpret_cast<Elem*>(staging + ((step & 1u) + 2 * group) * kStagingBufferBytes) + rowInTile;
+        if (issuer) tmaStoreWaitRead<1>();
+        epilogueBarrier(group);
+        const Elem* cin = reinterpret_cast<const Elem*>(epi.C) + (row + (col0 + c) * epi.ldc);
+#pragma unroll
+        for (int j = 0; j < kStoreCols; ++j) {
+            Acc r = alpha * accumulatorValue<Acc>(v[j]);
+            if (readC && rowOk && j < count) {
+                if constexpr (MODE == kStoreF32 || MODE == kStoreS32) r += beta * Acc(cin[j * epi.ldc]);
+                else if constexpr (MODE == kStoreF16) r += beta * __half2float(cin[j * epi.ldc]);
+                else r += beta * __bfloat162float(cin[j * epi.ldc]);
+            }
+            if constexpr (MODE == kStoreF32 || MODE == kStoreS32) buf[j * kBM] = r;
+            else if constexpr (MODE == kStoreF16) buf[j * kBM] = __float2half_rn(r);
+            else buf[j * kBM] = __float2bfloat16_rn(r);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        epilogueBarrier(group);
+        if (issuer) tmaStore3d(mapD, smemAddr(buf - rowInTile), row0, col0 + c, batchEntry);
+        ++step;
+    }
+}
+
 // Tile number -> (batch entry, tile row, tile column). Tiles are numbered so that consecutive numbers, which run
 // at the same time on neighbouring SMs, cover `groupM` tile rows by a few tile columns: their A and B panels
 // are then fetched from HBM once and served from L2 to the other CTAs that need them.
@@ -194,20 +331,22 @@ struct SmemPlan {
     static constexpr int kStageBytes = kStageABytes + kStageBBytes;
     static constexpr int kStages = kSmemBudget / kStageBytes;
     static constexpr int kTmemCols = 2 * BN;  // two accumulators
-    static constexpr int kDynamicBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int kDynamicBytes = kStages * kStageBytes + kStagingBytes + 1024 /* alignment slack */ + 256 /* barriers */;
     static_assert(kStages >= 3, "ring too short");
     static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols >= 32 && kTmemCols <= 512, "TMEM allocation size");
 };
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB) {
+ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+               const __grid_constant__ CUtensorMap mapD) {
     using Plan = SmemPlan<BN>;
     constexpr int kStages = Plan::kStages;
     extern __shared__ unsigned char smemRaw[];
     // the swizzled layout is defined on 1024-byte aligned addresses
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + kStages * Plan::kStageBytes);
+    unsigned char* staging = smem + kStages * Plan::kStageBytes;  // epilogue buffers, 1024-byte aligned like the stages
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(staging + kStagingBytes);
     // bars[0 .. S): stage filled; [S .. 2S): stage drained; [2S, 2S+2): accumulator ready; [2S+2, 2S+4): accumulator drained
     unsigned* tmemSlot = reinterpret_cast<unsigned*>(bars + 2 * kStages + 4);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
@@ -306,52 +445,48 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
     } else {
         // ---- epilogue: TMEM -> registers -> global ----
         const int quarter = warp % 4;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31
-        unsigned tileCount = 0;
+        const int group = (warp - 2) / 4;
+        unsigned tileCount = 0, storeStep = 0;
+        const bool issuer = threadIdx.x == 64 + 128 * group;  // first lane of the group's first warp owns its bulk stores
         bool ok = true;
         for (long long tile = blockIdx.x; ok && tile < g.totalTiles; tile += gridDim.x, ++tileCount) {
             const TileCoord t = tileCoord(g, tile);
             const unsigned acc = tileCount & 1, accPhase = (tileCount >> 1) & 1;
-            ok = mbarWait(accFullBar + 8 * acc, accPhase, abortFlag, kStatusEpilogueWait);
-            ok = __all_sync(0xFFFFFFFFu, ok);
+            mbarWait(accFullBar + 8 * acc, accPhase, abortFlag, kStatusEpilogueWait);
+            epilogueBarrier(group);  // the four warps take the same decision: a wait that gave up has raised the flag by now
+            ok = *abortFlag == 0;
             if (!ok) break;
             tcgen05FenceAfter();
             const int row = t.row * kBM + quarter * 32 + lane;
             const int col0 = t.col * BN;
             const unsigned taddr = tmemBase + acc * BN + (unsigned(quarter * 32) << 16);
             const bool rowOk = row < g.m;
+            const int rowInTile = quarter * 32 + lane;
             if (g.kind == kKindI8) {
                 Epilogue<int> epi;
                 epi.init(g.epi, t.batch);
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
-                    if (col0 + c >= g.n) break;
-                    unsigned v[32];
-                    tmemLoad32(taddr + c, v);
-                    if (rowOk) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + c + j < g.n) epi.store(row, col0 + c + j, int(v[j]));
-                    }
-                }
+                if (g.tmaStore && epi.mode == kStoreS32 && !g.debugSkipStore)
+                    drainAccumulatorStaged<BN, kStoreS32>(epi, taddr, rowInTile, row, rowOk, t.row * kBM, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
+                else
+                    drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
             } else {
                 Epilogue<float> epi;
                 epi.init(g.epi, t.batch);
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
-                    if (col0 + c >= g.n) break;
-                    unsigned v[32];
-                    tmemLoad32(taddr + c, v);
-                    if (rowOk) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + c + j < g.n) epi.store(row, col0 + c + j, __uint_as_float(v[j]));
-                    }
-                }
+                const bool staged = g.tmaStore && !g.debugSkipStore;
+                if (staged && epi.mode == kStoreF32)
+                    drainAccumulatorStaged<BN, kStoreF32>(epi, taddr, rowInTile, row, rowOk, t.row * kBM, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
+                else if (staged && epi.mode == kStoreF16)
+                    drainAccumulatorStaged<BN, kStoreF16>(epi, taddr, rowInTile, row, rowOk, t.row * kBM, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
+                else if (staged && epi.mode == kStoreBF16)
+                    drainAccumulatorStaged<BN, kStoreBF16>(epi, taddr, rowInTile, row, rowOk, t.row * kBM, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
+                else
+                    drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
             }
             tcgen05FenceBefore();
             __syncwarp();
             if (lane == 0) mbarArrive(accEmptyBar + 8 * acc);
         }
+        if (issuer) tmaStoreWaitAll();  // the bulk stores read shared memory and must be done before the CTA ends
     }
 
     // ---- common exit ----
@@ -431,12 +566,15 @@ int ummaKindOf(const Problem& p) {
     if (p.typeA != p.typeB) return -1;
     if ((p.typeA == kF16 || p.typeA == kBF16) && p.accType == kF32) return kKindF16;
     if (p.typeA == kS8 && p.accType == kS32) return kKindI8;
-    if (p.typeA == kF32 && p.accType == kF32 && p.allowTf32) return kKindTf32;
+    // fp32 operands contiguous along m or n would need the 32-byte-atom swizzle (the only MN-major layout the
+    // tensor cores take for 32-bit elements); they stay on the FFMA kernel
+    if (p.typeA == kF32 && p.accType == kF32 && p.allowTf32 && p.transA && !p.transB) return kKindTf32;
     return -1;
 }
 
 template <int BN>
-cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtensorMap& mapB, int slot, cudaStream_t stream) {
+cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtensorMap& mapB, const CUtensorMap& mapD, int slot,
+                       cudaStream_t stream) {
     using Plan = SmemPlan<BN>;
     DeviceInfo& d = deviceInfo();
     if (!d.attrSet[slot]) {
@@ -446,7 +584,7 @@ cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtenso
         d.attrSet[slot] = true;
     }
     const unsigned grid = unsigned(std::min<long long>(g.totalTiles, d.sms));
-    ummaGemmKernel<BN><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(g, mapA, mapB);
+    ummaGemmKernel<BN><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(g, mapA, mapB, mapD);
     countLaunch();
     return cudaGetLastError();
 }
@@ -479,6 +617,9 @@ cudaError_t launchUmma(const Problem& p) {
         const long long cost = (tiles + d.sms - 1) / d.sms * (cand + 32);
         if (best < 0 || cost < best) best = cost, bn = cand;
     }
+    static const int forcedBn = [] { const char* v = std::getenv("VKZB_UMMA_BN"); return v ? std::atoi(v) : 0; }();
+    if (forcedBn == 256 || forcedBn == 128 || forcedBn == 64) bn = forcedBn;
+    static const int skipStore = [] { const char* v = std::getenv("VKZB_UMMA_SKIP_STORE"); return v ? std::atoi(v) : 0; }();
 
     UmmaArgs g{};
     g.m = p.m, g.n = p.n, g.k = p.k, g.batch = p.batch;
@@ -509,6 +650,7 @@ cudaError_t launchUmma(const Problem& p) {
     g.batchMulA = p.batch > 1 && p.strideA != 0;
     g.batchMulB = p.batch > 1 && p.strideB != 0;
     g.epi = p.epi;
+    g.debugSkipStore = skipStore;
 
     CUtensorMap mapA, mapB;
     const long long batchA = g.batchMulA ? p.batch : 1, batchB = g.batchMulB ? p.batch : 1;
@@ -518,9 +660,31 @@ cudaError_t launchUmma(const Problem& p) {
                                 : encodeOperand(&mapB, p.B, p.typeB, p.k, p.n, p.ldb, batchB, p.strideB, g.sliceElems, bn);
     if (!okA || !okB) return cudaErrorInvalidValue;
 
-    if (bn == 256) return launchWith<256>(g, mapA, mapB, 0, p.stream);
-    if (bn == 128) return launchWith<128>(g, mapA, mapB, 1, p.stream);
-    return launchWith<64>(g, mapA, mapB, 2, p.stream);
+    // D through TMA when every address the bulk stores start at is 16-byte aligned; otherwise direct stores.
+    // (With beta != 0 and C another matrix than D, C's type must be D's: the staged form reads C as D's type.)
+    CUtensorMap mapD{};
+    const EpilogueArgs& e = p.epi;
+    const int esD = dtypeSize(e.typeD);
+    // TMA clips a store at the tensor's edge in units of 16 bytes, so a column length that is not a multiple of 16 bytes
+    // would let it write into the padding between m and ldd: those shapes keep the direct stores too.
+    g.tmaStore = !e.pointerArrays && (reinterpret_cast<uintptr_t>(e.D) & 15) == 0 && (e.ldd * esD) % 16 == 0 && ((long long)p.m * esD) % 16 == 0 &&
+                 (p.batch == 1 || (e.strideD * esD) % 16 == 0) && (p.batch == 1 || e.strideD != 0);
+    static const int noTmaStore = [] { const char* v = std::getenv("VKZB_UMMA_DIRECT_STORE"); return v ? std::atoi(v) : 0; }();
+    if (noTmaStore) g.tmaStore = 0;
+    if (g.tmaStore) {
+        const CUtensorMapDataType dt = e.typeD == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : e.typeD == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                       : e.typeD == kS32 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+        const cuuint64_t dims[3] = {cuuint64_t(p.m), cuuint64_t(p.n), cuuint64_t(p.batch)};
+        const cuuint64_t strides[2] = {cuuint64_t(e.ldd) * esD, p.batch > 1 ? cuuint64_t(e.strideD) * esD : cuuint64_t(e.ldd) * esD * cuuint64_t(p.n)};
+        const cuuint32_t box[3] = {cuuint32_t(kBM), cuuint32_t(kStoreCols), 1}, ones[3] = {1, 1, 1};
+        if (encodeTiled()(&mapD, dt, 3, e.D, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            g.tmaStore = 0;
+    }
+
+    if (bn == 256) return launchWith<256>(g, mapA, mapB, mapD, 0, p.stream);
+    if (bn == 128) return launchWith<128>(g, mapA, mapB, mapD, 1, p.stream);
+    return launchWith<64>(g, mapA, mapB, mapD, 2, p.stream);
 }
 
 int ummaDeviceStatus() {
