@@ -1,0 +1,295 @@
+"""Behaviour of the C ABI beyond the case table: status codes, pointer modes, stream capture, int8, cuBLASLt, Sgemv, Dgemm.
+
+Expectations follow k0zi/Vulkanizer: validation and early outs src/cublas/cublas.cpp:698-710; `_64` forms :1161-1209; Sgemv
+:1143-1159 and tests/cublas.cpp:345-392; cuBLASLt tests/cublas.cpp:395-488 (D may differ from C, C stays untouched, D is rounded
+once before bias / activation); f64 tests/cublas.cpp:265-340; 4 KiB-aliased leading dimensions checked on a sample of C,
+tests/cublas.cpp:550-585. int8 has no counterpart in the reference: the expectation is exact integer arithmetic.
+"""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+
+from harness import CUDA_TYPE, DeviceBuffer, N, T
+from oracle import pyoracle as orc
+from vulkanizer_b200 import capi
+
+
+@pytest.fixture(scope="module")
+def blas(cuda):
+    b = capi.Cublas()
+    yield b
+    b.destroy()
+
+
+@pytest.fixture(scope="module")
+def lt(cuda):
+    h = capi.CublasLt()
+    yield h
+    h.destroy()
+
+
+# ---- status codes ------------------------------------------------------------------------------------------------
+
+@pytest.mark.gpu
+def test_validation_and_early_outs(cuda, blas):
+    A, _ = orc.fill_lcg("f32", 64, 1)
+    d = DeviceBuffer(cuda, A)
+    p = d.ptr
+    S = capi
+    assert blas.sgemm(N, N, -1, 2, 2, 1.0, p, 2, p, 2, 0.0, p, 2, check=False) == S.STATUS_INVALID_VALUE      # negative size
+    assert blas.sgemm(N, N, 4, 2, 2, 1.0, p, 3, p, 2, 0.0, p, 4, check=False) == S.STATUS_INVALID_VALUE       # lda < rows of A
+    assert blas.sgemm(T, N, 4, 2, 2, 1.0, p, 1, p, 2, 0.0, p, 4, check=False) == S.STATUS_INVALID_VALUE       # op(A) = T: lda < k
+    assert blas.sgemm(N, N, 4, 2, 2, 1.0, p, 4, p, 2, 0.0, p, 3, check=False) == S.STATUS_INVALID_VALUE       # ldc < m
+    assert blas.sgemm(7, N, 4, 2, 2, 1.0, p, 4, p, 2, 0.0, p, 4, check=False) == S.STATUS_INVALID_VALUE       # bad operation
+    before = blas.launch_count()
+    assert blas.sgemm(N, N, 0, 2, 2, 1.0, p, 1, p, 2, 0.0, p, 1, check=False) == S.STATUS_SUCCESS             # m = 0: nothing to do
+    assert blas.sgemm(N, N, 2, 0, 2, 1.0, p, 2, p, 2, 0.0, p, 2, check=False) == S.STATUS_SUCCESS
+    assert blas.launch_count() == before and blas.last_path() == S.PATH_NONE
+    # null alpha
+    lib = blas.lib
+    assert lib.cublasSgemm_v2(blas.handle, N, N, 2, 2, 2, None, p, 2, p, 2, None, p, 2) == S.STATUS_INVALID_VALUE
+    # unsupported type combinations
+    assert blas.gemm_ex(N, N, 2, 2, 2, 1.0, p, S.CUDA_R_8I, 4, p, S.CUDA_R_8I, 4, 0.0, p, S.CUDA_R_32F, 4, S.COMPUTE_32F, check=False) == S.STATUS_NOT_SUPPORTED
+    assert blas.gemm_ex(N, N, 2, 2, 2, 1.0, p, 4, 4, p, 4, 4, 0.0, p, 4, 4, S.COMPUTE_32F, check=False) == S.STATUS_NOT_SUPPORTED  # complex
+    assert lib.cublasSgemm_v2_64(blas.handle, N, N, 1 << 32, 1, 1, None, p, 1 << 32, p, 1, None, p, 1 << 32) == S.STATUS_NOT_SUPPORTED
+    assert d.download() is not None  # guard bands intact
+
+
+@pytest.mark.gpu
+def test_k_zero_and_beta_zero_semantics(cuda, blas):
+    """k = 0 scales C by beta (tests/cublas.cpp:662); beta = 0 must not read C, so NaNs in C do not propagate."""
+    m, n, k = 70, 33, 40
+    A, av = orc.fill_lcg("f16", m * k, 1)
+    B, bv = orc.fill_lcg("f16", k * n, 2)
+    Cn = np.full(m * n, np.nan, dtype=np.float32)
+    dA, dB, dC = DeviceBuffer(cuda, A), DeviceBuffer(cuda, B), DeviceBuffer(cuda, Cn)
+    blas.gemm_ex(T, N, m, n, k, 1.0, dA.ptr, capi.CUDA_R_16F, k, dB.ptr, capi.CUDA_R_16F, k, 0.0, dC.ptr, capi.CUDA_R_32F, m)
+    got = dC.download()
+    want = av.reshape(m, k).astype(np.float64) @ bv.reshape(n, k).astype(np.float64).T
+    assert np.isfinite(got).all() and np.allclose(got.reshape(n, m).T, want, atol=1e-4)
+
+
+# ---- pointer modes and stream capture ------------------------------------------------------------------------------
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(256, 136, 192, "f16"), (200, 130, 100, "f32"), (300, 1, 257, "f16")])
+def test_device_pointer_mode_inside_stream_capture(cuda, shape):
+    """alpha and beta live on the device and the call is captured into a CUDA graph: nothing may synchronise or copy back
+    (the reference copies each scalar to the host with a blocking call, cublas.cpp:241-243, and so cannot be captured)."""
+    torch = cuda
+    m, n, k, kind = shape
+    A, _ = orc.fill_lcg(kind, m * k, 1)
+    B, _ = orc.fill_lcg(kind, k * n, 2)
+    Cm, _ = orc.fill_lcg("f32", m * n, 3)
+    want, want_abs = orc.gemm_fp64(True, False, m, n, k, 1, 0.75, A, kind, k, 0, B, kind, k, 0, -1.5, Cm, "f32", m, 0)
+    dA, dB, dC = DeviceBuffer(torch, A), DeviceBuffer(torch, B), DeviceBuffer(torch, Cm)
+    scalars = torch.tensor([0.75, -1.5], dtype=torch.float32, device="cuda")
+    b = capi.Cublas()
+    b.set_pointer_mode(capi.POINTER_MODE_DEVICE)
+    stream = torch.cuda.Stream()
+    b.set_stream(stream.cuda_stream)
+    t = CUDA_TYPE[kind]
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            b.gemm_ex(T, N, m, n, k, scalars.data_ptr(), dA.ptr, t, k, dB.ptr, t, k, scalars.data_ptr() + 4, dC.ptr, capi.CUDA_R_32F, m,
+                      device_scalars=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(dC.download(), Cm), "capturing must not run the kernel"
+    graph.replay()
+    torch.cuda.synchronize()
+    got = dC.download()
+    tol = 1e-5 * np.maximum(1, np.abs(want)) * math.sqrt(k + 1)
+    assert (np.abs(got - want) <= tol).all()
+    b.destroy()
+
+
+# ---- int8 -> int32 (bit exact) ---------------------------------------------------------------------------------------
+
+S8_CASES = [
+    # ta, tb, m, n, k, lda pad, alpha, beta, batch
+    ("tn aligned tensor cores", T, N, 256, 192, 512, 0, 1, 0, 1),
+    ("tn ragged edges", T, N, 200, 137, 400, 0, 1, 0, 1),
+    ("tn k tail and beta", T, N, 130, 72, 1000, 0, 3, -2, 1),
+    ("tn batched", T, N, 128, 96, 256, 0, 1, 0, 5),
+    ("tn long k", T, N, 64, 48, 11008, 0, 1, 0, 1),
+    ("nn aligned", N, N, 256, 128, 256, 0, 1, 0, 1),
+    ("nt aligned", N, T, 144, 160, 192, 0, 2, 1, 1),
+    ("tt aligned", T, T, 160, 144, 320, 0, 1, 0, 1),
+    ("tn unaligned ld (generic kernel)", T, N, 70, 33, 129, 3, 1, 1, 1),
+    ("gemv int8", T, N, 300, 1, 512, 0, 1, 0, 1),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", S8_CASES, ids=lambda c: c[0])
+def test_int8_gemm_is_bit_exact(cuda, blas, case):
+    from vulkanizer_b200 import synth
+    name, ta, tb, m, n, k, pad, alpha, beta, batch = case
+    rows_a, cols_a = (k, m) if ta == T else (m, k)
+    rows_b, cols_b = (n, k) if tb == T else (k, n)
+    lda, ldb, ldc = rows_a + pad, rows_b + pad, m + (2 if pad else 0)
+    sA, sB, sC = lda * cols_a, ldb * cols_b, ldc * n
+    A = synth.int8_uniform(2, sA * batch)
+    B = synth.int8_uniform(2, sB * batch, first=sA * batch)
+    C0 = (synth.int8_uniform(9, sC * batch).astype(np.int32)) * 1000
+    want = orc.gemm_s8(ta == T, tb == T, m, n, k, batch, alpha, A, lda, sA, B, ldb, sB, beta, C0.copy(), ldc, sC)
+    dA, dB, dC = DeviceBuffer(cuda, A), DeviceBuffer(cuda, B), DeviceBuffer(cuda, C0)
+    blas.gemm_strided_batched_ex(ta, tb, m, n, k, alpha, dA.ptr, capi.CUDA_R_8I, lda, sA, dB.ptr, capi.CUDA_R_8I, ldb, sB, beta, dC.ptr,
+                                 capi.CUDA_R_32I, ldc, sC, batch, capi.COMPUTE_32I)
+    got = dC.download()
+    assert np.array_equal(got, want), f"{name}: {int((got != want).sum())} of {got.size} differ"
+    if "tensor cores" in name or "aligned" in name and "unaligned" not in name:
+        assert blas.last_path() == capi.PATH_UMMA
+    assert blas.device_status() == 0
+
+
+# ---- cuBLASLt ----------------------------------------------------------------------------------------------------------
+
+LT_CASES = [
+    ("lt TN bias", T, N, 70, 33, 40, 1, "f32", capi.LT_EPILOGUE_BIAS, 1.0, 0.0),
+    ("lt NN relu bias beta", N, N, 50, 20, 64, 1, "f32", capi.LT_EPILOGUE_RELU_BIAS, 0.5, 1.5),
+    ("lt TN gelu bias f16", T, N, 64, 48, 32, 1, "f16", capi.LT_EPILOGUE_GELU_BIAS, 1.0, 0.0),
+    ("lt NT default batched", N, T, 30, 17, 25, 3, "f32", capi.LT_EPILOGUE_DEFAULT, 1.0, -1.0),
+    ("lt TN gelu bf16 tensor cores", T, N, 256, 136, 128, 2, "bf16", capi.LT_EPILOGUE_GELU, 1.0, 0.5),
+    ("lt TN relu bias f16 tensor cores", T, N, 384, 264, 192, 1, "f16", capi.LT_EPILOGUE_RELU_BIAS, 0.5, 0.0),
+    ("lt TN default f16 -> D != C", T, N, 256, 128, 64, 1, "f16", capi.LT_EPILOGUE_DEFAULT, 1.0, 2.0),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", LT_CASES, ids=lambda c: c[0])
+def test_lt_matmul_fused_epilogue(cuda, lt, case):
+    name, ta, tb, m, n, k, batch, kind, epilogue, alpha, beta = case
+    rows_a, cols_a = (k, m) if ta == T else (m, k)
+    rows_b, cols_b = (n, k) if tb == T else (k, n)
+    sA, sB, sC = rows_a * cols_a, rows_b * cols_b, m * n
+    A, _ = orc.fill_lcg(kind, sA * batch, 31)
+    B, _ = orc.fill_lcg(kind, sB * batch, 32)
+    Cm, _ = orc.fill_lcg(kind, sC * batch, 33)
+    D0, _ = orc.fill_lcg(kind, sC * batch, 34)
+    bias, _ = orc.fill_lcg(kind, m, 35)
+    bits = (1 if epilogue & capi.LT_EPILOGUE_BIAS else 0) | (2 if (epilogue & ~4) == capi.LT_EPILOGUE_RELU else 0) | \
+           (4 if (epilogue & ~4) == capi.LT_EPILOGUE_GELU else 0)
+    want = orc.lt_fp64(ta == T, tb == T, m, n, k, batch, alpha, A, B, beta, Cm, bias, kind, bits)
+    dA, dB, dC, dD, dBias = (DeviceBuffer(cuda, x) for x in (A, B, Cm, D0, bias))
+    t = CUDA_TYPE[kind]
+    lt.matmul(ta, tb, m, n, k, alpha, dA.ptr, t, rows_a, dB.ptr, t, rows_b, beta, dC.ptr, t, m, dD.ptr, t, m, epilogue=epilogue,
+              bias=dBias.ptr, batch=batch, stride_a=sA, stride_b=sB, stride_c=sC, stride_d=sC)
+    got = orc.to_float(dD.download(), kind)
+    rel = 1e-5 if kind == "f32" else 4e-3 if kind == "f16" else 1.6e-2
+    tol = rel * np.maximum(1.0, np.abs(want)) * math.sqrt(k)
+    bad = ~(np.abs(got - want) <= tol)
+    assert not bad.any(), f"{name}: {int(bad.sum())} wrong, first got {got[np.argmax(bad)]} want {want[np.argmax(bad)]}"
+    assert np.array_equal(dC.download(), Cm), "C is only read"
+    if "tensor cores" in name:
+        assert lt.last_path() == capi.PATH_UMMA
+
+
+@pytest.mark.gpu
+def test_lt_refuses_what_it_does_not_serve(cuda, lt):
+    A, _ = orc.fill_lcg("f32", 64 * 64, 1)
+    d = DeviceBuffer(cuda, A)
+    args = (N, N, 8, 8, 8, 1.0, d.ptr, capi.CUDA_R_32F, 8, d.ptr, capi.CUDA_R_32F, 8, 0.0, d.ptr, capi.CUDA_R_32F, 8, d.ptr, capi.CUDA_R_32F, 8)
+    assert lt.matmul(*args, epilogue=128 | 2, check=False) == capi.STATUS_NOT_SUPPORTED   # RELU_AUX
+    assert lt.matmul(*args, order=1, check=False) == capi.STATUS_NOT_SUPPORTED            # row-major layouts
+    assert lt.matmul(*args, epilogue=capi.LT_EPILOGUE_BIAS, bias=0, check=False) == capi.STATUS_INVALID_VALUE  # bias epilogue without a pointer
+    assert lt.matmul(*args, check=False) == capi.STATUS_SUCCESS
+
+
+@pytest.mark.gpu
+def test_cublas_handle_is_a_valid_lt_handle(cuda, blas):
+    """Applications pass a cublasHandle_t where a cublasLtHandle_t is expected (the reference's own test does,
+    tests/cublas.cpp:447-452); both libraries share one context layout."""
+    lt = capi.CublasLt()
+    real = lt.handle
+    lt.handle = blas.handle
+    try:
+        A, av = orc.fill_lcg("f32", 16 * 16, 1)
+        Cz = np.zeros(256, dtype=np.float32)
+        dA, dD = DeviceBuffer(cuda, A), DeviceBuffer(cuda, Cz)
+        lt.matmul(N, N, 16, 16, 16, 1.0, dA.ptr, capi.CUDA_R_32F, 16, dA.ptr, capi.CUDA_R_32F, 16, 0.0, dD.ptr, capi.CUDA_R_32F, 16, dD.ptr,
+                  capi.CUDA_R_32F, 16)
+        a = av.reshape(16, 16).T.astype(np.float64)
+        assert np.allclose(dD.download().reshape(16, 16).T, a @ a, atol=1e-4)
+    finally:
+        lt.handle = real
+        lt.destroy()
+
+
+# ---- Sgemv, Dgemm, batched pointers, aliased leading dimensions -------------------------------------------------------
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("trans, m, n, incx, incy", [(N, 300, 77, 1, 1), (T, 130, 1000, 1, 1), (N, 65, 200, 3, 2), (T, 70, 129, 2, 5)])
+def test_sgemv(cuda, blas, trans, m, n, incx, incy):
+    lda = m + 3
+    rows, cols = (n, m) if trans == T else (m, n)   # op(A) is rows x cols
+    A, av = orc.fill_lcg("f32", lda * n, 1)
+    x, xv = orc.fill_lcg("f32", cols * incx, 2)
+    y, yv = orc.fill_lcg("f32", rows * incy, 3)
+    dA, dx, dy = DeviceBuffer(cuda, A), DeviceBuffer(cuda, x), DeviceBuffer(cuda, y)
+    blas.sgemv(trans, m, n, 0.5, dA.ptr, lda, dx.ptr, incx, -2.0, dy.ptr, incy)
+    a = av.reshape(n, lda)[:, :m].T.astype(np.float64)      # m x n
+    op = a.T if trans == T else a
+    want = yv.astype(np.float64).copy()
+    want[::incy][:rows] = 0.5 * (op @ xv[::incx][:cols].astype(np.float64)) - 2.0 * yv[::incy][:rows]
+    got = dy.download()
+    assert np.allclose(got, want, atol=1e-5 * math.sqrt(cols + 1) * max(1.0, np.abs(want).max()))  # strided gaps of y untouched too
+    assert blas.last_path() == capi.PATH_GEMV
+    assert blas.sgemv(N, 4, 4, 1.0, dA.ptr, 4, dx.ptr, -1, 0.0, dy.ptr, 1, check=False) == capi.STATUS_NOT_SUPPORTED   # negative increment
+    assert blas.sgemv(N, 4, 4, 1.0, dA.ptr, 4, dx.ptr, 0, 0.0, dy.ptr, 1, check=False) == capi.STATUS_INVALID_VALUE
+    assert blas.lib.cublasSgemv_v2_64(blas.handle, N, 1 << 32, 1, None, dA.ptr, 1 << 32, dx.ptr, 1, None, dy.ptr, 1) == capi.STATUS_NOT_SUPPORTED
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ta, tb", [(N, N), (T, N), (N, T), (T, T)])
+def test_dgemm(cuda, blas, ta, tb):
+    rng = np.random.default_rng(11)
+    m, n, k = 67, 45, 130
+    rows_a, cols_a = (k, m) if ta == T else (m, k)
+    rows_b, cols_b = (n, k) if tb == T else (k, n)
+    lda, ldb, ldc = rows_a + 3, rows_b + 1, m + 2
+    A = rng.standard_normal(lda * cols_a)
+    B = rng.standard_normal(ldb * cols_b)
+    C0 = rng.standard_normal(ldc * n)
+    dA, dB, dC = DeviceBuffer(cuda, A), DeviceBuffer(cuda, B), DeviceBuffer(cuda, C0)
+    blas.dgemm(ta, tb, m, n, k, 1.25, dA.ptr, lda, dB.ptr, ldb, -0.5, dC.ptr, ldc)
+    a = A.reshape(cols_a, lda)[:, :rows_a].T
+    b = B.reshape(cols_b, ldb)[:, :rows_b].T
+    want = C0.copy().reshape(n, ldc)
+    want[:, :m] = (1.25 * ((a.T if ta == T else a) @ (b.T if tb == T else b)) - 0.5 * C0.reshape(n, ldc)[:, :m].T).T
+    assert np.allclose(dC.download(), want.ravel(), rtol=0, atol=1e-12 * k)
+
+
+@pytest.mark.gpu
+def test_aliased_leading_dimension_sample(cuda, blas):
+    """Leading dimensions that are multiples of 4 KiB (tests/cublas.cpp:550-585 checks every 7th row and column and the last)."""
+    m, n, k, ld = 300, 264, 2048, 2048
+    A, _ = orc.fill_lcg("f16", ld * m, 1)
+    B, _ = orc.fill_lcg("f16", ld * n, 2)
+    Cz = np.zeros(m * n, dtype=np.float32)
+    dA, dB, dC = DeviceBuffer(cuda, A), DeviceBuffer(cuda, B), DeviceBuffer(cuda, Cz)
+    blas.gemm_ex(T, N, m, n, k, 1.0, dA.ptr, capi.CUDA_R_16F, ld, dB.ptr, capi.CUDA_R_16F, ld, 0.0, dC.ptr, capi.CUDA_R_32F, m)
+    rows = sorted(set(range(0, m, 7)) | {m - 1})
+    cols = sorted(set(range(0, n, 7)) | {n - 1})
+    want = orc.dots_fp64(True, False, k, A, "f16", ld, B, "f16", ld, rows, cols)
+    got = dC.download().reshape(n, m).T[np.ix_(rows, cols)]
+    assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max()) * math.sqrt(k + 1)
+    assert blas.last_path() == capi.PATH_UMMA
+
+
+@pytest.mark.gpu
+def test_operand_shared_by_every_batch_entry(cuda, blas):
+    """strideA = 0: one A for the whole batch (what cublasLtMatmul passes for a non-batched operand, cublasLt.cpp:381)."""
+    m, n, k, batch = 128, 96, 64, 4
+    A, av = orc.fill_lcg("f16", m * k, 1)
+    B, bv = orc.fill_lcg("f16", k * n * batch, 2)
+    Cz = np.zeros(m * n * batch, dtype=np.float32)
+    dA, dB, dC = DeviceBuffer(cuda, A), DeviceBuffer(cuda, B), DeviceBuffer(cuda, Cz)
+    blas.gemm_strided_batched_ex(T, N, m, n, k, 1.0, dA.ptr, capi.CUDA_R_16F, k, 0, dB.ptr, capi.CUDA_R_16F, k, k * n, 0.0, dC.ptr,
+                                 capi.CUDA_R_32F, m, m * n, batch)
+    a = av.reshape(m, k).astype(np.float64)
+    want = np.stack([(a @ bv.reshape(batch, n, k)[e].astype(np.float64).T).T for e in range(batch)])
+    assert np.allclose(dC.download().reshape(batch, n, m), want, atol=1e-4)

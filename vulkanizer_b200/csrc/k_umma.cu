@@ -612,13 +612,15 @@ cudaError_t launchUmma(const Problem& p) {
     const int tilesM = (p.m + kBM - 1) / kBM;
     int bn = 256;
     long long best = -1;
+    const int mnBoxElems = kSliceBytes / es;  // an MN-major operand arrives in boxes of 128 bytes of m or n
     for (int cand : {256, 128, 64}) {
+        if (p.transB && cand % mnBoxElems != 0) continue;  // int8 B^T: a box holds 128 columns, so no 64-wide tile
         const long long tiles = (long long)tilesM * ((p.n + cand - 1) / cand) * p.batch;
         const long long cost = (tiles + d.sms - 1) / d.sms * (cand + 32);
         if (best < 0 || cost < best) best = cost, bn = cand;
     }
     static const int forcedBn = [] { const char* v = std::getenv("VKZB_UMMA_BN"); return v ? std::atoi(v) : 0; }();
-    if (forcedBn == 256 || forcedBn == 128 || forcedBn == 64) bn = forcedBn;
+    if ((forcedBn == 256 || forcedBn == 128 || forcedBn == 64) && !(p.transB && forcedBn % mnBoxElems != 0)) bn = forcedBn;
     static const int skipStore = [] { const char* v = std::getenv("VKZB_UMMA_SKIP_STORE"); return v ? std::atoi(v) : 0; }();
 
     UmmaArgs g{};
