@@ -388,7 +388,7 @@ def main():
     if args.impl == "reference":
         return run_reference_arm(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world > 1 or args.gpus > 1:
+    if world > 1 or args.gpus > 1 or args.workload == "cfg5b_bf16_32768_nsharded":
         from vulkanizer_b200 import multi_gpu_bench
         return multi_gpu_bench.run(args)
     return run_single_gpu(args)

@@ -1,0 +1,116 @@
+"""One rank of the collective test: run as a child process by tests/test_nccl_gpu.py (and by hand on a multi-GPU box).
+
+    python tests/nccl_worker.py <id file> <nranks> <rank> <device>
+
+Every collective of this repository's libnccl.so.2 is run on integer-valued data, so the expected results are exact
+(`==` comparisons, as in k0zi/Vulkanizer's tests/nccl.cpp:88, 111-112). Prints "rank <r> ok" on success.
+"""
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+
+def main():
+    id_file, nranks, rank, device = Path(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4])
+    import torch
+    from vulkanizer_b200 import capi
+
+    torch.cuda.set_device(device)
+    torch.zeros(1, device="cuda")
+    if rank == 0:
+        tmp = id_file.with_suffix(".tmp")
+        tmp.write_bytes(capi.NcclComm.unique_id())
+        tmp.rename(id_file)
+    deadline = time.time() + 60
+    while not id_file.exists():
+        assert time.time() < deadline, "rank 0 never published the unique id"
+        time.sleep(0.01)
+    comm = capi.NcclComm(nranks, rank, id_file.read_bytes())
+    stream = torch.cuda.Stream()
+    s = stream.cuda_stream
+    n = 1000
+
+    def dev(a):
+        return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+    def val(r, count=n):  # what rank r contributes
+        return (np.arange(count) % 17 - 8 + 3 * r).astype(np.float32)
+
+    with torch.cuda.stream(stream):
+        # all-gather, out of place and in place
+        send, recv = dev(val(rank)), torch.zeros(n * nranks, device="cuda")
+        comm.all_gather(send.data_ptr(), recv.data_ptr(), n, "float32", s)
+        stream.synchronize()
+        assert np.array_equal(recv.cpu().numpy(), np.concatenate([val(r) for r in range(nranks)]))
+        inplace = torch.zeros(n * nranks, device="cuda")
+        inplace[rank * n:(rank + 1) * n] = send
+        comm.all_gather(inplace.data_ptr() + 4 * rank * n, inplace.data_ptr(), n, "float32", s)
+        stream.synchronize()
+        assert np.array_equal(inplace.cpu().numpy(), np.concatenate([val(r) for r in range(nranks)]))
+        # all-reduce: sum in place, max out of place, bf16 average, int64 product-free sum
+        x = dev(val(rank))
+        comm.all_reduce(x.data_ptr(), x.data_ptr(), n, "float32", capi.NCCL_SUM, s)
+        stream.synchronize()
+        assert np.array_equal(x.cpu().numpy(), sum(val(r) for r in range(nranks)))
+        y, out = dev(val(rank)), torch.zeros(n, device="cuda")
+        comm.all_reduce(y.data_ptr(), out.data_ptr(), n, "float32", capi.NCCL_MAX, s)
+        stream.synchronize()
+        assert np.array_equal(out.cpu().numpy(), np.max([val(r) for r in range(nranks)], axis=0))
+        h = dev(val(rank)).to(torch.bfloat16)
+        comm.all_reduce(h.data_ptr(), h.data_ptr(), n, "bfloat16", capi.NCCL_AVG, s)
+        stream.synchronize()
+        want = torch.from_numpy(sum(val(r) for r in range(nranks)) / nranks).to(torch.bfloat16)
+        assert torch.equal(h.cpu(), want)
+        i64 = dev((np.arange(7) + rank * 10).astype(np.int64))  # fewer elements than ranks would leave empty slices: 7 > nranks here
+        comm.all_reduce(i64.data_ptr(), i64.data_ptr(), 7, "int64", capi.NCCL_SUM, s)
+        stream.synchronize()
+        assert np.array_equal(i64.cpu().numpy(), sum(np.arange(7) + r * 10 for r in range(nranks)))
+        # broadcast from the last rank
+        root = nranks - 1
+        b = dev(val(rank))
+        comm.broadcast(b.data_ptr(), b.data_ptr(), n, "float32", root, s)
+        stream.synchronize()
+        assert np.array_equal(b.cpu().numpy(), val(root))
+        # reduce-scatter
+        full = dev(np.concatenate([val(rank) + 100 * q for q in range(nranks)]))
+        part = torch.zeros(n, device="cuda")
+        comm.reduce_scatter(full.data_ptr(), part.data_ptr(), n, "float32", capi.NCCL_SUM, s)
+        stream.synchronize()
+        assert np.array_equal(part.cpu().numpy(), sum(val(r) + 100 * rank for r in range(nranks)))
+        # reduce to rank 0, gather to rank 1 % nranks, all-to-all
+        r0 = torch.zeros(n, device="cuda")
+        comm.reduce(dev(val(rank)).data_ptr(), r0.data_ptr(), n, "float32", 0, capi.NCCL_SUM, s)
+        stream.synchronize()
+        if rank == 0:
+            assert np.array_equal(r0.cpu().numpy(), sum(val(r) for r in range(nranks)))
+        groot = 1 % nranks
+        g = torch.zeros(n * nranks, device="cuda")
+        keep = dev(val(rank))
+        comm.gather(keep.data_ptr(), g.data_ptr(), n, "float32", groot, s)
+        stream.synchronize()
+        if rank == groot:
+            assert np.array_equal(g.cpu().numpy(), np.concatenate([val(r) for r in range(nranks)]))
+        a2a_send = dev(np.concatenate([val(rank) + 1000 * q for q in range(nranks)]))
+        a2a_recv = torch.zeros(n * nranks, device="cuda")
+        comm.all_to_all(a2a_send.data_ptr(), a2a_recv.data_ptr(), n, "float32", s)
+        stream.synchronize()
+        assert np.array_equal(a2a_recv.cpu().numpy(), np.concatenate([val(r) + 1000 * rank for r in range(nranks)]))
+        # a large, repeated gather: buffers are mapped once and reused
+        big = 1 << 22
+        src = torch.full((big,), float(rank + 1), device="cuda")
+        dst = torch.zeros(big * nranks, device="cuda")
+        for _ in range(3):
+            comm.all_gather(src.data_ptr(), dst.data_ptr(), big, "float32", s)
+        stream.synchronize()
+        assert torch.equal(dst.view(nranks, big)[:, ::4096].cpu(), torch.arange(1, nranks + 1, dtype=torch.float32)[:, None].expand(nranks, big // 4096))
+    assert comm.async_error() == 0
+    comm.destroy()
+    print(f"rank {rank} ok", flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -10,6 +10,8 @@ from .capi import (  # noqa: F401
     BlasError,
     Cublas,
     CublasLt,
+    NcclComm,
+    nccl_library,
     build_libraries,
     cublas_library,
     cublaslt_library,

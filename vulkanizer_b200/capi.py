@@ -143,6 +143,111 @@ def cublaslt_library() -> C.CDLL:
     return _cublaslt
 
 
+_nccl = None
+NCCL_TYPES = {"int8": 0, "uint8": 1, "int32": 2, "uint32": 3, "int64": 4, "uint64": 5, "float16": 6, "float32": 7, "float64": 8, "bfloat16": 9}
+NCCL_SUM, NCCL_PROD, NCCL_MAX, NCCL_MIN, NCCL_AVG = range(5)
+
+
+class NcclUniqueId(C.Structure):
+    _fields_ = [("internal", C.c_char * 128)]
+
+
+def nccl_library() -> C.CDLL:
+    global _nccl
+    if _nccl is None:
+        lib = _load("libnccl.so.2")
+        coll = [_vp, _vp, _sz, _i]
+        protos = {
+            "ncclGetVersion": [C.POINTER(_i)],
+            "ncclGetUniqueId": [C.POINTER(NcclUniqueId)],
+            "ncclCommInitRank": [C.POINTER(_vp), _i, NcclUniqueId, _i],
+            "ncclCommInitAll": [C.POINTER(_vp), _i, C.POINTER(_i)],
+            "ncclCommDestroy": [_vp],
+            "ncclCommAbort": [_vp],
+            "ncclCommCount": [_vp, C.POINTER(_i)],
+            "ncclCommUserRank": [_vp, C.POINTER(_i)],
+            "ncclCommCuDevice": [_vp, C.POINTER(_i)],
+            "ncclCommGetAsyncError": [_vp, C.POINTER(_i)],
+            "ncclAllGather": coll + [_vp, _vp],
+            "ncclAllReduce": coll + [_i, _vp, _vp],
+            "ncclReduceScatter": coll + [_i, _vp, _vp],
+            "ncclReduce": coll + [_i, _i, _vp, _vp],
+            "ncclBroadcast": coll + [_i, _vp, _vp],
+            "ncclGather": coll + [_i, _vp, _vp],
+            "ncclAlltoAll": coll + [_vp, _vp],
+            "ncclGroupStart": [],
+            "ncclGroupEnd": [],
+        }
+        for name, args in protos.items():
+            fn = getattr(lib, name)
+            fn.argtypes, fn.restype = args, _i
+        lib.ncclGetErrorString.argtypes, lib.ncclGetErrorString.restype = [_i], C.c_char_p
+        lib.ncclGetLastError.argtypes, lib.ncclGetLastError.restype = [_vp], C.c_char_p
+        _nccl = lib
+    return _nccl
+
+
+class NcclError(RuntimeError):
+    pass
+
+
+class NcclComm:
+    """One communicator of this repository's libnccl.so.2. The 128-byte unique id travels between the ranks by any means the
+    caller has (the benchmark broadcasts it with torch.distributed, as an MPI program would with MPI_Bcast)."""
+
+    def __init__(self, nranks: int, rank: int, unique_id: bytes):
+        self.lib = nccl_library()
+        uid = NcclUniqueId()
+        C.memmove(C.addressof(uid), unique_id, 128)
+        comm = _vp()
+        self._check("ncclCommInitRank", self.lib.ncclCommInitRank(C.byref(comm), nranks, uid, rank), None)
+        self.comm, self.nranks, self.rank = comm, nranks, rank
+
+    @staticmethod
+    def unique_id() -> bytes:
+        uid = NcclUniqueId()
+        status = nccl_library().ncclGetUniqueId(C.byref(uid))
+        if status:
+            raise NcclError(f"ncclGetUniqueId: {status}")
+        return C.string_at(C.addressof(uid), 128)
+
+    def _check(self, call, status, comm):
+        if status:
+            detail = self.lib.ncclGetLastError(comm).decode() if comm else ""
+            raise NcclError(f"{call}: {self.lib.ncclGetErrorString(status).decode()} ({detail})")
+
+    def all_gather(self, send, recv, count, dtype, stream=0):
+        self._check("ncclAllGather", self.lib.ncclAllGather(send, recv, count, NCCL_TYPES[dtype], self.comm, stream), self.comm)
+
+    def all_reduce(self, send, recv, count, dtype, op=NCCL_SUM, stream=0):
+        self._check("ncclAllReduce", self.lib.ncclAllReduce(send, recv, count, NCCL_TYPES[dtype], op, self.comm, stream), self.comm)
+
+    def reduce_scatter(self, send, recv, recvcount, dtype, op=NCCL_SUM, stream=0):
+        self._check("ncclReduceScatter", self.lib.ncclReduceScatter(send, recv, recvcount, NCCL_TYPES[dtype], op, self.comm, stream), self.comm)
+
+    def reduce(self, send, recv, count, dtype, root, op=NCCL_SUM, stream=0):
+        self._check("ncclReduce", self.lib.ncclReduce(send, recv, count, NCCL_TYPES[dtype], op, root, self.comm, stream), self.comm)
+
+    def broadcast(self, send, recv, count, dtype, root, stream=0):
+        self._check("ncclBroadcast", self.lib.ncclBroadcast(send, recv, count, NCCL_TYPES[dtype], root, self.comm, stream), self.comm)
+
+    def gather(self, send, recv, count, dtype, root, stream=0):
+        self._check("ncclGather", self.lib.ncclGather(send, recv, count, NCCL_TYPES[dtype], root, self.comm, stream), self.comm)
+
+    def all_to_all(self, send, recv, count, dtype, stream=0):
+        self._check("ncclAlltoAll", self.lib.ncclAlltoAll(send, recv, count, NCCL_TYPES[dtype], self.comm, stream), self.comm)
+
+    def async_error(self) -> int:
+        out = _i(0)
+        self.lib.ncclCommGetAsyncError(self.comm, C.byref(out))
+        return out.value
+
+    def destroy(self):
+        if self.comm is not None:
+            self.lib.ncclCommDestroy(self.comm)
+            self.comm = None
+
+
 def declared_symbols(header: str) -> list[str]:
     """Function names a header under include/ declares (for the export check)."""
     text = (INCLUDE_DIR / header).read_text()

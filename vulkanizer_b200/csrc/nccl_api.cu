@@ -1,0 +1,771 @@
+// libnccl.so.2: collectives between the ranks of one machine over NVLink / NVSwitch peer memory.
+//
+// Same exported surface as k0zi/Vulkanizer's src/nccl/nccl.cpp:497-753 (the subset declared in include/vkzb_nccl.h; the rest
+// answers ncclInvalidUsage like src/nccl/nccl_stubs.cpp:30-36), rebuilt for a machine whose GPUs reach one another directly:
+//
+//   bootstrap   a POSIX shared-memory object named after the 128-bit token in ncclUniqueId (the reference's
+//               UniqueId{magic, token[2]}, nccl.cpp:59-66, 503-509) holds one slot per rank; only ADDRESSES travel through it,
+//               as CUDA IPC handles of the caller's buffers, posted per operation in a 4-deep ring;
+//   data        every collective is "pull": after a barrier (all ranks' streams have reached the operation, so their send
+//               buffers are final) a rank reads its peers' send buffers through the IPC mappings, with stream-ordered
+//               cudaMemcpyAsync (copy engines, no SMs, so a gather overlaps a GEMM) or a reduction kernel, and a closing
+//               barrier tells the peers their buffers are free again;
+//   barriers    device side: each rank stores a sequence number into a flag word in every peer's arena
+//               (st.release.sys over NVLink) and waits, bounded by %globaltimer, for its own flags to reach it. The
+//               collective stays asynchronous on its stream. When two ranks share a GPU (kernels of different ranks may
+//               not wait on one another on one device) the ranks meet on counters in the shared-memory object instead and
+//               the call synchronises its stream, as the reference's does (nccl.cpp:338).
+//
+// Reductions accumulate floats in double and integers in 64 bits, in rank order (nccl.cpp:152-182): identical bits everywhere.
+// Every wait is bounded: VKZB_NCCL_TIMEOUT_S seconds on the host (default 120), 20 s on the device; ncclCommAbort releases
+// host waiters (nccl.cpp:554-557).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <random>
+#include <string>
+#include <thread>
+#include <vector>
+
+#define VKZB_HAVE_CUDA_TYPES
+#include "../../include/vkzb_nccl.h"
+
+namespace {
+
+constexpr int kMaxRanks = 16;
+constexpr uint32_t kMagic = 0x564B5A42u;
+constexpr int kPostRing = 4;
+constexpr unsigned long long kDeviceWaitNs = 20000000000ull;
+
+struct IdPayload {
+    uint32_t magic, reserved;
+    uint64_t token[2];
+};
+static_assert(sizeof(IdPayload) <= NCCL_UNIQUE_ID_BYTES, "id payload");
+
+struct BufferPost {
+    cudaIpcMemHandle_t handle;
+    uint64_t base, offset;
+};
+struct OpPost {
+    BufferPost send, recv;
+};
+struct RankSlot {
+    std::atomic<uint32_t> state;  // 0 empty, 1 published, 2 left
+    int pid;
+    char busId[32];
+    cudaIpcMemHandle_t arenaHandle;
+    uint64_t arenaRaw;
+    std::atomic<uint64_t> postSeq;      // operations whose addresses are posted
+    std::atomic<uint64_t> hostBarrier;  // host-side barriers passed (ranks sharing a GPU)
+    OpPost posts[kPostRing];
+};
+struct Shared {
+    std::atomic<uint32_t> abort;
+    RankSlot ranks[kMaxRanks];
+};
+
+// Device memory of one rank that its peers map: flag words written by the peers, and a status word.
+struct Arena {
+    unsigned long long flags[kMaxRanks];
+    unsigned status;
+};
+
+enum OpKind { kAllGather, kBroadcast, kAllReduce, kReduceScatter, kReduce, kGather, kAllToAll };
+
+}  // namespace
+
+struct ncclComm {
+    int rank = 0, nranks = 1, device = 0;
+    Shared* shared = nullptr;
+    std::string shmName;
+    Arena* arena = nullptr;
+    Arena* peerArena[kMaxRanks] = {};
+    bool samePid[kMaxRanks] = {};
+    bool hostSync = false;  // some ranks share a GPU
+    uint64_t opSeq = 0, deviceBarrierSeq = 0, hostBarrierSeq = 0;
+    struct Mapping {
+        cudaIpcMemHandle_t handle;
+        void* local;
+    };
+    std::map<std::pair<int, uint64_t>, Mapping> mappings;  // (peer, remote base) -> local mapping
+    std::string lastError;
+    std::atomic<bool> aborted{false};
+};
+
+namespace {
+
+thread_local int t_groupDepth = 0;
+
+struct Op {
+    ncclComm* comm;
+    int kind;
+    const void* send;
+    void* recv;
+    size_t count;
+    ncclDataType_t type;
+    ncclRedOp_t op;
+    int root;
+    cudaStream_t stream;
+    uint64_t seq = 0;
+    const char* peerSend[kMaxRanks] = {};
+    char* peerRecv[kMaxRanks] = {};
+};
+thread_local std::vector<Op> t_queue;
+
+double timeoutSeconds() {
+    static const double s = [] {
+        const char* v = std::getenv("VKZB_NCCL_TIMEOUT_S");
+        const double d = v ? std::atof(v) : 0;
+        return d > 0 ? d : 120.0;
+    }();
+    return s;
+}
+
+size_t typeSize(ncclDataType_t t) {
+    switch (t) {
+    case ncclInt8: case ncclUint8: case ncclFloat8e4m3: case ncclFloat8e5m2: return 1;
+    case ncclFloat16: case ncclBfloat16: return 2;
+    case ncclInt32: case ncclUint32: case ncclFloat32: return 4;
+    case ncclInt64: case ncclUint64: case ncclFloat64: return 8;
+    default: return 0;
+    }
+}
+
+ncclResult_t fail(ncclComm* c, ncclResult_t r, const std::string& what) {
+    if (c) c->lastError = what;
+    if (std::getenv("VKZB_LOG")) std::fprintf(stderr, "vkzb nccl: %s\n", what.c_str());
+    return r;
+}
+
+// Polls `ready` with a back-off until it holds, the communicator is aborted, or the time is up.
+template <class F>
+ncclResult_t hostWait(ncclComm* c, F ready, const char* what) {
+    const auto start = std::chrono::steady_clock::now();
+    for (unsigned spins = 0;; ++spins) {
+        if (ready()) return ncclSuccess;
+        if (c->aborted.load() || c->shared->abort.load()) return fail(c, ncclRemoteError, std::string("aborted while waiting for ") + what);
+        if (std::chrono::duration<double>(std::chrono::steady_clock::now() - start).count() > timeoutSeconds())
+            return fail(c, ncclRemoteError, std::string("timed out waiting for ") + what);
+        if (spins < 2000) std::this_thread::yield();
+        else std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+}
+
+// ---- device side ----------------------------------------------------------------------------------------------------
+
+struct FlagTable {
+    unsigned long long* peer[kMaxRanks];  // peer p's flag word for this rank
+};
+
+__global__ void barrierKernel(FlagTable peers, unsigned long long* mine, unsigned* status, int me, int n, unsigned long long seq) {
+    const int p = threadIdx.x;
+    if (p >= n || p == me) return;
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(peers.peer[p]), "l"(seq) : "memory");
+    unsigned long long start;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+    for (;;) {
+        unsigned long long v;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine + p) : "memory");
+        if (v >= seq) return;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (now - start > kDeviceWaitNs) {
+            atomicExch(status, 1u + unsigned(p));  // peer p never arrived
+            return;
+        }
+        __nanosleep(200);
+    }
+}
+
+struct SourceTable {
+    const void* src[kMaxRanks];
+};
+
+template <typename T> struct AccOf { using type = double; };
+template <> struct AccOf<signed char> { using type = long long; };
+template <> struct AccOf<unsigned char> { using type = unsigned long long; };
+template <> struct AccOf<int> { using type = long long; };
+template <> struct AccOf<unsigned> { using type = unsigned long long; };
+template <> struct AccOf<long long> { using type = long long; };
+template <> struct AccOf<unsigned long long> { using type = unsigned long long; };
+
+template <typename A, typename T> __device__ __forceinline__ A widen(T v) { return A(v); }
+template <> __device__ __forceinline__ double widen<double, __half>(__half v) { return double(__half2float(v)); }
+template <> __device__ __forceinline__ double widen<double, __nv_bfloat16>(__nv_bfloat16 v) { return double(__bfloat162float(v)); }
+template <typename T, typename A> __device__ __forceinline__ T narrow(A v) { return T(v); }
+template <> __device__ __forceinline__ __half narrow<__half, double>(double v) { return __float2half_rn(float(v)); }
+template <> __device__ __forceinline__ __nv_bfloat16 narrow<__nv_bfloat16, double>(double v) { return __float2bfloat16_rn(float(v)); }
+
+// out[i] = reduction over ranks, in rank order, of src[r][i]; every rank that runs it gets the same bits.
+template <typename T>
+__global__ void reduceKernel(T* out, SourceTable table, size_t n, int nranks, int op) {
+    using A = typename AccOf<T>::type;
+    for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+        A acc = widen<A, T>(static_cast<const T*>(table.src[0])[i]);
+        for (int r = 1; r < nranks; ++r) {
+            const A v = widen<A, T>(static_cast<const T*>(table.src[r])[i]);
+            if (op == ncclProd) acc = acc * v;
+            else if (op == ncclMax) acc = v > acc ? v : acc;
+            else if (op == ncclMin) acc = v < acc ? v : acc;
+            else acc = acc + v;
+        }
+        if (op == ncclAvg) acc = acc / A(nranks);
+        out[i] = narrow<T, A>(acc);
+    }
+}
+
+cudaError_t launchReduce(void* out, const SourceTable& t, size_t n, int nranks, ncclDataType_t type, int op, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    const int threads = 256;
+    const unsigned blocks = unsigned(std::min<size_t>((n + threads - 1) / threads, 1024));
+    switch (type) {
+    case ncclInt8: reduceKernel<<<blocks, threads, 0, s>>>(static_cast<signed char*>(out), t, n, nranks, op); break;
+    case ncclUint8: reduceKernel<<<blocks, threads, 0, s>>>(static_cast<unsigned char*>(out), t, n, nranks, op); break;
+    case ncclInt32: reduceKernel<<<blocks, threads, 0, s>>>(static_cast<int*>(out), t, n, nranks, op); break;
+    case ncclUint32: reduceKernel<<<blocks, threads, 0, s>>>(static_cast<unsigned*>(out), t, n, nranks, op); break;
+    case ncclInt64: reduceKernel<<<blocks, threads, 0, s>>>(static_cast<long long*>(out), t, n, nranks, op); break;
+    case ncclUint64: reduceKernel<<<blocks, threads, 0, s>>>(static_cast<unsigned long long*>(out), t, n, nranks, op); break;
+    case ncclFloat16: reduceKernel<<<blocks, threads, 0, s>>>(static_cast<__half*>(out), t, n, nranks, op); break;
+    case ncclBfloat16: reduceKernel<<<blocks, threads, 0, s>>>(static_cast<__nv_bfloat16*>(out), t, n, nranks, op); break;
+    case ncclFloat32: reduceKernel<<<blocks, threads, 0, s>>>(static_cast<float*>(out), t, n, nranks, op); break;
+    case ncclFloat64: reduceKernel<<<blocks, threads, 0, s>>>(static_cast<double*>(out), t, n, nranks, op); break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+// ---- addresses -------------------------------------------------------------------------------------------------------
+
+using AddressRangeFn = int (*)(unsigned long long*, size_t*, unsigned long long);
+
+AddressRangeFn addressRange() {
+    static const AddressRangeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<AddressRangeFn>(p);
+    }();
+    return fn;
+}
+
+// The IPC handle of the allocation that holds `ptr`, and ptr's offset in it.
+bool describeBuffer(const void* ptr, BufferPost& out) {
+    std::memset(&out, 0, sizeof out);
+    if (!ptr) return true;
+    unsigned long long base = 0;
+    size_t size = 0;
+    if (!addressRange() || addressRange()(&base, &size, reinterpret_cast<unsigned long long>(ptr)) != 0) return false;
+    out.base = base;
+    out.offset = reinterpret_cast<unsigned long long>(ptr) - base;
+    return cudaIpcGetMemHandle(&out.handle, reinterpret_cast<void*>(base)) == cudaSuccess;
+}
+
+// Local address of a peer's posted buffer: the raw pointer inside one process, an IPC mapping across processes.
+void* mapPeerBuffer(ncclComm* c, int peer, const BufferPost& post) {
+    if (!post.base) return nullptr;
+    if (c->samePid[peer]) return reinterpret_cast<void*>(post.base + post.offset);
+    const auto key = std::make_pair(peer, post.base);
+    auto it = c->mappings.find(key);
+    if (it != c->mappings.end() && std::memcmp(&it->second.handle, &post.handle, sizeof post.handle) != 0) {
+        cudaIpcCloseMemHandle(it->second.local);  // the address was freed and allocated again: a different allocation
+        c->mappings.erase(it);
+        it = c->mappings.end();
+    }
+    if (it == c->mappings.end()) {
+        void* local = nullptr;
+        if (cudaIpcOpenMemHandle(&local, post.handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        it = c->mappings.emplace(key, ncclComm::Mapping{post.handle, local}).first;
+    }
+    return static_cast<char*>(it->second.local) + post.offset;
+}
+
+// ---- barriers ---------------------------------------------------------------------------------------------------------
+
+ncclResult_t barrier(std::vector<Op*>& ops) {
+    // device side where every rank has its own GPU: asynchronous on the stream
+    for (Op* o : ops) {
+        ncclComm* c = o->comm;
+        if (c->hostSync || c->nranks == 1) continue;
+        FlagTable t{};
+        for (int p = 0; p < c->nranks; ++p) t.peer[p] = p == c->rank ? nullptr : &c->peerArena[p]->flags[c->rank];
+        barrierKernel<<<1, 32, 0, o->stream>>>(t, c->arena->flags, &c->arena->status, c->rank, c->nranks, ++c->deviceBarrierSeq);
+        if (cudaGetLastError() != cudaSuccess) return fail(c, ncclUnhandledCudaError, "barrier kernel launch failed");
+    }
+    // host side where ranks share a GPU: drain the streams, publish, then wait for the peers
+    for (Op* o : ops) {
+        ncclComm* c = o->comm;
+        if (!c->hostSync || c->nranks == 1) continue;
+        if (cudaStreamSynchronize(o->stream) != cudaSuccess) return fail(c, ncclUnhandledCudaError, "stream synchronize failed");
+        c->shared->ranks[c->rank].hostBarrier.store(++c->hostBarrierSeq, std::memory_order_release);
+    }
+    for (Op* o : ops) {
+        ncclComm* c = o->comm;
+        if (!c->hostSync || c->nranks == 1) continue;
+        const uint64_t want = c->hostBarrierSeq;
+        const ncclResult_t r = hostWait(c, [&] {
+            for (int p = 0; p < c->nranks; ++p)
+                if (c->shared->ranks[p].hostBarrier.load(std::memory_order_acquire) < want) return false;
+            return true;
+        }, "the other ranks at a barrier");
+        if (r != ncclSuccess) return r;
+    }
+    return ncclSuccess;
+}
+
+// ---- the collectives, as one or two rounds of pulls --------------------------------------------------------------------
+
+cudaError_t copyAsync(void* dst, const void* src, size_t bytes, cudaStream_t s) {
+    if (bytes == 0 || dst == src) return cudaSuccess;
+    return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, s);
+}
+
+void sliceOf(size_t count, int nranks, int r, size_t& first, size_t& len) {
+    const size_t per = (count + nranks - 1) / nranks;
+    first = std::min(count, per * size_t(r));
+    len = std::min(count, first + per) - first;
+}
+
+bool needsSecondRound(const Op& o) { return o.kind == kAllReduce; }
+
+ncclResult_t runRound(Op& o, int round) {
+    ncclComm* c = o.comm;
+    const int n = c->nranks, me = c->rank;
+    const size_t es = typeSize(o.type), bytes = o.count * es;
+    cudaError_t e = cudaSuccess;
+    const auto local = [&](int p) { return p == me; };
+    switch (o.kind) {
+    case kAllGather:
+        // start with the next rank so that the ranks do not all read from rank 0 at the same moment
+        for (int i = 0; i < n && e == cudaSuccess; ++i) {
+            const int p = (me + 1 + i) % n;
+            e = copyAsync(static_cast<char*>(o.recv) + size_t(p) * bytes, local(p) ? static_cast<const char*>(o.send) : o.peerSend[p], bytes, o.stream);
+        }
+        break;
+    case kBroadcast:
+        e = copyAsync(o.recv, local(o.root) ? static_cast<const char*>(o.send) : o.peerSend[o.root], bytes, o.stream);
+        break;
+    case kGather:
+        if (me == o.root)
+            for (int i = 0; i < n && e == cudaSuccess; ++i) {
+                const int p = (me + 1 + i) % n;
+                e = copyAsync(static_cast<char*>(o.recv) + size_t(p) * bytes, local(p) ? static_cast<const char*>(o.send) : o.peerSend[p], bytes, o.stream);
+            }
+        break;
+    case kAllToAll:
+        for (int i = 0; i < n && e == cudaSuccess; ++i) {
+            const int p = (me + 1 + i) % n;
+            const char* src = (local(p) ? static_cast<const char*>(o.send) : o.peerSend[p]) + size_t(me) * bytes;
+            e = copyAsync(static_cast<char*>(o.recv) + size_t(p) * bytes, src, bytes, o.stream);
+        }
+        break;
+    case kReduce:
+    case kReduceScatter: {
+        if (o.kind == kReduce && me != o.root) break;
+        SourceTable t{};
+        const size_t skip = o.kind == kReduceScatter ? size_t(me) * bytes : 0;  // rank r keeps block r of the reduction
+        for (int p = 0; p < n; ++p) t.src[p] = (local(p) ? static_cast<const char*>(o.send) : o.peerSend[p]) + skip;
+        e = launchReduce(o.recv, t, o.count, n, o.type, o.op, o.stream);
+        break;
+    }
+    case kAllReduce: {
+        // round 0: this rank reduces its slice of every rank's send buffer into its own receive buffer (no rank reads the
+        // slice another one writes, so send == recv is safe); round 1: it pulls the other slices from their owners.
+        if (round == 0) {
+            size_t first, len;
+            sliceOf(o.count, n, me, first, len);
+            SourceTable t{};
+            for (int p = 0; p < n; ++p) t.src[p] = (local(p) ? static_cast<const char*>(o.send) : o.peerSend[p]) + first * es;
+            e = launchReduce(static_cast<char*>(o.recv) + first * es, t, len, n, o.type, o.op, o.stream);
+        } else {
+            for (int i = 0; i + 1 < n && e == cudaSuccess; ++i) {
+                const int p = (me + 1 + i) % n;
+                size_t first, len;
+                sliceOf(o.count, n, p, first, len);
+                e = copyAsync(static_cast<char*>(o.recv) + first * es, o.peerRecv[p] + first * es, len * es, o.stream);
+            }
+        }
+        break;
+    }
+    }
+    return e == cudaSuccess ? ncclSuccess : fail(c, ncclUnhandledCudaError, std::string("data movement failed: ") + cudaGetErrorString(e));
+}
+
+ncclResult_t execute(std::vector<Op>& ops) {
+    // 1. every operation posts its buffers' addresses
+    for (Op& o : ops) {
+        ncclComm* c = o.comm;
+        if (c->aborted.load()) return fail(c, ncclInvalidUsage, "communicator was aborted");
+        cudaSetDevice(c->device);
+        o.seq = ++c->opSeq;
+        if (c->nranks == 1) continue;
+        RankSlot& slot = c->shared->ranks[c->rank];
+        OpPost& post = slot.posts[o.seq % kPostRing];
+        if (!describeBuffer(o.send, post.send) || !describeBuffer(o.recv, post.recv))
+            return fail(c, ncclInvalidArgument, "a buffer is not device memory that can be shared with the other ranks (cudaMalloc memory is)");
+        slot.postSeq.store(o.seq, std::memory_order_release);
+    }
+    // 2. ... and maps what the peers posted
+    for (Op& o : ops) {
+        ncclComm* c = o.comm;
+        if (c->nranks == 1) continue;
+        cudaSetDevice(c->device);
+        const ncclResult_t r = hostWait(c, [&] {
+            for (int p = 0; p < c->nranks; ++p)
+                if (c->shared->ranks[p].postSeq.load(std::memory_order_acquire) < o.seq) return false;
+            return true;
+        }, "the other ranks to enter the collective");
+        if (r != ncclSuccess) return r;
+        for (int p = 0; p < c->nranks; ++p) {
+            if (p == c->rank) continue;
+            const OpPost& post = c->shared->ranks[p].posts[o.seq % kPostRing];
+            o.peerSend[p] = static_cast<const char*>(mapPeerBuffer(c, p, post.send));
+            o.peerRecv[p] = static_cast<char*>(mapPeerBuffer(c, p, post.recv));
+            const bool needSend = !(o.kind == kBroadcast && p != o.root) && !((o.kind == kGather || o.kind == kReduce) && c->rank != o.root);
+            if ((needSend && post.send.base && !o.peerSend[p]) || (o.kind == kAllReduce && !o.peerRecv[p]))
+                return fail(c, ncclUnhandledCudaError, "could not map a peer's buffer (cudaIpcOpenMemHandle)");
+        }
+    }
+    // 3. barrier, pulls, (barrier, pulls,) barrier
+    std::vector<Op*> all, second;
+    for (Op& o : ops) {
+        all.push_back(&o);
+        if (needsSecondRound(o)) second.push_back(&o);
+    }
+    ncclResult_t r = barrier(all);
+    for (Op& o : ops) {
+        if (r != ncclSuccess) return r;
+        cudaSetDevice(o.comm->device);
+        r = runRound(o, 0);
+    }
+    if (r == ncclSuccess && !second.empty()) {
+        r = barrier(second);
+        for (Op* o : second) {
+            if (r != ncclSuccess) return r;
+            cudaSetDevice(o->comm->device);
+            r = runRound(*o, 1);
+        }
+    }
+    if (r == ncclSuccess) r = barrier(all);
+    return r;
+}
+
+ncclResult_t submit(Op op) {
+    if (!op.comm) return ncclInvalidArgument;
+    if (typeSize(op.type) == 0 || (!op.recv && op.count && !(op.kind == kReduce || op.kind == kGather))) return fail(op.comm, ncclInvalidArgument, "bad datatype or null buffer");
+    if ((op.kind == kBroadcast || op.kind == kReduce || op.kind == kGather) && (op.root < 0 || op.root >= op.comm->nranks))
+        return fail(op.comm, ncclInvalidArgument, "root out of range");
+    if (unsigned(op.op) >= unsigned(ncclNumOps) && (op.kind == kAllReduce || op.kind == kReduce || op.kind == kReduceScatter))
+        return fail(op.comm, ncclInvalidUsage, "custom reduction operators are not served");
+    if (t_groupDepth > 0) {
+        t_queue.push_back(op);
+        return ncclSuccess;
+    }
+    std::vector<Op> one{op};
+    int prev = 0;
+    cudaGetDevice(&prev);
+    const ncclResult_t r = execute(one);
+    cudaSetDevice(prev);
+    return r;
+}
+
+std::string shmNameOf(const IdPayload& id) {
+    char name[80];
+    std::snprintf(name, sizeof name, "/vkzb-nccl-%016llx%016llx", (unsigned long long)id.token[0], (unsigned long long)id.token[1]);
+    return name;
+}
+
+ncclResult_t initRank(ncclComm_t* out, int nranks, const ncclUniqueId& uid, int rank) {
+    if (!out || nranks < 1 || rank < 0 || rank >= nranks) return ncclInvalidArgument;
+    if (nranks > kMaxRanks) return ncclInvalidArgument;
+    IdPayload id;
+    std::memcpy(&id, uid.internal, sizeof id);
+    if (id.magic != kMagic) return ncclInvalidArgument;
+    if (cudaFree(nullptr) != cudaSuccess) return ncclUnhandledCudaError;
+    auto* c = new ncclComm;
+    c->rank = rank, c->nranks = nranks;
+    cudaGetDevice(&c->device);
+    c->shmName = shmNameOf(id);
+    const int fd = shm_open(c->shmName.c_str(), O_CREAT | O_RDWR, 0600);
+    if (fd < 0 || ftruncate(fd, sizeof(Shared)) != 0) {
+        if (fd >= 0) close(fd);
+        delete c;
+        return ncclSystemError;
+    }
+    void* mem = mmap(nullptr, sizeof(Shared), PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);  // a new object reads as zeros
+    close(fd);
+    if (mem == MAP_FAILED) {
+        delete c;
+        return ncclSystemError;
+    }
+    c->shared = static_cast<Shared*>(mem);
+    if (cudaMalloc(reinterpret_cast<void**>(&c->arena), sizeof(Arena)) != cudaSuccess || cudaMemset(c->arena, 0, sizeof(Arena)) != cudaSuccess) {
+        munmap(mem, sizeof(Shared));
+        delete c;
+        return ncclUnhandledCudaError;
+    }
+    RankSlot& slot = c->shared->ranks[rank];
+    slot.pid = int(getpid());
+    cudaDeviceGetPCIBusId(slot.busId, sizeof slot.busId, c->device);
+    slot.arenaRaw = reinterpret_cast<uint64_t>(c->arena);
+    if (nranks > 1 && cudaIpcGetMemHandle(&slot.arenaHandle, c->arena) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(c, ncclUnhandledCudaError, "cudaIpcGetMemHandle failed for the flag arena");
+    }
+    slot.state.store(1, std::memory_order_release);
+    const ncclResult_t r = hostWait(c, [&] {
+        for (int p = 0; p < nranks; ++p)
+            if (c->shared->ranks[p].state.load(std::memory_order_acquire) == 0) return false;
+        return true;
+    }, "every rank to join the communicator");
+    if (r != ncclSuccess) return r;
+    for (int p = 0; p < nranks; ++p) {
+        const RankSlot& s = c->shared->ranks[p];
+        c->samePid[p] = s.pid == slot.pid;
+        for (int q = 0; q < p; ++q)
+            if (!std::strcmp(c->shared->ranks[q].busId, s.busId)) c->hostSync = true;
+        if (p == rank) continue;
+        if (c->samePid[p]) {
+            c->peerArena[p] = reinterpret_cast<Arena*>(s.arenaRaw);
+            int peerDev = -1;
+            cudaDeviceGetByPCIBusId(&peerDev, s.busId);
+            if (peerDev >= 0 && peerDev != c->device && cudaDeviceEnablePeerAccess(peerDev, 0) != cudaSuccess) cudaGetLastError();
+        } else if (cudaIpcOpenMemHandle(reinterpret_cast<void**>(&c->peerArena[p]), s.arenaHandle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(c, ncclUnhandledCudaError, "cudaIpcOpenMemHandle failed for a peer's flag arena (no peer access between the GPUs?)");
+        }
+    }
+    *out = c;
+    return ncclSuccess;
+}
+
+void destroy(ncclComm* c) {
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(c->device);
+    cudaDeviceSynchronize();
+    for (auto& m : c->mappings) cudaIpcCloseMemHandle(m.second.local);
+    for (int p = 0; p < c->nranks; ++p)
+        if (p != c->rank && c->peerArena[p] && !c->samePid[p]) cudaIpcCloseMemHandle(c->peerArena[p]);
+    if (c->shared) {
+        c->shared->ranks[c->rank].state.store(2, std::memory_order_release);
+        bool last = true;
+        for (int p = 0; p < c->nranks; ++p)
+            if (c->shared->ranks[p].state.load() != 2) last = false;
+        if (last) shm_unlink(c->shmName.c_str());
+        munmap(c->shared, sizeof(Shared));
+    }
+    if (c->arena) cudaFree(c->arena);
+    cudaSetDevice(prev);
+    delete c;
+}
+
+}  // namespace
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+ncclResult_t ncclGetVersion(int* version) {
+    if (!version) return ncclInvalidArgument;
+    *version = NCCL_VERSION_CODE;
+    return ncclSuccess;
+}
+
+ncclResult_t ncclGetUniqueId(ncclUniqueId* uniqueId) {
+    if (!uniqueId) return ncclInvalidArgument;
+    std::memset(uniqueId, 0, sizeof *uniqueId);
+    std::random_device rd;
+    IdPayload id{kMagic, 0, {(uint64_t(rd()) << 32) | rd(), (uint64_t(rd()) << 32) ^ uint64_t(getpid()) ^ uint64_t(std::chrono::steady_clock::now().time_since_epoch().count())}};
+    std::memcpy(uniqueId->internal, &id, sizeof id);
+    return ncclSuccess;
+}
+
+ncclResult_t ncclCommInitRank(ncclComm_t* comm, int nranks, ncclUniqueId commId, int rank) { return initRank(comm, nranks, commId, rank); }
+ncclResult_t ncclCommInitRankConfig(ncclComm_t* comm, int nranks, ncclUniqueId commId, int rank, ncclConfig_t*) {
+    return initRank(comm, nranks, commId, rank);
+}
+
+// One communicator per listed device, all in this process (nccl.cpp:528-543).
+ncclResult_t ncclCommInitAll(ncclComm_t* comms, int ndev, const int* devlist) {
+    if (!comms || ndev < 1 || ndev > kMaxRanks) return ncclInvalidArgument;
+    ncclUniqueId id;
+    ncclGetUniqueId(&id);
+    int prev = 0;
+    cudaGetDevice(&prev);
+    std::vector<ncclResult_t> results(ndev, ncclSuccess);
+    std::vector<std::thread> threads;
+    for (int r = 0; r < ndev; ++r)
+        threads.emplace_back([&, r] {
+            if (cudaSetDevice(devlist ? devlist[r] : r) != cudaSuccess) {
+                results[r] = ncclInvalidArgument;
+                return;
+            }
+            results[r] = initRank(&comms[r], ndev, id, r);
+        });
+    for (auto& t : threads) t.join();
+    cudaSetDevice(prev);
+    for (ncclResult_t r : results)
+        if (r != ncclSuccess) return r;
+    return ncclSuccess;
+}
+
+ncclResult_t ncclCommFinalize(ncclComm_t comm) { return comm ? ncclSuccess : ncclInvalidArgument; }
+
+ncclResult_t ncclCommDestroy(ncclComm_t comm) {
+    if (!comm) return ncclSuccess;
+    destroy(comm);
+    return ncclSuccess;
+}
+
+ncclResult_t ncclCommAbort(ncclComm_t comm) {
+    if (!comm) return ncclInvalidArgument;
+    comm->aborted.store(true);
+    if (comm->shared) comm->shared->abort.store(1);
+    return ncclSuccess;
+}
+
+const char* ncclGetErrorString(ncclResult_t result) {
+    switch (result) {
+    case ncclSuccess: return "no error";
+    case ncclUnhandledCudaError: return "unhandled cuda error";
+    case ncclSystemError: return "unhandled system error";
+    case ncclInternalError: return "internal error";
+    case ncclInvalidArgument: return "invalid argument";
+    case ncclInvalidUsage: return "invalid usage";
+    case ncclRemoteError: return "remote process exited or there was a network error";
+    case ncclInProgress: return "NCCL operation in progress";
+    default: return "unknown result code";
+    }
+}
+
+const char* ncclGetLastError(ncclComm_t comm) { return comm ? comm->lastError.c_str() : ""; }
+
+// Reads the device status word (a blocking copy): non-zero means a device-side barrier gave up on a peer.
+ncclResult_t ncclCommGetAsyncError(ncclComm_t comm, ncclResult_t* asyncError) {
+    if (!comm || !asyncError) return ncclInvalidArgument;
+    unsigned status = 0;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(comm->device);
+    const cudaError_t e = cudaMemcpy(&status, &comm->arena->status, sizeof status, cudaMemcpyDeviceToHost);
+    cudaSetDevice(prev);
+    *asyncError = e != cudaSuccess ? ncclUnhandledCudaError : status || comm->aborted.load() ? ncclRemoteError : ncclSuccess;
+    return ncclSuccess;
+}
+
+ncclResult_t ncclCommCount(const ncclComm_t comm, int* count) {
+    if (!comm || !count) return ncclInvalidArgument;
+    *count = comm->nranks;
+    return ncclSuccess;
+}
+ncclResult_t ncclCommCuDevice(const ncclComm_t comm, int* device) {
+    if (!comm || !device) return ncclInvalidArgument;
+    *device = comm->device;
+    return ncclSuccess;
+}
+ncclResult_t ncclCommUserRank(const ncclComm_t comm, int* rank) {
+    if (!comm || !rank) return ncclInvalidArgument;
+    *rank = comm->rank;
+    return ncclSuccess;
+}
+ncclResult_t ncclCommRegister(const ncclComm_t comm, void* buff, size_t, void** handle) {
+    if (!comm || !handle) return ncclInvalidArgument;
+    *handle = buff;  // every cudaMalloc buffer is reachable already; nothing to prepare
+    return ncclSuccess;
+}
+ncclResult_t ncclCommDeregister(const ncclComm_t comm, void*) { return comm ? ncclSuccess : ncclInvalidArgument; }
+ncclResult_t ncclMemAlloc(void** ptr, size_t size) {
+    if (!ptr) return ncclInvalidArgument;
+    return cudaMalloc(ptr, size) == cudaSuccess ? ncclSuccess : ncclUnhandledCudaError;
+}
+ncclResult_t ncclMemFree(void* ptr) { return cudaFree(ptr) == cudaSuccess ? ncclSuccess : ncclUnhandledCudaError; }
+
+ncclResult_t ncclAllGather(const void* sendbuff, void* recvbuff, size_t sendcount, ncclDataType_t datatype, ncclComm_t comm, cudaStream_t stream) {
+    return submit({comm, kAllGather, sendbuff, recvbuff, sendcount, datatype, ncclSum, 0, stream});
+}
+ncclResult_t ncclBroadcast(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, int root, ncclComm_t comm, cudaStream_t stream) {
+    return submit({comm, kBroadcast, sendbuff, recvbuff, count, datatype, ncclSum, root, stream});
+}
+ncclResult_t ncclBcast(void* buff, size_t count, ncclDataType_t datatype, int root, ncclComm_t comm, cudaStream_t stream) {
+    return submit({comm, kBroadcast, buff, buff, count, datatype, ncclSum, root, stream});
+}
+ncclResult_t ncclAllReduce(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op, ncclComm_t comm, cudaStream_t stream) {
+    return submit({comm, kAllReduce, sendbuff, recvbuff, count, datatype, op, 0, stream});
+}
+ncclResult_t ncclReduceScatter(const void* sendbuff, void* recvbuff, size_t recvcount, ncclDataType_t datatype, ncclRedOp_t op, ncclComm_t comm, cudaStream_t stream) {
+    return submit({comm, kReduceScatter, sendbuff, recvbuff, recvcount, datatype, op, 0, stream});
+}
+ncclResult_t ncclReduce(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op, int root, ncclComm_t comm, cudaStream_t stream) {
+    return submit({comm, kReduce, sendbuff, recvbuff, count, datatype, op, root, stream});
+}
+ncclResult_t ncclGather(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, int root, ncclComm_t comm, cudaStream_t stream) {
+    return submit({comm, kGather, sendbuff, recvbuff, count, datatype, ncclSum, root, stream});
+}
+ncclResult_t ncclAlltoAll(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclComm_t comm, cudaStream_t stream) {
+    return submit({comm, kAllToAll, sendbuff, recvbuff, count, datatype, ncclSum, 0, stream});
+}
+
+ncclResult_t ncclGroupStart(void) {
+    ++t_groupDepth;
+    return ncclSuccess;
+}
+
+ncclResult_t ncclGroupEnd(void) {
+    if (t_groupDepth <= 0) return ncclInvalidUsage;
+    if (--t_groupDepth > 0) return ncclSuccess;
+    std::vector<Op> ops;
+    ops.swap(t_queue);
+    if (ops.empty()) return ncclSuccess;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    const ncclResult_t r = execute(ops);
+    cudaSetDevice(prev);
+    return r;
+}
+
+// Not served yet (include/vkzb_nccl.h lists them): parameterless like the reference's stubs, so any signature binds.
+#define VKZB_NCCL_STUB(name) \
+    ncclResult_t name() { return ncclInvalidUsage; }
+VKZB_NCCL_STUB(ncclSend)
+VKZB_NCCL_STUB(ncclRecv)
+VKZB_NCCL_STUB(ncclCommSplit)
+VKZB_NCCL_STUB(ncclCommInitRankScalable)
+VKZB_NCCL_STUB(ncclRedOpCreatePreMulSum)
+VKZB_NCCL_STUB(ncclRedOpDestroy)
+VKZB_NCCL_STUB(ncclGroupSimulateEnd)
+VKZB_NCCL_STUB(ncclCommGetUniqueId)
+VKZB_NCCL_STUB(ncclCommGrow)
+VKZB_NCCL_STUB(ncclCommMemStats)
+VKZB_NCCL_STUB(ncclCommResume)
+VKZB_NCCL_STUB(ncclCommRevoke)
+VKZB_NCCL_STUB(ncclCommShrink)
+VKZB_NCCL_STUB(ncclCommSuspend)
+VKZB_NCCL_STUB(ncclCommWindowDeregister)
+VKZB_NCCL_STUB(ncclCommWindowRegister)
+VKZB_NCCL_STUB(ncclDevCommCreate)
+VKZB_NCCL_STUB(ncclDevCommDestroy)
+VKZB_NCCL_STUB(ncclGetLsaMultimemDevicePointer)
+VKZB_NCCL_STUB(ncclGetPeerDevicePointer)
+VKZB_NCCL_STUB(ncclPutSignal)
+VKZB_NCCL_STUB(ncclSignal)
+VKZB_NCCL_STUB(ncclWaitSignal)
+VKZB_NCCL_STUB(ncclWinGetUserPtr)
+
+}  // extern "C"
+#pragma GCC visibility pop

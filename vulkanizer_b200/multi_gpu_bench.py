@@ -1,0 +1,187 @@
+"""Multi-GPU arm of bench.py: the N-sharded large GEMM with its column blocks gathered over NVLink.
+
+Workload cfg5b_bf16_32768_nsharded: D = A^T B with A, B 32768 x 32768 bf16 (normal(0, 1), seed 5), D 32768 x 32768 fp32,
+alpha = 1, beta = 0, through cublasLtMatmul. The columns of B and D are dealt to the ranks block-cyclically: column chunk
+c (W columns) belongs to rank c mod G, so that the G chunks of one "round" lie side by side in D and ncclAllGather, whose
+result layout is rank-major, can gather them in place (send = the rank's own chunk inside the receive region). Rank r
+multiplies its chunk of round j on the compute stream and gathers round j on a second stream while round j + 1 is being
+multiplied; A (2 GiB) is replicated, every rank ends with the whole of D. This is the partitioning of k0zi/Vulkanizer's
+`partOf(g, rows=false, first, count)` (src/cublas/cublas.cpp:542-546) applied across GPUs, with the exchange step its
+libnccl surface provides (src/nccl/nccl.cpp:691-695). Strong scaling: the total work is fixed.
+
+torch.distributed (gloo) is only the plumbing: it carries the 128-byte communicator id, the barrier around the timed region and
+the maximum over the ranks' device times. All GPU work goes through this repository's libcublasLt.so.12 and libnccl.so.2.
+"""
+from __future__ import annotations
+
+import json
+import os
+import statistics
+import time
+
+
+def column_chunks(n: int, ranks: int, width: int):
+    """Rounds of `ranks` chunks of `width` columns: [(round, first column of the round, first column of chunk of rank r for r in ranks)]."""
+    assert n % (ranks * width) == 0, "the column count must be a multiple of ranks x chunk width"
+    return [(j, j * ranks * width, [(j * ranks + r) * width for r in range(ranks)]) for j in range(n // (ranks * width))]
+
+
+def pick_width(n: int, ranks: int) -> int:
+    """1024 columns fill the 148 SMs almost evenly (1024 tiles of 128 x 256 = 6.9 waves); smaller when that leaves under four rounds."""
+    width = 1024
+    while width > 256 and n // (ranks * width) < 4:
+        width //= 2
+    return width
+
+
+def run(args):
+    import torch
+    import torch.distributed as dist
+
+    from bench import ClockSampler, measured_peaks, physical_gpu_index, FALLBACK_PEAKS
+    from vulkanizer_b200 import capi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.cuda.set_device(local)
+    torch.zeros(1, device="cuda")
+
+    size = int(os.environ.get("VKZB_BENCH_SIZE", "32768"))
+    m = n = k = size
+    width = pick_width(n, world)
+    rounds = column_chunks(n, world, width)
+
+    # the communicator id travels through the process group
+    box = [capi.NcclComm.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    comm = capi.NcclComm(world, rank, box[0])
+
+    # operands: A identical on every rank; of B only the rank's own chunks, chunk c generated from seed (5, c)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(5)
+    A = torch.empty(m * k, dtype=torch.bfloat16, device="cuda")  # stored k x m (op T), lda = k
+    step_elems = 1 << 26
+    for first in range(0, m * k, step_elems):
+        cnt = min(step_elems, m * k - first)
+        A[first:first + cnt] = torch.randn(cnt, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    Bmine = torch.empty(len(rounds) * width * k, dtype=torch.bfloat16, device="cuda")  # the rank's chunks, one after another
+    for j, _, firsts in rounds:
+        gen.manual_seed(5 * 100003 + firsts[rank] // width)
+        Bmine[j * width * k:(j + 1) * width * k] = torch.randn(width * k, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    D = torch.zeros(m * n, dtype=torch.float32, device="cuda")  # column-major m x n, ldd = m: 4 GiB at full size
+
+    lt = capi.CublasLt()
+    compute, gather = torch.cuda.Stream(), torch.cuda.Stream()
+    bf16, f32 = capi.CUDA_R_16BF, capi.CUDA_R_32F
+    events = [torch.cuda.Event() for _ in rounds]
+
+    def step():
+        for j, round_first, firsts in rounds:
+            mine = D.data_ptr() + 4 * firsts[rank] * m
+            lt.matmul(capi.OP_T, capi.OP_N, m, width, k, 1.0, A.data_ptr(), bf16, k, Bmine.data_ptr() + 2 * j * width * k, bf16, k, 0.0,
+                      mine, f32, m, mine, f32, m, stream=compute.cuda_stream)
+            if world > 1:
+                events[j].record(compute)
+                gather.wait_event(events[j])
+                comm.all_gather(mine, D.data_ptr() + 4 * round_first * m, width * m, "float32", gather.cuda_stream)
+        if world > 1:
+            compute.wait_stream(gather)  # the step ends when every rank's columns have arrived
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    assert lt.last_path() == capi.PATH_UMMA
+    launches0 = lt.launch_count()
+    sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
+    dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    start.record(compute)
+    for _ in range(args.steps):
+        step()
+    stop.record(compute)
+    torch.cuda.synchronize()
+    dist.barrier()
+    t1 = time.time()
+    ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    total_ms = float(ms.item())
+    clocks = sampler.stop(t0, t1) if sampler else None
+    launches = lt.launch_count() - launches0
+    assert comm.async_error() == 0, "a device-side barrier of the gather gave up"
+
+    # a spot check that the gather delivered every rank's columns: column sums of a few remote chunks against a local product
+    check_ok = True
+    if world > 1:
+        other = (rank + 1) % world
+        j, _, firsts = rounds[-1]
+        gen.manual_seed(5 * 100003 + firsts[other] // width)
+        Bother = torch.randn(width * k, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16).view(width, k)
+        rows = torch.arange(0, m, 997, device="cuda")
+        want = (A.view(m, k)[rows].float() @ Bother[:8].float().T)  # (rows, 8 columns)
+        got = D.view(n, m)[firsts[other]:firsts[other] + 8][:, rows].T
+        check_ok = bool(torch.allclose(got, want, rtol=2e-2, atol=2e-2 * (k ** 0.5)))
+    ok = torch.tensor([1 if check_ok else 0])
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    assert int(ok.item()) == 1, "gathered columns do not match a local product"
+
+    # end to end: the rank's inputs come from pinned host memory, its own columns of D go back
+    hostA = torch.empty(m * k, dtype=torch.bfloat16).pin_memory()
+    hostB = torch.empty(Bmine.numel(), dtype=torch.bfloat16).pin_memory()
+    hostD = torch.empty(len(rounds) * width * m, dtype=torch.float32).pin_memory()
+    hostA.copy_(A)
+    hostB.copy_(Bmine)
+    e2e_steps = 2
+
+    def step_e2e():
+        with torch.cuda.stream(compute):
+            A.copy_(hostA, non_blocking=True)
+            Bmine.copy_(hostB, non_blocking=True)
+        step()
+        with torch.cuda.stream(compute):
+            for j, _, firsts in rounds:
+                hostD[j * width * m:(j + 1) * width * m].copy_(D[firsts[rank] * m:(firsts[rank] + width) * m], non_blocking=True)
+
+    step_e2e()
+    torch.cuda.synchronize()
+    dist.barrier()
+    start.record(compute)
+    for _ in range(e2e_steps):
+        step_e2e()
+    stop.record(compute)
+    torch.cuda.synchronize()
+    e2e_ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64)
+    dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+
+    flops = 2.0 * m * n * k
+    if rank == 0:
+        peaks, peak_kind = measured_peaks()
+        peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])) * world
+        value = flops * args.steps / (total_ms * 1e-3) / 1e12
+        gathered_bytes = (world - 1) * (n // world) * m * 4
+        line = {
+            "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "cfg5b_bf16_32768_nsharded", "call": "cublasLtMatmul + ncclAllGather", "opA": "T", "opB": "N", "m": m, "n": n,
+                       "k": k, "a_b_type": "bf16", "c_type": "f32", "alpha": 1, "beta": 0, "seed": 5, "parallelism": f"n-sharded x{world}",
+                       "chunk_columns": width, "rounds": len(rounds),
+                       "l2": "operands of one step hold 8 GiB > L2, no flush", "timing": "CUDA events on the compute stream, maximum over ranks"},
+            "roofline": {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak, "traffic": None,
+                         "peak_source": f"{peak_kind}: cuBLAS bf16 sustained x {world} GPUs (the step is a long loop of GEMMs)",
+                         "kernel": "ummaGemmKernel<256>", "nvlink_bytes_in_per_gpu_per_step": gathered_bytes,
+                         "nvlink_floor_ms": gathered_bytes / 770e9 * 1e3},
+            "e2e": {"value": flops * e2e_steps / (float(e2e_ms.item()) * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": (hostA.numel() + hostB.numel()) * 2 * world, "d2h_bytes_per_step": hostD.numel() * 4 * world},
+            "gpu_launches": launches * world, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    comm.destroy()
+    lt.destroy()
+    dist.barrier()
+    dist.destroy_process_group()
