@@ -1,0 +1,65 @@
+"""Host-side logic of the multi-GPU path on CPU: the block-cyclic column partition, and two gloo ranks agreeing on it and
+on the communicator id they would hand to ncclCommInitRank."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+from vulkanizer_b200.multi_gpu_bench import column_chunks, pick_width
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.mark.parametrize("n, ranks", [(32768, 1), (32768, 2), (32768, 4), (32768, 8), (8192, 2)])
+def test_partition_covers_every_column_once_in_gather_order(n, ranks):
+    width = pick_width(n, ranks)
+    rounds = column_chunks(n, ranks, width)
+    seen = []
+    for j, round_first, firsts in rounds:
+        assert round_first == j * ranks * width
+        # ncclAllGather puts rank r's block at offset r * count: the chunks of a round must lie in rank order, side by side
+        assert firsts == [round_first + r * width for r in range(ranks)]
+        seen += [c for f in firsts for c in range(f, f + width, width)]
+    assert sorted(seen) == list(range(0, n, width))
+    assert len(rounds) >= 4 or width == 256
+
+
+def test_uneven_split_is_refused():
+    with pytest.raises(AssertionError):
+        column_chunks(1000, 3, 256)
+
+
+WORKER = r'''
+import os, sys, hashlib
+sys.path.insert(0, sys.argv[1])
+import torch.distributed as dist
+from vulkanizer_b200.multi_gpu_bench import column_chunks, pick_width
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", rank=rank, world_size=world)
+box = [bytes(range(128)) if rank == 0 else None]          # stands in for ncclGetUniqueId on rank 0
+dist.broadcast_object_list(box, src=0)
+assert box[0] == bytes(range(128))
+rounds = column_chunks(8192, world, pick_width(8192, world))
+mine = [firsts[rank] for _, _, firsts in rounds]
+gathered = [None] * world
+dist.all_gather_object(gathered, mine)
+flat = sorted(c for part in gathered for c in part)
+assert flat == list(range(0, 8192, pick_width(8192, world))), flat
+assert all(set(gathered[a]).isdisjoint(gathered[b]) for a in range(world) for b in range(a))
+dist.barrier()
+dist.destroy_process_group()
+print("rank", rank, "ok")
+'''
+
+
+def test_two_gloo_ranks_agree_on_partition_and_id(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29577", WORLD_SIZE="2")
+    procs = [subprocess.Popen([sys.executable, str(script), str(ROOT)], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    for r, p in enumerate(procs):
+        out, _ = p.communicate(timeout=120)
+        assert p.returncode == 0 and f"rank {r} ok" in out, out[-2000:]

@@ -6,7 +6,7 @@
 //
 // The work is one pass over M, so the kernel is bound by HBM bandwidth. When rows are contiguous along
 // the reduction (op(A) = A^T for n = 1) and 16-byte aligned, one warp streams one row with 128-bit loads,
-// four loads in flight per lane, fp32 partial sums per lane and a shuffle tree at the end; no shared memory,
+// eight loads in flight per lane, fp32 partial sums per lane and a shuffle tree at the end; no shared memory,
 // no block-level barrier. Any other layout takes the strided kernel (a thread per row, coalesced when the
 // rows are interleaved in memory).
 #include "epilogue.cuh"
@@ -74,7 +74,7 @@ __device__ __forceinline__ uint4 streamLoad(const void* p) {
 }
 
 constexpr int kWarpsPerBlock = 8;
-constexpr int kUnroll = 4;
+constexpr int kUnroll = 8;  // 16-byte loads in flight per lane: a row of 4096 halves is two trips to memory
 
 // One warp per row; M and v both 16-bit of the same type, rows contiguous and 16-byte aligned, incv = 1.
 template <bool BF16>
@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) gemvRowsVec16(const GemvA
         for (int u = 0; u < kUnroll; ++u) acc[u] = dot8<BF16>(a[u], __ldg(vec + c + 32 * u), acc[u]);
     }
     for (; c < chunks; c += 32) acc[0] = dot8<BF16>(streamLoad(mrow + c), __ldg(vec + c), acc[0]);
-    float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    float sum = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
     // the ragged end of a row whose length is not a multiple of 8
     for (int i = chunks * 8 + lane; i < g.len; i += 32)
         sum = fmaf(loadAs<float>(M, row * g.rowStride + i, g.typeM), loadAs<float>(v, i, g.typeV), sum);

@@ -181,6 +181,61 @@ __device__ __forceinline__ void ummaIssue(int kind, unsigned tmemD, unsigned lon
     }
 }
 
+// ---- two-CTA pairs (cta_group::2): the two CTAs of a cluster share one MMA of 256 rows ------------------------------
+
+__device__ __forceinline__ unsigned clusterCtaRank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The shared::cluster address of the same shared-memory offset in the CTA of rank `rank`.
+__device__ __forceinline__ unsigned mapToCta(unsigned localAddr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(localAddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void clusterSync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Load into this CTA's shared memory, completion counted on a barrier that may live in the pair's other CTA.
+__device__ __forceinline__ void tmaLoad3dPair(unsigned dst, const CUtensorMap* map, unsigned clusterBar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(map)), "r"(clusterBar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+// Arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far have completed.
+__device__ __forceinline__ void tcgen05CommitPair(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((unsigned short)3)
+                 : "memory");
+}
+__device__ __forceinline__ void mbarArriveCluster(unsigned clusterBar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterBar) : "memory");
+}
+__device__ __forceinline__ void ummaIssuePair(int kind, unsigned tmemD, unsigned long long descA, unsigned long long descB,
+                                              unsigned idesc, unsigned accumulate) {
+    if (kind == kKindF16) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else if (kind == kKindI8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
 // 32 lanes x 32 columns of 32-bit accumulators: thread i of the warp receives row i, columns c .. c + 31.
 __device__ __forceinline__ void tmemLoad32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile(
@@ -325,22 +380,25 @@ __device__ __forceinline__ TileCoord tileCoord(const UmmaArgs& g, long long tile
     return {batch, firstRow + inGroup % rowsInGroup, inGroup / rowsInGroup};
 }
 
-template <int BN>
+// PAIR: the kernel runs as clusters of two CTAs that share each MMA (M = 256): a CTA stages its own 128 rows of A and only
+// half of the tile's B columns, so a k slice costs it (128 + BN / 2) rows of 128 bytes from L2 instead of (128 + BN).
+template <int BN, bool PAIR>
 struct SmemPlan {
-    static constexpr int kStageBBytes = BN * kSliceBytes;
+    static constexpr int kCtaB = PAIR ? BN / 2 : BN;  // B rows (tile columns) this CTA stages
+    static constexpr int kStageBBytes = kCtaB * kSliceBytes;
     static constexpr int kStageBytes = kStageABytes + kStageBBytes;
     static constexpr int kStages = kSmemBudget / kStageBytes;
-    static constexpr int kTmemCols = 2 * BN;  // two accumulators
+    static constexpr int kTmemCols = 2 * BN;  // two accumulators of BN columns for this CTA's 128 rows
     static constexpr int kDynamicBytes = kStages * kStageBytes + kStagingBytes + 1024 /* alignment slack */ + 256 /* barriers */;
-    static_assert(kStages >= 3, "ring too short");
+    static_assert(kStages >= 3 && kStages <= 12, "ring length");
     static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols >= 32 && kTmemCols <= 512, "TMEM allocation size");
 };
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                const __grid_constant__ CUtensorMap mapD) {
-    using Plan = SmemPlan<BN>;
+    using Plan = SmemPlan<BN, PAIR>;
     constexpr int kStages = Plan::kStages;
     extern __shared__ unsigned char smemRaw[];
     // the swizzled layout is defined on 1024-byte aligned addresses
@@ -355,6 +413,11 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
     const unsigned smemBase = smemAddr(smem);
     const unsigned fullBar = smemAddr(bars), emptyBar = fullBar + 8 * kStages;
     const unsigned accFullBar = emptyBar + 8 * kStages, accEmptyBar = accFullBar + 16;
+    // In a pair, CTA 0 (the leader) issues the MMAs for both; work is dealt to pairs, not CTAs.
+    const unsigned ctaRank = PAIR ? clusterCtaRank() : 0u;
+    const bool leader = ctaRank == 0;
+    const long long firstUnit = PAIR ? blockIdx.x / 2 : blockIdx.x, unitStride = PAIR ? gridDim.x / 2 : gridDim.x;
+    constexpr int kTileRows = PAIR ? 2 * kBM : kBM;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -363,20 +426,28 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
         }
         for (int a = 0; a < 2; ++a) {
             mbarInit(accFullBar + 8 * a, 1);
-            mbarInit(accEmptyBar + 8 * a, kEpilogueWarps);
+            mbarInit(accEmptyBar + 8 * a, kEpilogueWarps * (PAIR ? 2 : 1));  // the leader hears from both CTAs' epilogues
         }
         *abortFlag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(tmemSlot)),
-                     "r"(unsigned(Plan::kTmemCols))
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {  // the same warp of both CTAs allocates the same columns in both TMEMs
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(tmemSlot)),
+                         "r"(unsigned(Plan::kTmemCols))
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(tmemSlot)),
+                         "r"(unsigned(Plan::kTmemCols))
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tcgen05FenceBefore();
     __syncthreads();
+    if constexpr (PAIR) clusterSync();  // the other CTA's barriers exist before anything is signalled on them
     tcgen05FenceAfter();
     const unsigned tmemBase = *tmemSlot;
 
@@ -386,26 +457,30 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
             int stage = 0;
             unsigned phase = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; ok && tile < g.totalTiles; tile += gridDim.x) {
+            // completion of both CTAs' loads is counted on the leader's barrier, where the MMA issuer waits
+            const unsigned fullBarLeader = PAIR ? mapToCta(fullBar, 0) : fullBar;
+            for (long long tile = firstUnit; ok && tile < g.totalTiles; tile += unitStride) {
                 const TileCoord t = tileCoord(g, tile);
-                const int row0 = t.row * kBM, col0 = t.col * BN;
+                const int row0 = t.row * kTileRows + int(ctaRank) * kBM, col0 = t.col * BN + int(ctaRank) * Plan::kCtaB;
                 for (int ks = 0; ks < g.numKSlices; ++ks) {
                     if (!(ok = mbarWait(emptyBar + 8 * stage, phase ^ 1, abortFlag, kStatusProducerWait))) break;
-                    const unsigned bar = fullBar + 8 * stage;
-                    mbarArriveExpectTx(bar, unsigned(Plan::kStageBytes));
+                    const unsigned bar = fullBarLeader + 8 * stage;
+                    if (leader) mbarArriveExpectTx(fullBar + 8 * stage, unsigned(Plan::kStageBytes) * (PAIR ? 2u : 1u));
                     const unsigned dstA = smemBase + stage * Plan::kStageBytes, dstB = dstA + kStageABytes;
                     const int k0 = ks * g.sliceElems;
+                    const auto load = [&](unsigned dst, const CUtensorMap* map, int c0, int c1, int c2) {
+                        if constexpr (PAIR) tmaLoad3dPair(dst, map, bar, c0, c1, c2);
+                        else tmaLoad3d(dst, map, bar, c0, c1, c2);
+                    };
                     if (g.mnMajorA) {
-                        for (int b = 0; b < g.boxesA; ++b)
-                            tmaLoad3d(dstA + b * g.boxBytesA, &mapA, bar, row0 + b * g.boxElemsA, k0, t.batch * g.batchMulA);
+                        for (int b = 0; b < g.boxesA; ++b) load(dstA + b * g.boxBytesA, &mapA, row0 + b * g.boxElemsA, k0, t.batch * g.batchMulA);
                     } else {
-                        tmaLoad3d(dstA, &mapA, bar, k0, row0, t.batch * g.batchMulA);
+                        load(dstA, &mapA, k0, row0, t.batch * g.batchMulA);
                     }
                     if (g.mnMajorB) {
-                        for (int b = 0; b < g.boxesB; ++b)
-                            tmaLoad3d(dstB + b * g.boxBytesB, &mapB, bar, col0 + b * g.boxElemsB, k0, t.batch * g.batchMulB);
+                        for (int b = 0; b < g.boxesB; ++b) load(dstB + b * g.boxBytesB, &mapB, col0 + b * g.boxElemsB, k0, t.batch * g.batchMulB);
                     } else {
-                        tmaLoad3d(dstB, &mapB, bar, k0, col0, t.batch * g.batchMulB);
+                        load(dstB, &mapB, k0, col0, t.batch * g.batchMulB);
                     }
                     if (++stage == kStages) stage = 0, phase ^= 1;
                 }
@@ -413,12 +488,12 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
         }
         __syncwarp();
     } else if (warp == 1) {
-        // ---- MMA issuer ----
-        if (lane == 0) {
+        // ---- MMA issuer (in a pair: the leader only) ----
+        if (lane == 0 && leader) {
             int stage = 0;
             unsigned phase = 0, tileCount = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; ok && tile < g.totalTiles; tile += gridDim.x, ++tileCount) {
+            for (long long tile = firstUnit; ok && tile < g.totalTiles; tile += unitStride, ++tileCount) {
                 const unsigned acc = tileCount & 1, accPhase = (tileCount >> 1) & 1;
                 if (!(ok = mbarWait(accEmptyBar + 8 * acc, accPhase ^ 1, abortFlag, kStatusMmaTmemWait))) break;
                 tcgen05FenceAfter();
@@ -433,12 +508,18 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                     for (int j = 0; j < kMmasPerStage; ++j) {
                         const unsigned long long descA = (static_cast<unsigned long long>(g.descHi) << 32) | (loA + j * g.kStepA);
                         const unsigned long long descB = (static_cast<unsigned long long>(g.descHi) << 32) | (loB + j * g.kStepB);
-                        ummaIssue(g.kind, tmemD, descA, descB, g.idesc, (ks | j) != 0 ? 1u : 0u);
+                        if constexpr (PAIR) ummaIssuePair(g.kind, tmemD, descA, descB, g.idesc, (ks | j) != 0 ? 1u : 0u);
+                        else ummaIssue(g.kind, tmemD, descA, descB, g.idesc, (ks | j) != 0 ? 1u : 0u);
                     }
-                    tcgen05Commit(emptyBar + 8 * stage);  // the stage may be refilled once these MMAs have read it
+                    // the stage may be refilled (in both CTAs of a pair) once these MMAs have read it
+                    if constexpr (PAIR) tcgen05CommitPair(emptyBar + 8 * stage);
+                    else tcgen05Commit(emptyBar + 8 * stage);
                     if (++stage == kStages) stage = 0, phase ^= 1;
                 }
-                if (ok) tcgen05Commit(accFullBar + 8 * acc);
+                if (ok) {
+                    if constexpr (PAIR) tcgen05CommitPair(accFullBar + 8 * acc);
+                    else tcgen05Commit(accFullBar + 8 * acc);
+                }
             }
         }
         __syncwarp();
@@ -449,7 +530,7 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
         unsigned tileCount = 0, storeStep = 0;
         const bool issuer = threadIdx.x == 64 + 128 * group;  // first lane of the group's first warp owns its bulk stores
         bool ok = true;
-        for (long long tile = blockIdx.x; ok && tile < g.totalTiles; tile += gridDim.x, ++tileCount) {
+        for (long long tile = firstUnit; ok && tile < g.totalTiles; tile += unitStride, ++tileCount) {
             const TileCoord t = tileCoord(g, tile);
             const unsigned acc = tileCount & 1, accPhase = (tileCount >> 1) & 1;
             mbarWait(accFullBar + 8 * acc, accPhase, abortFlag, kStatusEpilogueWait);
@@ -457,7 +538,8 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
             ok = *abortFlag == 0;
             if (!ok) break;
             tcgen05FenceAfter();
-            const int row = t.row * kBM + quarter * 32 + lane;
+            const int tileRow0 = t.row * kTileRows + int(ctaRank) * kBM;  // this CTA's 128 rows of the tile
+            const int row = tileRow0 + quarter * 32 + lane;
             const int col0 = t.col * BN;
             const unsigned taddr = tmemBase + acc * BN + (unsigned(quarter * 32) << 16);
             const bool rowOk = row < g.m;
@@ -466,7 +548,7 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                 Epilogue<int> epi;
                 epi.init(g.epi, t.batch);
                 if (g.tmaStore && epi.mode == kStoreS32 && !g.debugSkipStore)
-                    drainAccumulatorStaged<BN, kStoreS32>(epi, taddr, rowInTile, row, rowOk, t.row * kBM, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
+                    drainAccumulatorStaged<BN, kStoreS32>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
                 else
                     drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
             } else {
@@ -474,17 +556,20 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                 epi.init(g.epi, t.batch);
                 const bool staged = g.tmaStore && !g.debugSkipStore;
                 if (staged && epi.mode == kStoreF32)
-                    drainAccumulatorStaged<BN, kStoreF32>(epi, taddr, rowInTile, row, rowOk, t.row * kBM, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
+                    drainAccumulatorStaged<BN, kStoreF32>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
                 else if (staged && epi.mode == kStoreF16)
-                    drainAccumulatorStaged<BN, kStoreF16>(epi, taddr, rowInTile, row, rowOk, t.row * kBM, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
+                    drainAccumulatorStaged<BN, kStoreF16>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
                 else if (staged && epi.mode == kStoreBF16)
-                    drainAccumulatorStaged<BN, kStoreBF16>(epi, taddr, rowInTile, row, rowOk, t.row * kBM, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
+                    drainAccumulatorStaged<BN, kStoreBF16>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
                 else
                     drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
             }
             tcgen05FenceBefore();
             __syncwarp();
-            if (lane == 0) mbarArrive(accEmptyBar + 8 * acc);
+            if (lane == 0) {
+                if constexpr (PAIR) mbarArriveCluster(mapToCta(accEmptyBar + 8 * acc, 0));
+                else mbarArrive(accEmptyBar + 8 * acc);
+            }
         }
         if (issuer) tmaStoreWaitAll();  // the bulk stores read shared memory and must be done before the CTA ends
     }
@@ -493,10 +578,13 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
     if (*abortFlag) __nanosleep(20000);  // let copies still in flight land before the shared memory is released
     tcgen05FenceBefore();
     __syncthreads();
+    if constexpr (PAIR) clusterSync();  // neither CTA leaves while the other may still read its shared memory or signal it
     if (warp == 1) {
         tcgen05FenceAfter();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(unsigned(Plan::kTmemCols))
-                     : "memory");
+        if constexpr (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(unsigned(Plan::kTmemCols)) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(unsigned(Plan::kTmemCols)) : "memory");
     }
 }
 
@@ -521,7 +609,8 @@ EncodeTiledFn encodeTiled() {
 struct DeviceInfo {
     int sms = 0;
     bool sm100 = false;
-    bool attrSet[3] = {};
+    bool attrSet[5] = {};
+    int clusters[5] = {};  // concurrent two-CTA clusters per kernel variant
 };
 
 DeviceInfo& deviceInfo() {
@@ -572,21 +661,53 @@ int ummaKindOf(const Problem& p) {
     return -1;
 }
 
-template <int BN>
+// How many two-CTA clusters of this kernel the device runs at once (shared memory allows one CTA per SM, and the two
+// CTAs of a cluster must sit in one GPC, so this can fall a little short of half the SM count).
+template <int BN, bool PAIR>
 cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtensorMap& mapB, const CUtensorMap& mapD, int slot,
                        cudaStream_t stream) {
-    using Plan = SmemPlan<BN>;
+    using Plan = SmemPlan<BN, PAIR>;
     DeviceInfo& d = deviceInfo();
     if (!d.attrSet[slot]) {
-        if (cudaError_t e = cudaFuncSetAttribute(ummaGemmKernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kDynamicBytes);
+        if (cudaError_t e = cudaFuncSetAttribute(ummaGemmKernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kDynamicBytes);
             e != cudaSuccess)
             return e;
+        if (PAIR) {
+            cudaLaunchConfig_t probe{};
+            probe.gridDim = dim3(unsigned(d.sms) / 2 * 2), probe.blockDim = dim3(kThreads), probe.dynamicSmemBytes = Plan::kDynamicBytes;
+            cudaLaunchAttribute attr{};
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+            probe.attrs = &attr, probe.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, ummaGemmKernel<BN, PAIR>, &probe) != cudaSuccess || clusters < 1) {
+                cudaGetLastError();
+                clusters = d.sms / 2;
+            }
+            d.clusters[slot] = std::min(clusters, d.sms / 2);
+        }
         d.attrSet[slot] = true;
     }
-    const unsigned grid = unsigned(std::min<long long>(g.totalTiles, d.sms));
-    ummaGemmKernel<BN><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(g, mapA, mapB, mapD);
     countLaunch();
-    return cudaGetLastError();
+    if (!PAIR) {
+        const unsigned grid = unsigned(std::min<long long>(g.totalTiles, d.sms));
+        ummaGemmKernel<BN, PAIR><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(g, mapA, mapB, mapD);
+        return cudaGetLastError();
+    }
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(2u * unsigned(std::min<long long>(g.totalTiles, d.clusters[slot])));
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = Plan::kDynamicBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+    config.attrs = &attr, config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, ummaGemmKernel<BN, PAIR>, g, mapA, mapB, mapD);
+}
+
+int pairClusters() {  // before the first launch has asked the device: half the SMs
+    return deviceInfo().sms / 2;
 }
 
 }  // namespace
@@ -607,26 +728,36 @@ cudaError_t launchUmma(const Problem& p) {
     const int es = elemSizeOf(p.typeA);
     DeviceInfo& d = deviceInfo();
 
-    // Tile width: the candidate that needs the least time by a simple model, waves of tiles times a cost
-    // per tile that grows with the tile's width plus a fixed part.
-    const int tilesM = (p.m + kBM - 1) / kBM;
-    int bn = 256;
-    long long best = -1;
+    // Tile shape: the candidate that needs the least time by a simple model. The main loop is bound by how fast operand
+    // slices arrive from L2, so the cost of a candidate is its number of waves over the machine times the rows of 128
+    // bytes one CTA fetches per k slice: 128 + BN for a CTA on its own, 128 + BN / 2 in a two-CTA pair (tile 256 x BN).
     const int mnBoxElems = kSliceBytes / es;  // an MN-major operand arrives in boxes of 128 bytes of m or n
-    for (int cand : {256, 128, 64}) {
-        if (p.transB && cand % mnBoxElems != 0) continue;  // int8 B^T: a box holds 128 columns, so no 64-wide tile
-        const long long tiles = (long long)tilesM * ((p.n + cand - 1) / cand) * p.batch;
-        const long long cost = (tiles + d.sms - 1) / d.sms * (cand + 32);
-        if (best < 0 || cost < best) best = cost, bn = cand;
-    }
     static const int forcedBn = [] { const char* v = std::getenv("VKZB_UMMA_BN"); return v ? std::atoi(v) : 0; }();
-    if ((forcedBn == 256 || forcedBn == 128 || forcedBn == 64) && !(p.transB && forcedBn % mnBoxElems != 0)) bn = forcedBn;
+    static const int forcedPair = [] { const char* v = std::getenv("VKZB_UMMA_PAIR"); return v ? std::atoi(v) : -1; }();
+    int bn = 0;
+    bool pair = false;
+    long long best = -1;
+    for (int usePair = 1; usePair >= 0; --usePair) {
+        if (forcedPair >= 0 && usePair != forcedPair) continue;
+        for (int cand : {256, 128, 64}) {
+            if (usePair && cand == 64) continue;
+            if (forcedBn && cand != forcedBn) continue;
+            const int ctaB = usePair ? cand / 2 : cand;
+            if (p.transB && ctaB % mnBoxElems != 0) continue;  // int8 B^T: a box holds 128 columns
+            const long long units = (long long)((p.m + (usePair ? 255 : 127)) / (usePair ? 256 : 128)) * ((p.n + cand - 1) / cand) * p.batch;
+            const long long slots = usePair ? pairClusters() : d.sms;
+            const long long cost = (units + slots - 1) / slots * (kBM + ctaB);
+            if (best < 0 || cost < best) best = cost, bn = cand, pair = usePair != 0;
+        }
+    }
+    if (!bn) bn = p.transB && mnBoxElems > 64 ? 128 : 64, pair = false;  // forced values that fit nothing: smallest legal tile
+    const int tilesM = (p.m + (pair ? 255 : 127)) / (pair ? 256 : 128);
     static const int skipStore = [] { const char* v = std::getenv("VKZB_UMMA_SKIP_STORE"); return v ? std::atoi(v) : 0; }();
 
     UmmaArgs g{};
     g.m = p.m, g.n = p.n, g.k = p.k, g.batch = p.batch;
     g.tilesM = tilesM, g.tilesN = (p.n + bn - 1) / bn;
-    g.groupM = 16;
+    g.groupM = pair ? 8 : 16;  // about as many tile rows as tile columns among the tiles in flight
     g.totalTiles = (long long)g.tilesM * g.tilesN * p.batch;
     g.sliceElems = kSliceBytes / es;
     g.numKSlices = (p.k + g.sliceElems - 1) / g.sliceElems;
@@ -636,7 +767,7 @@ cudaError_t launchUmma(const Problem& p) {
     const unsigned format = kind == kKindF16 ? (p.typeA == kBF16 ? 1u : 0u) : kind == kKindTf32 ? 2u : 1u /* signed 8-bit */;
     const unsigned cFormat = kind == kKindI8 ? 2u : 1u;  // s32 : f32
     g.idesc = cFormat << 4 | format << 7 | format << 10 | unsigned(g.mnMajorA) << 15 | unsigned(g.mnMajorB) << 16 |
-              unsigned(bn >> 3) << 17 | unsigned(kBM >> 4) << 24;
+              unsigned(bn >> 3) << 17 | unsigned((pair ? 2 * kBM : kBM) >> 4) << 24;
     // stride offset 1024 bytes (8 rows of 128 bytes), descriptor version 1, 128-byte swizzle
     g.descHi = (1024u >> 4) | 1u << 14 | 2u << 29;
     const unsigned mnBoxBytes = unsigned(g.sliceElems) * kSliceBytes;  // slice-length rows of 128 bytes
@@ -648,7 +779,8 @@ cudaError_t launchUmma(const Problem& p) {
     g.boxElemsA = g.boxElemsB = kSliceBytes / es;
     g.boxBytesA = g.boxBytesB = int(mnBoxBytes);
     g.boxesA = g.mnMajorA ? kBM / g.boxElemsA : 1;
-    g.boxesB = g.mnMajorB ? bn / g.boxElemsB : 1;
+    const int ctaB = pair ? bn / 2 : bn;  // B rows one CTA stages
+    g.boxesB = g.mnMajorB ? ctaB / g.boxElemsB : 1;
     g.batchMulA = p.batch > 1 && p.strideA != 0;
     g.batchMulB = p.batch > 1 && p.strideB != 0;
     g.epi = p.epi;
@@ -659,7 +791,7 @@ cudaError_t launchUmma(const Problem& p) {
     const bool okA = g.mnMajorA ? encodeOperand(&mapA, p.A, p.typeA, p.m, p.k, p.lda, batchA, p.strideA, g.boxElemsA, g.sliceElems)
                                 : encodeOperand(&mapA, p.A, p.typeA, p.k, p.m, p.lda, batchA, p.strideA, g.sliceElems, kBM);
     const bool okB = g.mnMajorB ? encodeOperand(&mapB, p.B, p.typeB, p.n, p.k, p.ldb, batchB, p.strideB, g.boxElemsB, g.sliceElems)
-                                : encodeOperand(&mapB, p.B, p.typeB, p.k, p.n, p.ldb, batchB, p.strideB, g.sliceElems, bn);
+                                : encodeOperand(&mapB, p.B, p.typeB, p.k, p.n, p.ldb, batchB, p.strideB, g.sliceElems, ctaB);
     if (!okA || !okB) return cudaErrorInvalidValue;
 
     // D through TMA when every address the bulk stores start at is 16-byte aligned; otherwise direct stores.
@@ -684,9 +816,10 @@ cudaError_t launchUmma(const Problem& p) {
             g.tmaStore = 0;
     }
 
-    if (bn == 256) return launchWith<256>(g, mapA, mapB, mapD, 0, p.stream);
-    if (bn == 128) return launchWith<128>(g, mapA, mapB, mapD, 1, p.stream);
-    return launchWith<64>(g, mapA, mapB, mapD, 2, p.stream);
+    if (pair) return bn == 256 ? launchWith<256, true>(g, mapA, mapB, mapD, 3, p.stream) : launchWith<128, true>(g, mapA, mapB, mapD, 4, p.stream);
+    if (bn == 256) return launchWith<256, false>(g, mapA, mapB, mapD, 0, p.stream);
+    if (bn == 128) return launchWith<128, false>(g, mapA, mapB, mapD, 1, p.stream);
+    return launchWith<64, false>(g, mapA, mapB, mapD, 2, p.stream);
 }
 
 int ummaDeviceStatus() {
