@@ -26,7 +26,9 @@
 // word, raises a CTA-wide abort flag, and all roles fall through to the common exit, which frees TMEM.
 #include <cuda.h>
 
+#include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "epilogue.cuh"
@@ -71,6 +73,7 @@ struct UmmaArgs {
     int boxElemsA, boxElemsB;       // elements of m / n per box when MN-major
     int batchMulA, batchMulB;       // 0: the operand is shared by every batch entry
     int debugSkipStore;             // measurement aid: run everything but the global stores
+    int debugSkipLoad, debugSkipMma;  // measurement aids: main loop without its TMA loads / without its MMAs
     int tmaStore;                   // D is 16-byte aligned in every dimension: results leave through shared memory and TMA
     EpilogueArgs epi;
 };
@@ -107,10 +110,14 @@ __device__ __forceinline__ unsigned long long globalTimerNs() {
 
 // Waits for the phase with `parity` to complete. Returns false when the CTA is aborting or the wait ran out
 // of time; in the latter case the code is recorded and the abort flag raised for the other roles.
+// SLEEP_NS > 0 puts the waiting thread to sleep between polls: the epilogue warps wait for most of a tile's main loop
+// and share their scheduler with the warp that issues the MMAs, whose issue slots a polling loop would take.
+template <unsigned SLEEP_NS>
 __device__ __noinline__ bool mbarWaitSlow(unsigned bar, unsigned parity, volatile int* abortFlag, unsigned code) {
     const unsigned long long start = globalTimerNs();
     for (unsigned spins = 0;; ++spins) {
         if (mbarTryWait(bar, parity)) return true;
+        if constexpr (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if ((spins & 63u) == 63u) {
             if (*abortFlag) return false;
             if (globalTimerNs() - start > kWaitLimitNs) {
@@ -122,9 +129,10 @@ __device__ __noinline__ bool mbarWaitSlow(unsigned bar, unsigned parity, volatil
         }
     }
 }
+template <unsigned SLEEP_NS = 0>
 __device__ __forceinline__ bool mbarWait(unsigned bar, unsigned parity, volatile int* abortFlag, unsigned code) {
     if (mbarTryWait(bar, parity)) return true;
-    return mbarWaitSlow(bar, parity, abortFlag, code);
+    return mbarWaitSlow<SLEEP_NS>(bar, parity, abortFlag, code);
 }
 
 __device__ __forceinline__ void tmaLoad3d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1, int c2) {
@@ -150,6 +158,13 @@ __device__ __forceinline__ void tmaStoreWaitAll() { asm volatile("cp.async.bulk.
 // Barrier among the four warps of one epilogue group (hardware barriers 1 and 2; 0 is __syncthreads).
 __device__ __forceinline__ void epilogueBarrier(int group) { asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory"); }
 
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool electOne() {
+    unsigned elected;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+    return elected != 0;
+}
+
 __device__ __forceinline__ void tcgen05FenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05FenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -158,27 +173,25 @@ __device__ __forceinline__ void tcgen05Commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void ummaIssue(int kind, unsigned tmemD, unsigned long long descA, unsigned long long descB,
-                                          unsigned idesc, unsigned accumulate) {
-    if (kind == kKindF16) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
-            : "memory");
-    } else if (kind == kKindI8) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
-            : "memory");
+// One tcgen05.mma with kind and CTA group fixed at compile time: the issuing lane runs nothing but address arithmetic
+// between two of these, and how fast it can issue them bounds the whole kernel (one MMA of 128 x 256 x 16 is 128 clocks of
+// tensor-core work; every instruction the lane spends per MMA beyond that budget leaves the tensor cores idle).
+template <int KIND, bool PAIR>
+__device__ __forceinline__ void ummaIssueFixed(unsigned tmemD, unsigned long long descA, unsigned long long descB, unsigned idesc,
+                                               unsigned accumulate) {
+#define VKZB_UMMA(GROUP, KINDNAME)                                                                              \
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                              \
+                 "tcgen05.mma.cta_group::" GROUP ".kind::" KINDNAME " [%0], %1, %2, %3, p;\n\t}"                   \
+                 ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)                              \
+                 : "memory")
+    if constexpr (KIND == kKindF16) {
+        if constexpr (PAIR) VKZB_UMMA("2", "f16"); else VKZB_UMMA("1", "f16");
+    } else if constexpr (KIND == kKindI8) {
+        if constexpr (PAIR) VKZB_UMMA("2", "i8"); else VKZB_UMMA("1", "i8");
     } else {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
-            : "memory");
+        if constexpr (PAIR) VKZB_UMMA("2", "tf32"); else VKZB_UMMA("1", "tf32");
     }
+#undef VKZB_UMMA
 }
 
 // ---- two-CTA pairs (cta_group::2): the two CTAs of a cluster share one MMA of 256 rows ------------------------------
@@ -213,29 +226,6 @@ __device__ __forceinline__ void tcgen05CommitPair(unsigned bar) {
 __device__ __forceinline__ void mbarArriveCluster(unsigned clusterBar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterBar) : "memory");
 }
-__device__ __forceinline__ void ummaIssuePair(int kind, unsigned tmemD, unsigned long long descA, unsigned long long descB,
-                                              unsigned idesc, unsigned accumulate) {
-    if (kind == kKindF16) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
-            : "memory");
-    } else if (kind == kKindI8) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
-            : "memory");
-    } else {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
-            : "memory");
-    }
-}
-
 // 32 lanes x 32 columns of 32-bit accumulators: thread i of the warp receives row i, columns c .. c + 31.
 __device__ __forceinline__ void tmemLoad32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile(
@@ -394,6 +384,54 @@ struct SmemPlan {
     static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols >= 32 && kTmemCols <= 512, "TMEM allocation size");
 };
 
+// The MMA issuer's loop for one operand kind. The whole warp walks it (so addresses and descriptors are warp-uniform
+// values), one elected lane issues. Per k slice: wait for the stage, four MMAs whose descriptors differ by a constant,
+// one commit that frees the stage when they have read it.
+template <int BN, bool PAIR, int KIND>
+__device__ __forceinline__ void mmaIssuerLoop(const UmmaArgs& g, unsigned smemBase, unsigned fullBar, unsigned emptyBar, unsigned accFullBar,
+                                              unsigned accEmptyBar, unsigned tmemBase, long long firstUnit, long long unitStride,
+                                              volatile int* abortFlag) {
+    using Plan = SmemPlan<BN, PAIR>;
+    constexpr int kStages = Plan::kStages;
+    const unsigned long long hi = static_cast<unsigned long long>(g.descHi) << 32;
+    const unsigned lboA = g.lboA << 16, lboB = g.lboB << 16, stepA = g.kStepA, stepB = g.kStepB, idesc = g.idesc;
+    const int slices = g.numKSlices;
+    const bool skipLoad = g.debugSkipLoad != 0, skipMma = g.debugSkipMma != 0;
+    int stage = 0;
+    unsigned phase = 0, tileCount = 0;
+    bool ok = true;
+    for (long long tile = firstUnit; ok && tile < g.totalTiles; tile += unitStride, ++tileCount) {
+        const unsigned acc = tileCount & 1, accPhase = (tileCount >> 1) & 1;
+        if (!(ok = mbarWait(accEmptyBar + 8 * acc, accPhase ^ 1, abortFlag, kStatusMmaTmemWait))) break;
+        tcgen05FenceAfter();
+        const unsigned tmemD = tmemBase + acc * BN;
+        for (int ks = 0; ks < slices; ++ks) {
+            if (!skipLoad && !(ok = mbarWait(fullBar + 8 * stage, phase, abortFlag, kStatusMmaFullWait))) break;
+            tcgen05FenceAfter();
+            const unsigned addrA = smemBase + stage * Plan::kStageBytes, addrB = addrA + kStageABytes;
+            const unsigned long long descA = hi | (((addrA & 0x3FFFFu) >> 4) | lboA), descB = hi | (((addrB & 0x3FFFFu) >> 4) | lboB);
+            if (electOne()) {
+                if (!skipMma) {
+                    ummaIssueFixed<KIND, PAIR>(tmemD, descA, descB, idesc, ks != 0 ? 1u : 0u);
+#pragma unroll
+                    for (int j = 1; j < kMmasPerStage; ++j)  // the low word cannot carry into the high one: addresses stay below 2^14 units
+                        ummaIssueFixed<KIND, PAIR>(tmemD, descA + j * stepA, descB + j * stepB, idesc, 1u);
+                }
+                // the stage may be refilled (in both CTAs of a pair) once these MMAs have read it
+                if constexpr (PAIR) tcgen05CommitPair(emptyBar + 8 * stage);
+                else tcgen05Commit(emptyBar + 8 * stage);
+            }
+            __syncwarp();
+            if (++stage == kStages) stage = 0, phase ^= 1;
+        }
+        if (ok && electOne()) {
+            if constexpr (PAIR) tcgen05CommitPair(accFullBar + 8 * acc);
+            else tcgen05Commit(accFullBar + 8 * acc);
+        }
+        __syncwarp();
+    }
+}
+
 template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
@@ -453,7 +491,7 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
 
     if (warp == 0) {
         // ---- TMA producer ----
-        if (lane == 0) {
+        if (lane == 0 && !g.debugSkipLoad) {
             int stage = 0;
             unsigned phase = 0;
             bool ok = true;
@@ -489,38 +527,13 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
         __syncwarp();
     } else if (warp == 1) {
         // ---- MMA issuer (in a pair: the leader only) ----
-        if (lane == 0 && leader) {
-            int stage = 0;
-            unsigned phase = 0, tileCount = 0;
-            bool ok = true;
-            for (long long tile = firstUnit; ok && tile < g.totalTiles; tile += unitStride, ++tileCount) {
-                const unsigned acc = tileCount & 1, accPhase = (tileCount >> 1) & 1;
-                if (!(ok = mbarWait(accEmptyBar + 8 * acc, accPhase ^ 1, abortFlag, kStatusMmaTmemWait))) break;
-                tcgen05FenceAfter();
-                const unsigned tmemD = tmemBase + acc * BN;
-                for (int ks = 0; ks < g.numKSlices; ++ks) {
-                    if (!(ok = mbarWait(fullBar + 8 * stage, phase, abortFlag, kStatusMmaFullWait))) break;
-                    tcgen05FenceAfter();
-                    const unsigned addrA = smemBase + stage * Plan::kStageBytes, addrB = addrA + kStageABytes;
-                    const unsigned loA = ((addrA & 0x3FFFFu) >> 4) | (g.lboA << 16);
-                    const unsigned loB = ((addrB & 0x3FFFFu) >> 4) | (g.lboB << 16);
-#pragma unroll
-                    for (int j = 0; j < kMmasPerStage; ++j) {
-                        const unsigned long long descA = (static_cast<unsigned long long>(g.descHi) << 32) | (loA + j * g.kStepA);
-                        const unsigned long long descB = (static_cast<unsigned long long>(g.descHi) << 32) | (loB + j * g.kStepB);
-                        if constexpr (PAIR) ummaIssuePair(g.kind, tmemD, descA, descB, g.idesc, (ks | j) != 0 ? 1u : 0u);
-                        else ummaIssue(g.kind, tmemD, descA, descB, g.idesc, (ks | j) != 0 ? 1u : 0u);
-                    }
-                    // the stage may be refilled (in both CTAs of a pair) once these MMAs have read it
-                    if constexpr (PAIR) tcgen05CommitPair(emptyBar + 8 * stage);
-                    else tcgen05Commit(emptyBar + 8 * stage);
-                    if (++stage == kStages) stage = 0, phase ^= 1;
-                }
-                if (ok) {
-                    if constexpr (PAIR) tcgen05CommitPair(accFullBar + 8 * acc);
-                    else tcgen05Commit(accFullBar + 8 * acc);
-                }
-            }
+        if (leader) {
+            if (g.kind == kKindF16)
+                mmaIssuerLoop<BN, PAIR, kKindF16>(g, smemBase, fullBar, emptyBar, accFullBar, accEmptyBar, tmemBase, firstUnit, unitStride, abortFlag);
+            else if (g.kind == kKindI8)
+                mmaIssuerLoop<BN, PAIR, kKindI8>(g, smemBase, fullBar, emptyBar, accFullBar, accEmptyBar, tmemBase, firstUnit, unitStride, abortFlag);
+            else
+                mmaIssuerLoop<BN, PAIR, kKindTf32>(g, smemBase, fullBar, emptyBar, accFullBar, accEmptyBar, tmemBase, firstUnit, unitStride, abortFlag);
         }
         __syncwarp();
     } else {
@@ -533,7 +546,7 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
         for (long long tile = firstUnit; ok && tile < g.totalTiles; tile += unitStride, ++tileCount) {
             const TileCoord t = tileCoord(g, tile);
             const unsigned acc = tileCount & 1, accPhase = (tileCount >> 1) & 1;
-            mbarWait(accFullBar + 8 * acc, accPhase, abortFlag, kStatusEpilogueWait);
+            if (lane == 0) mbarWait(accFullBar + 8 * acc, accPhase, abortFlag, kStatusEpilogueWait);  // one poller per warp
             epilogueBarrier(group);  // the four warps take the same decision: a wait that gave up has raised the flag by now
             ok = *abortFlag == 0;
             if (!ok) break;
@@ -753,6 +766,7 @@ cudaError_t launchUmma(const Problem& p) {
     if (!bn) bn = p.transB && mnBoxElems > 64 ? 128 : 64, pair = false;  // forced values that fit nothing: smallest legal tile
     const int tilesM = (p.m + (pair ? 255 : 127)) / (pair ? 256 : 128);
     static const int skipStore = [] { const char* v = std::getenv("VKZB_UMMA_SKIP_STORE"); return v ? std::atoi(v) : 0; }();
+    static const int debugBits = [] { const char* v = std::getenv("VKZB_UMMA_DEBUG"); return v ? std::atoi(v) : 0; }();
 
     UmmaArgs g{};
     g.m = p.m, g.n = p.n, g.k = p.k, g.batch = p.batch;
@@ -784,7 +798,8 @@ cudaError_t launchUmma(const Problem& p) {
     g.batchMulA = p.batch > 1 && p.strideA != 0;
     g.batchMulB = p.batch > 1 && p.strideB != 0;
     g.epi = p.epi;
-    g.debugSkipStore = skipStore;
+    g.debugSkipStore = skipStore || (debugBits & 1);
+    g.debugSkipLoad = (debugBits & 2) != 0, g.debugSkipMma = (debugBits & 4) != 0;
 
     CUtensorMap mapA, mapB;
     const long long batchA = g.batchMulA ? p.batch : 1, batchB = g.batchMulB ? p.batch : 1;
@@ -816,6 +831,10 @@ cudaError_t launchUmma(const Problem& p) {
             g.tmaStore = 0;
     }
 
+    static const bool logChoice = [] { const char* v = std::getenv("VKZB_LOG"); return v && !std::strcmp(v, "debug"); }();
+    if (logChoice)
+        std::fprintf(stderr, "vkzb: umma tile %d x %d%s, %lld tiles, %d k slices, %s store\n", pair ? 256 : 128, bn, pair ? " (two-CTA pairs)" : "",
+                     g.totalTiles, g.numKSlices, g.tmaStore ? "TMA" : "direct");
     if (pair) return bn == 256 ? launchWith<256, true>(g, mapA, mapB, mapD, 3, p.stream) : launchWith<128, true>(g, mapA, mapB, mapD, 4, p.stream);
     if (bn == 256) return launchWith<256, false>(g, mapA, mapB, mapD, 0, p.stream);
     if (bn == 128) return launchWith<128, false>(g, mapA, mapB, mapD, 1, p.stream);
