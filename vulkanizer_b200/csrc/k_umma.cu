@@ -43,10 +43,9 @@ constexpr int kMmasPerStage = 4;            // 128 bytes / 32 bytes of k per tcg
 constexpr int kEpilogueGroups = 2;             // each group of 4 warps covers the 128 TMEM lanes and takes every other column step
 constexpr int kEpilogueWarps = 4 * kEpilogueGroups;
 constexpr int kThreads = 32 * (2 + kEpilogueWarps);
-constexpr int kSmemBudget = 200 * 1024;     // ring of stages; leaves room for barriers and alignment slack
+constexpr int kSmemTotal = 227 * 1024;      // dynamic shared memory a CTA may have on sm_100
 constexpr int kStoreCols = 16;                // columns per staged epilogue step
 constexpr int kStagingBufferBytes = kBM * kStoreCols * 4;             // 128 rows x 16 columns of 4 bytes
-constexpr int kStagingBytes = kEpilogueGroups * 2 * kStagingBufferBytes;  // two buffers per group
 constexpr unsigned long long kWaitLimitNs = 4000000000ull;  // a wait longer than this is a lost signal
 
 enum UmmaKind : int { kKindF16 = 0, kKindTf32 = 1, kKindI8 = 2 };
@@ -74,6 +73,7 @@ struct UmmaArgs {
     int batchMulA, batchMulB;       // 0: the operand is shared by every batch entry
     int debugSkipStore;             // measurement aid: run everything but the global stores
     int debugSkipLoad, debugSkipMma;  // measurement aids: main loop without its TMA loads / without its MMAs
+    int debugEpi;                    // measurement aids for the staged epilogue: 1 no bulk store, 2 no shared-memory writes, 4 no fence
     int tmaStore;                   // D is 16-byte aligned in every dimension: results leave through shared memory and TMA
     EpilogueArgs epi;
 };
@@ -241,7 +241,9 @@ __device__ __forceinline__ void tmemLoad32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ void tmemLoad16(unsigned taddr, unsigned (&r)[16]) {
+__device__ __forceinline__ void tmemWaitLoads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same load without the wait: the values may be used only after tmemWaitLoads().
+__device__ __forceinline__ void tmemLoad16Issue(unsigned taddr, unsigned (&r)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -249,9 +251,7 @@ __device__ __forceinline__ void tmemLoad16(unsigned taddr, unsigned (&r)[16]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-
 template <typename Acc>
 __device__ __forceinline__ Acc accumulatorValue(unsigned bits) {
     if constexpr (std::is_same_v<Acc, int>) return int(bits);
@@ -288,9 +288,11 @@ __device__ __forceinline__ void storeChunk(const Epilogue<Acc>& epi, const unsig
     }
 }
 
-// One accumulator (this warp's 32 rows; its group's share of the BN columns) from TMEM to global memory, 32 columns at a time.
-template <int BN, typename Acc>
-__device__ __forceinline__ void drainAccumulator(const Epilogue<Acc>& epi, unsigned taddr, int row, bool rowOk, int col0, int n, int group) {
+// One accumulator (this warp's 32 rows; its group's share of the BN columns) from TMEM straight to global memory, 32 columns at
+// a time, with the store form fixed at compile time. Out of line, one instance per form: the direct path serves the shapes
+// TMA cannot (D not 16-byte aligned in every dimension), and keeping it out of the kernel body keeps the staged path lean.
+template <int BN, int MODE, typename Acc>
+__device__ __noinline__ void drainAccumulatorDirect(const Epilogue<Acc>& epi, unsigned taddr, int row, bool rowOk, int col0, int n, int group) {
 #pragma unroll 1
     for (int c = group * 32; c < BN; c += 32 * kEpilogueGroups) {
         const int count = n - (col0 + c);
@@ -298,17 +300,30 @@ __device__ __forceinline__ void drainAccumulator(const Epilogue<Acc>& epi, unsig
         unsigned v[32];
         tmemLoad32(taddr + c, v);
         if (!rowOk) continue;
-        switch (epi.mode) {
-        case kStoreF32: if constexpr (std::is_same_v<Acc, float>) storeChunk<kStoreF32>(epi, v, row, col0 + c, count); break;
-        case kStoreF16: if constexpr (std::is_same_v<Acc, float>) storeChunk<kStoreF16>(epi, v, row, col0 + c, count); break;
-        case kStoreBF16: if constexpr (std::is_same_v<Acc, float>) storeChunk<kStoreBF16>(epi, v, row, col0 + c, count); break;
-        case kStoreS32: if constexpr (std::is_same_v<Acc, int>) storeChunk<kStoreS32>(epi, v, row, col0 + c, count); break;
-        default:
+        if constexpr (MODE == kStoreSlow) {
+#pragma unroll 1
+            for (int j = 0; j < 32; ++j) {
+                unsigned bits = v[0];  // select v[j] without indexing registers dynamically
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (j < count) epi.storeSlow(row, col0 + c + j, accumulatorValue<Acc>(v[j]));
-            break;
+                for (int q = 1; q < 32; ++q) bits = j == q ? v[q] : bits;
+                if (j < count) epi.storeSlow(row, col0 + c + j, accumulatorValue<Acc>(bits));
+            }
+        } else {
+            storeChunk<MODE>(epi, v, row, col0 + c, count);
         }
+    }
+}
+
+template <int BN, typename Acc>
+__device__ __forceinline__ void drainAccumulator(const Epilogue<Acc>& epi, unsigned taddr, int row, bool rowOk, int col0, int n, int group) {
+    if constexpr (std::is_same_v<Acc, int>) {
+        if (epi.mode == kStoreS32) drainAccumulatorDirect<BN, kStoreS32>(epi, taddr, row, rowOk, col0, n, group);
+        else drainAccumulatorDirect<BN, kStoreSlow>(epi, taddr, row, rowOk, col0, n, group);
+    } else {
+        if (epi.mode == kStoreF32) drainAccumulatorDirect<BN, kStoreF32>(epi, taddr, row, rowOk, col0, n, group);
+        else if (epi.mode == kStoreF16) drainAccumulatorDirect<BN, kStoreF16>(epi, taddr, row, rowOk, col0, n, group);
+        else if (epi.mode == kStoreBF16) drainAccumulatorDirect<BN, kStoreBF16>(epi, taddr, row, rowOk, col0, n, group);
+        else drainAccumulatorDirect<BN, kStoreSlow>(epi, taddr, row, rowOk, col0, n, group);
     }
 }
 
@@ -317,40 +332,80 @@ __device__ __forceinline__ void drainAccumulator(const Epilogue<Acc>& epi, unsig
 // writes full lines, clips rows and columns outside D, and keeps many stores in flight where four warps of scalar
 // stores cannot. Two buffers per group alternate: a buffer is rewritten only after the bulk store that read it two steps
 // earlier has finished reading.
-template <int BN, int MODE, typename Acc>
-__device__ __forceinline__ void drainAccumulatorStaged(const Epilogue<Acc>& epi, unsigned taddr, int rowInTile, int row, bool rowOk,
-                                                       int row0, int col0, int n, int batchEntry, const CUtensorMap* mapD,
-                                                       unsigned char* staging, unsigned& step, bool issuer, int group) {
+// One staged step: 16 columns of this warp's rows, already in registers, through a shared-memory buffer to a bulk store.
+template <int MODE, int NB, typename Acc>
+__device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const unsigned (&v)[kStoreCols], int rowInTile, int row, bool rowOk,
+                                              int row0, int col, int count, int batchEntry, const CUtensorMap* mapD, unsigned char* staging,
+                                              unsigned& step, bool issuer, int group, int dbg) {
     using Elem = std::conditional_t<MODE == kStoreF32, float, std::conditional_t<MODE == kStoreS32, int,
                  std::conditional_t<MODE == kStoreF16, __half, __nv_bfloat16>>>;
     const Acc alpha = epi.alpha, beta = epi.beta;
-    const bool readC = epi.readC;
-#pragma unroll 1
-    for (int c = group * kStoreCols; c < BN; c += kStoreCols * kEpilogueGroups) {
-        const int count = n - (col0 + c);
-        if (count <= 0) break;
-        unsigned v[kStoreCols];
-        tmemLoad16(taddr + c, v);
-        Elem* buf = reinterpret_cast<Elem*>(staging + ((step & 1u) + 2 * group) * kStagingBufferBytes) + rowInTile;
+    Elem* buf = reinterpret_cast<Elem*>(staging + (step % NB + NB * group) * kStagingBufferBytes) + rowInTile;
+    if constexpr (NB < 3) {  // two buffers: the one about to be rewritten is checked right here, and announced by a barrier
         if (issuer) tmaStoreWaitRead<1>();
         epilogueBarrier(group);
-        const Elem* cin = reinterpret_cast<const Elem*>(epi.C) + (row + (col0 + c) * epi.ldc);
+    }
+    if (!(dbg & 2)) {
+        if (epi.readC && rowOk) {
+            const Elem* cin = reinterpret_cast<const Elem*>(epi.C) + (row + col * epi.ldc);
 #pragma unroll
-        for (int j = 0; j < kStoreCols; ++j) {
-            Acc r = alpha * accumulatorValue<Acc>(v[j]);
-            if (readC && rowOk && j < count) {
-                if constexpr (MODE == kStoreF32 || MODE == kStoreS32) r += beta * Acc(cin[j * epi.ldc]);
-                else if constexpr (MODE == kStoreF16) r += beta * __half2float(cin[j * epi.ldc]);
-                else r += beta * __bfloat162float(cin[j * epi.ldc]);
+            for (int j = 0; j < kStoreCols; ++j) {
+                Acc r = alpha * accumulatorValue<Acc>(v[j]);
+                if (j < count) {
+                    if constexpr (MODE == kStoreF32 || MODE == kStoreS32) r += beta * Acc(cin[j * epi.ldc]);
+                    else if constexpr (MODE == kStoreF16) r += beta * __half2float(cin[j * epi.ldc]);
+                    else r += beta * __bfloat162float(cin[j * epi.ldc]);
+                }
+                if constexpr (MODE == kStoreF32 || MODE == kStoreS32) buf[j * kBM] = r;
+                else if constexpr (MODE == kStoreF16) buf[j * kBM] = __float2half_rn(r);
+                else buf[j * kBM] = __float2bfloat16_rn(r);
             }
-            if constexpr (MODE == kStoreF32 || MODE == kStoreS32) buf[j * kBM] = r;
-            else if constexpr (MODE == kStoreF16) buf[j * kBM] = __float2half_rn(r);
-            else buf[j * kBM] = __float2bfloat16_rn(r);
+        } else {
+#pragma unroll
+            for (int j = 0; j < kStoreCols; ++j) {
+                const Acc r = alpha * accumulatorValue<Acc>(v[j]);
+                if constexpr (MODE == kStoreF32 || MODE == kStoreS32) buf[j * kBM] = r;
+                else if constexpr (MODE == kStoreF16) buf[j * kBM] = __float2half_rn(r);
+                else buf[j * kBM] = __float2bfloat16_rn(r);
+            }
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        epilogueBarrier(group);
-        if (issuer) tmaStore3d(mapD, smemAddr(buf - rowInTile), row0, col0 + c, batchEntry);
-        ++step;
+    }
+    if (!(dbg & 4)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    epilogueBarrier(group);
+    if (issuer && !(dbg & 1)) {
+        tmaStore3d(mapD, smemAddr(buf - rowInTile), row0, col, batchEntry);
+        // more buffers: after this step's store is on its way, make sure the buffer of the step AFTER the next one is
+        // free; the other warps learn it at the next step's barrier, before they reach that buffer
+        if constexpr (NB >= 3) tmaStoreWaitRead<NB - 2>();
+    }
+    ++step;
+}
+
+// The accumulator in staged steps, kBatch at a time: a TMEM load takes long to deliver, so the
+// loads of several steps are issued together and waited for once (one load per wait left the epilogue waiting on TMEM
+// for more than half of its time).
+template <int BN, int MODE, int NB, typename Acc>
+__device__ __forceinline__ void drainAccumulatorStaged(const Epilogue<Acc>& epi, unsigned taddr, int rowInTile, int row, bool rowOk,
+                                                       int row0, int col0, int n, int batchEntry, const CUtensorMap* mapD,
+                                                       unsigned char* staging, unsigned& step, bool issuer, int group, int dbg) {
+    constexpr int kStride = kStoreCols * kEpilogueGroups;  // columns between two steps of one group
+    constexpr int kSteps = BN / kStride;                   // steps of one group per tile
+    constexpr int kBatch = kSteps < 2 ? kSteps : 2;  // four at a time spill registers and run three times slower
+#pragma unroll 1
+    for (int c = group * kStoreCols; c < BN; c += kBatch * kStride) {
+        if (n - (col0 + c) <= 0) break;
+        unsigned v[kBatch][kStoreCols];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b)
+            if (n - (col0 + c + b * kStride) > 0) tmemLoad16Issue(taddr + c + b * kStride, v[b]);
+        tmemWaitLoads();
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            const int count = n - (col0 + c + b * kStride);
+            if (count > 0)
+                stageAndStore<MODE, NB>(epi, v[b], rowInTile, row, rowOk, row0, col0 + c + b * kStride, count, batchEntry, mapD, staging, step, issuer,
+                                        group, dbg);
+        }
     }
 }
 
@@ -372,26 +427,82 @@ __device__ __forceinline__ TileCoord tileCoord(const UmmaArgs& g, long long tile
 
 // PAIR: the kernel runs as clusters of two CTAs that share each MMA (M = 256): a CTA stages its own 128 rows of A and only
 // half of the tile's B columns, so a k slice costs it (128 + BN / 2) rows of 128 bytes from L2 instead of (128 + BN).
-template <int BN, bool PAIR>
+// WIDE: for products with few k slices per tile the time goes into writing D, not into the main loop. Such launches
+// trade ring stages for epilogue buffers: six staging buffers per warp group instead of two keep enough bulk stores in
+// flight to cover the latency of a store (with two, a group can have 16 KiB on its way, about half of what HBM takes).
+template <int BN, bool PAIR, bool WIDE>
 struct SmemPlan {
     static constexpr int kCtaB = PAIR ? BN / 2 : BN;  // B rows (tile columns) this CTA stages
     static constexpr int kStageBBytes = kCtaB * kSliceBytes;
     static constexpr int kStageBytes = kStageABytes + kStageBBytes;
-    static constexpr int kStages = kSmemBudget / kStageBytes;
+    static constexpr int kStagingBuffers = WIDE ? 6 : 2;  // per epilogue group
+    static constexpr int kStagingBytes = kEpilogueGroups * kStagingBuffers * kStagingBufferBytes;
+    static constexpr int kOverhead = 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int kStages = (kSmemTotal - kStagingBytes - kOverhead) / kStageBytes > 12 ? 12 : (kSmemTotal - kStagingBytes - kOverhead) / kStageBytes;
     static constexpr int kTmemCols = 2 * BN;  // two accumulators of BN columns for this CTA's 128 rows
-    static constexpr int kDynamicBytes = kStages * kStageBytes + kStagingBytes + 1024 /* alignment slack */ + 256 /* barriers */;
-    static_assert(kStages >= 3 && kStages <= 12, "ring length");
+    static constexpr int kDynamicBytes = kStages * kStageBytes + kStagingBytes + kOverhead;
+    static_assert(kStages >= 2, "ring length");
     static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols >= 32 && kTmemCols <= 512, "TMEM allocation size");
+    static_assert(kDynamicBytes <= kSmemTotal, "shared memory");
 };
+
+// The TMA producer's loop. KMAJOR: both operands are contiguous along k (op(A) = A^T, op(B) = B), one box each per stage;
+// otherwise an operand that is contiguous along m or n arrives as several boxes of 128 bytes by slice-length rows.
+template <int BN, bool PAIR, bool WIDE, bool KMAJOR>
+__device__ __forceinline__ void producerLoop(const UmmaArgs& g, const CUtensorMap* mapA, const CUtensorMap* mapB, unsigned smemBase,
+                                             unsigned fullBar, unsigned emptyBar, unsigned ctaRank, long long firstUnit, long long unitStride,
+                                             volatile int* abortFlag) {
+    using Plan = SmemPlan<BN, PAIR, WIDE>;
+    constexpr int kStages = Plan::kStages;
+    constexpr int kTileRows = PAIR ? 2 * kBM : kBM;
+    const bool leader = ctaRank == 0;
+    // completion of both CTAs' loads is counted on the leader's barrier, where the MMA issuer waits
+    const unsigned fullBarLeader = PAIR ? mapToCta(fullBar, 0) : fullBar;
+    const int slices = g.numKSlices, sliceElems = g.sliceElems;
+    int stage = 0;
+    unsigned phase = 0;
+    for (long long tile = firstUnit; tile < g.totalTiles; tile += unitStride) {
+        const TileCoord t = tileCoord(g, tile);
+        const int row0 = t.row * kTileRows + int(ctaRank) * kBM, col0 = t.col * BN + int(ctaRank) * Plan::kCtaB;
+        const int batchA = t.batch * g.batchMulA, batchB = t.batch * g.batchMulB;
+        for (int ks = 0; ks < slices; ++ks) {
+            if (!mbarWait(emptyBar + 8 * stage, phase ^ 1, abortFlag, kStatusProducerWait)) return;
+            const unsigned bar = fullBarLeader + 8 * stage;
+            if (leader) mbarArriveExpectTx(fullBar + 8 * stage, unsigned(Plan::kStageBytes) * (PAIR ? 2u : 1u));
+            const unsigned dstA = smemBase + stage * Plan::kStageBytes, dstB = dstA + kStageABytes;
+            const int k0 = ks * sliceElems;
+            const auto load = [&](unsigned dst, const CUtensorMap* map, int c0, int c1, int c2) {
+                if constexpr (PAIR) tmaLoad3dPair(dst, map, bar, c0, c1, c2);
+                else tmaLoad3d(dst, map, bar, c0, c1, c2);
+            };
+            if constexpr (KMAJOR) {
+                load(dstA, mapA, k0, row0, batchA);
+                load(dstB, mapB, k0, col0, batchB);
+            } else {
+                if (g.mnMajorA) {
+                    for (int b = 0; b < g.boxesA; ++b) load(dstA + b * g.boxBytesA, mapA, row0 + b * g.boxElemsA, k0, batchA);
+                } else {
+                    load(dstA, mapA, k0, row0, batchA);
+                }
+                if (g.mnMajorB) {
+                    for (int b = 0; b < g.boxesB; ++b) load(dstB + b * g.boxBytesB, mapB, col0 + b * g.boxElemsB, k0, batchB);
+                } else {
+                    load(dstB, mapB, k0, col0, batchB);
+                }
+            }
+            if (++stage == kStages) stage = 0, phase ^= 1;
+        }
+    }
+}
 
 // The MMA issuer's loop for one operand kind. The whole warp walks it (so addresses and descriptors are warp-uniform
 // values), one elected lane issues. Per k slice: wait for the stage, four MMAs whose descriptors differ by a constant,
 // one commit that frees the stage when they have read it.
-template <int BN, bool PAIR, int KIND>
+template <int BN, bool PAIR, bool WIDE, int KIND>
 __device__ __forceinline__ void mmaIssuerLoop(const UmmaArgs& g, unsigned smemBase, unsigned fullBar, unsigned emptyBar, unsigned accFullBar,
                                               unsigned accEmptyBar, unsigned tmemBase, long long firstUnit, long long unitStride,
                                               volatile int* abortFlag) {
-    using Plan = SmemPlan<BN, PAIR>;
+    using Plan = SmemPlan<BN, PAIR, WIDE>;
     constexpr int kStages = Plan::kStages;
     const unsigned long long hi = static_cast<unsigned long long>(g.descHi) << 32;
     const unsigned lboA = g.lboA << 16, lboB = g.lboB << 16, stepA = g.kStepA, stepB = g.kStepB, idesc = g.idesc;
@@ -432,17 +543,17 @@ __device__ __forceinline__ void mmaIssuerLoop(const UmmaArgs& g, unsigned smemBa
     }
 }
 
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, bool WIDE>
 __global__ void __launch_bounds__(kThreads, 1)
 ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                const __grid_constant__ CUtensorMap mapD) {
-    using Plan = SmemPlan<BN, PAIR>;
+    using Plan = SmemPlan<BN, PAIR, WIDE>;
     constexpr int kStages = Plan::kStages;
     extern __shared__ unsigned char smemRaw[];
     // the swizzled layout is defined on 1024-byte aligned addresses
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
     unsigned char* staging = smem + kStages * Plan::kStageBytes;  // epilogue buffers, 1024-byte aligned like the stages
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(staging + kStagingBytes);
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(staging + Plan::kStagingBytes);
     // bars[0 .. S): stage filled; [S .. 2S): stage drained; [2S, 2S+2): accumulator ready; [2S+2, 2S+4): accumulator drained
     unsigned* tmemSlot = reinterpret_cast<unsigned*>(bars + 2 * kStages + 4);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
@@ -492,48 +603,21 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
     if (warp == 0) {
         // ---- TMA producer ----
         if (lane == 0 && !g.debugSkipLoad) {
-            int stage = 0;
-            unsigned phase = 0;
-            bool ok = true;
-            // completion of both CTAs' loads is counted on the leader's barrier, where the MMA issuer waits
-            const unsigned fullBarLeader = PAIR ? mapToCta(fullBar, 0) : fullBar;
-            for (long long tile = firstUnit; ok && tile < g.totalTiles; tile += unitStride) {
-                const TileCoord t = tileCoord(g, tile);
-                const int row0 = t.row * kTileRows + int(ctaRank) * kBM, col0 = t.col * BN + int(ctaRank) * Plan::kCtaB;
-                for (int ks = 0; ks < g.numKSlices; ++ks) {
-                    if (!(ok = mbarWait(emptyBar + 8 * stage, phase ^ 1, abortFlag, kStatusProducerWait))) break;
-                    const unsigned bar = fullBarLeader + 8 * stage;
-                    if (leader) mbarArriveExpectTx(fullBar + 8 * stage, unsigned(Plan::kStageBytes) * (PAIR ? 2u : 1u));
-                    const unsigned dstA = smemBase + stage * Plan::kStageBytes, dstB = dstA + kStageABytes;
-                    const int k0 = ks * g.sliceElems;
-                    const auto load = [&](unsigned dst, const CUtensorMap* map, int c0, int c1, int c2) {
-                        if constexpr (PAIR) tmaLoad3dPair(dst, map, bar, c0, c1, c2);
-                        else tmaLoad3d(dst, map, bar, c0, c1, c2);
-                    };
-                    if (g.mnMajorA) {
-                        for (int b = 0; b < g.boxesA; ++b) load(dstA + b * g.boxBytesA, &mapA, row0 + b * g.boxElemsA, k0, t.batch * g.batchMulA);
-                    } else {
-                        load(dstA, &mapA, k0, row0, t.batch * g.batchMulA);
-                    }
-                    if (g.mnMajorB) {
-                        for (int b = 0; b < g.boxesB; ++b) load(dstB + b * g.boxBytesB, &mapB, col0 + b * g.boxElemsB, k0, t.batch * g.batchMulB);
-                    } else {
-                        load(dstB, &mapB, k0, col0, t.batch * g.batchMulB);
-                    }
-                    if (++stage == kStages) stage = 0, phase ^= 1;
-                }
-            }
+            if (!g.mnMajorA && !g.mnMajorB)
+                producerLoop<BN, PAIR, WIDE, true>(g, &mapA, &mapB, smemBase, fullBar, emptyBar, ctaRank, firstUnit, unitStride, abortFlag);
+            else
+                producerLoop<BN, PAIR, WIDE, false>(g, &mapA, &mapB, smemBase, fullBar, emptyBar, ctaRank, firstUnit, unitStride, abortFlag);
         }
         __syncwarp();
     } else if (warp == 1) {
         // ---- MMA issuer (in a pair: the leader only) ----
         if (leader) {
             if (g.kind == kKindF16)
-                mmaIssuerLoop<BN, PAIR, kKindF16>(g, smemBase, fullBar, emptyBar, accFullBar, accEmptyBar, tmemBase, firstUnit, unitStride, abortFlag);
+                mmaIssuerLoop<BN, PAIR, WIDE, kKindF16>(g, smemBase, fullBar, emptyBar, accFullBar, accEmptyBar, tmemBase, firstUnit, unitStride, abortFlag);
             else if (g.kind == kKindI8)
-                mmaIssuerLoop<BN, PAIR, kKindI8>(g, smemBase, fullBar, emptyBar, accFullBar, accEmptyBar, tmemBase, firstUnit, unitStride, abortFlag);
+                mmaIssuerLoop<BN, PAIR, WIDE, kKindI8>(g, smemBase, fullBar, emptyBar, accFullBar, accEmptyBar, tmemBase, firstUnit, unitStride, abortFlag);
             else
-                mmaIssuerLoop<BN, PAIR, kKindTf32>(g, smemBase, fullBar, emptyBar, accFullBar, accEmptyBar, tmemBase, firstUnit, unitStride, abortFlag);
+                mmaIssuerLoop<BN, PAIR, WIDE, kKindTf32>(g, smemBase, fullBar, emptyBar, accFullBar, accEmptyBar, tmemBase, firstUnit, unitStride, abortFlag);
         }
         __syncwarp();
     } else {
@@ -561,7 +645,7 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                 Epilogue<int> epi;
                 epi.init(g.epi, t.batch);
                 if (g.tmaStore && epi.mode == kStoreS32 && !g.debugSkipStore)
-                    drainAccumulatorStaged<BN, kStoreS32>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
+                    drainAccumulatorStaged<BN, kStoreS32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, g.debugEpi);
                 else
                     drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
             } else {
@@ -569,11 +653,11 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                 epi.init(g.epi, t.batch);
                 const bool staged = g.tmaStore && !g.debugSkipStore;
                 if (staged && epi.mode == kStoreF32)
-                    drainAccumulatorStaged<BN, kStoreF32>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
+                    drainAccumulatorStaged<BN, kStoreF32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, g.debugEpi);
                 else if (staged && epi.mode == kStoreF16)
-                    drainAccumulatorStaged<BN, kStoreF16>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
+                    drainAccumulatorStaged<BN, kStoreF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, g.debugEpi);
                 else if (staged && epi.mode == kStoreBF16)
-                    drainAccumulatorStaged<BN, kStoreBF16>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group);
+                    drainAccumulatorStaged<BN, kStoreBF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, g.debugEpi);
                 else
                     drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
             }
@@ -622,8 +706,8 @@ EncodeTiledFn encodeTiled() {
 struct DeviceInfo {
     int sms = 0;
     bool sm100 = false;
-    bool attrSet[5] = {};
-    int clusters[5] = {};  // concurrent two-CTA clusters per kernel variant
+    bool attrSet[10] = {};
+    int clusters[10] = {};  // concurrent two-CTA clusters per kernel variant
 };
 
 DeviceInfo& deviceInfo() {
@@ -676,13 +760,13 @@ int ummaKindOf(const Problem& p) {
 
 // How many two-CTA clusters of this kernel the device runs at once (shared memory allows one CTA per SM, and the two
 // CTAs of a cluster must sit in one GPC, so this can fall a little short of half the SM count).
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, bool WIDE>
 cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtensorMap& mapB, const CUtensorMap& mapD, int slot,
                        cudaStream_t stream) {
-    using Plan = SmemPlan<BN, PAIR>;
+    using Plan = SmemPlan<BN, PAIR, WIDE>;
     DeviceInfo& d = deviceInfo();
     if (!d.attrSet[slot]) {
-        if (cudaError_t e = cudaFuncSetAttribute(ummaGemmKernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kDynamicBytes);
+        if (cudaError_t e = cudaFuncSetAttribute(ummaGemmKernel<BN, PAIR, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kDynamicBytes);
             e != cudaSuccess)
             return e;
         if (PAIR) {
@@ -693,7 +777,7 @@ cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtenso
             attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
             probe.attrs = &attr, probe.numAttrs = 1;
             int clusters = 0;
-            if (cudaOccupancyMaxActiveClusters(&clusters, ummaGemmKernel<BN, PAIR>, &probe) != cudaSuccess || clusters < 1) {
+            if (cudaOccupancyMaxActiveClusters(&clusters, ummaGemmKernel<BN, PAIR, WIDE>, &probe) != cudaSuccess || clusters < 1) {
                 cudaGetLastError();
                 clusters = d.sms / 2;
             }
@@ -704,7 +788,7 @@ cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtenso
     countLaunch();
     if (!PAIR) {
         const unsigned grid = unsigned(std::min<long long>(g.totalTiles, d.sms));
-        ummaGemmKernel<BN, PAIR><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(g, mapA, mapB, mapD);
+        ummaGemmKernel<BN, PAIR, WIDE><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(g, mapA, mapB, mapD);
         return cudaGetLastError();
     }
     cudaLaunchConfig_t config{};
@@ -716,7 +800,7 @@ cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtenso
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
     config.attrs = &attr, config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, ummaGemmKernel<BN, PAIR>, g, mapA, mapB, mapD);
+    return cudaLaunchKernelEx(&config, ummaGemmKernel<BN, PAIR, WIDE>, g, mapA, mapB, mapD);
 }
 
 int pairClusters() {  // before the first launch has asked the device: half the SMs
@@ -759,15 +843,20 @@ cudaError_t launchUmma(const Problem& p) {
             if (p.transB && ctaB % mnBoxElems != 0) continue;  // int8 B^T: a box holds 128 columns
             const long long units = (long long)((p.m + (usePair ? 255 : 127)) / (usePair ? 256 : 128)) * ((p.n + cand - 1) / cand) * p.batch;
             const long long slots = usePair ? pairClusters() : d.sms;
-            const long long cost = (units + slots - 1) / slots * (kBM + ctaB);
+            // plus a fixed cost per tile, in k slices: filling the pipeline and the accumulator hand-over (dearer between two CTAs)
+            const long long slicesPerTile = (p.k + kSliceBytes / es - 1) / (kSliceBytes / es) + (usePair ? 6 : 3);
+            const long long cost = (units + slots - 1) / slots * slicesPerTile * (kBM + ctaB);
             if (best < 0 || cost < best) best = cost, bn = cand, pair = usePair != 0;
         }
     }
     if (!bn) bn = p.transB && mnBoxElems > 64 ? 128 : 64, pair = false;  // forced values that fit nothing: smallest legal tile
     const int tilesM = (p.m + (pair ? 255 : 127)) / (pair ? 256 : 128);
     static const int skipStore = [] { const char* v = std::getenv("VKZB_UMMA_SKIP_STORE"); return v ? std::atoi(v) : 0; }();
+    static const int forcedWide = [] { const char* v = std::getenv("VKZB_UMMA_WIDE"); return v ? std::atoi(v) : -1; }();
     static const int debugBits = [] { const char* v = std::getenv("VKZB_UMMA_DEBUG"); return v ? std::atoi(v) : 0; }();
 
+    // few k slices per tile: the launch is bound by writing D, so it takes the variant with more epilogue buffers
+    const bool wide = forcedWide >= 0 ? forcedWide != 0 : (p.k + kSliceBytes / es - 1) / (kSliceBytes / es) <= 16;
     UmmaArgs g{};
     g.m = p.m, g.n = p.n, g.k = p.k, g.batch = p.batch;
     g.tilesM = tilesM, g.tilesN = (p.n + bn - 1) / bn;
@@ -800,6 +889,7 @@ cudaError_t launchUmma(const Problem& p) {
     g.epi = p.epi;
     g.debugSkipStore = skipStore || (debugBits & 1);
     g.debugSkipLoad = (debugBits & 2) != 0, g.debugSkipMma = (debugBits & 4) != 0;
+    g.debugEpi = (debugBits >> 5) & 7;
 
     CUtensorMap mapA, mapB;
     const long long batchA = g.batchMulA ? p.batch : 1, batchB = g.batchMulB ? p.batch : 1;
@@ -833,12 +923,18 @@ cudaError_t launchUmma(const Problem& p) {
 
     static const bool logChoice = [] { const char* v = std::getenv("VKZB_LOG"); return v && !std::strcmp(v, "debug"); }();
     if (logChoice)
-        std::fprintf(stderr, "vkzb: umma tile %d x %d%s, %lld tiles, %d k slices, %s store\n", pair ? 256 : 128, bn, pair ? " (two-CTA pairs)" : "",
+        std::fprintf(stderr, "vkzb: umma tile %d x %d%s, %lld tiles, %d k slices, %s store\n", pair ? 256 : 128, bn, pair ? (wide ? " (two-CTA pairs, wide epilogue)" : " (two-CTA pairs)") : (wide ? " (wide epilogue)" : ""),
                      g.totalTiles, g.numKSlices, g.tmaStore ? "TMA" : "direct");
-    if (pair) return bn == 256 ? launchWith<256, true>(g, mapA, mapB, mapD, 3, p.stream) : launchWith<128, true>(g, mapA, mapB, mapD, 4, p.stream);
-    if (bn == 256) return launchWith<256, false>(g, mapA, mapB, mapD, 0, p.stream);
-    if (bn == 128) return launchWith<128, false>(g, mapA, mapB, mapD, 1, p.stream);
-    return launchWith<64, false>(g, mapA, mapB, mapD, 2, p.stream);
+    if (wide) {
+        if (pair) return bn == 256 ? launchWith<256, true, true>(g, mapA, mapB, mapD, 8, p.stream) : launchWith<128, true, true>(g, mapA, mapB, mapD, 9, p.stream);
+        if (bn == 256) return launchWith<256, false, true>(g, mapA, mapB, mapD, 5, p.stream);
+        if (bn == 128) return launchWith<128, false, true>(g, mapA, mapB, mapD, 6, p.stream);
+        return launchWith<64, false, true>(g, mapA, mapB, mapD, 7, p.stream);
+    }
+    if (pair) return bn == 256 ? launchWith<256, true, false>(g, mapA, mapB, mapD, 3, p.stream) : launchWith<128, true, false>(g, mapA, mapB, mapD, 4, p.stream);
+    if (bn == 256) return launchWith<256, false, false>(g, mapA, mapB, mapD, 0, p.stream);
+    if (bn == 128) return launchWith<128, false, false>(g, mapA, mapB, mapD, 1, p.stream);
+    return launchWith<64, false, false>(g, mapA, mapB, mapD, 2, p.stream);
 }
 
 int ummaDeviceStatus() {
