@@ -7,47 +7,56 @@ from pathlib import Path
 
 import pytest
 
-from vulkanizer_b200.multi_gpu_bench import column_chunks, pick_width
+from vulkanizer_b200.multi_gpu_bench import column_chunks, round_widths
 
 ROOT = Path(__file__).resolve().parents[1]
 
 
-@pytest.mark.parametrize("n, ranks", [(32768, 1), (32768, 2), (32768, 4), (32768, 8), (8192, 2)])
+@pytest.mark.parametrize("n, ranks", [(32768, 1), (32768, 2), (32768, 4), (32768, 8), (8192, 2), (8192, 8), (4096, 4)])
 def test_partition_covers_every_column_once_in_gather_order(n, ranks):
-    width = pick_width(n, ranks)
-    rounds = column_chunks(n, ranks, width)
-    seen = []
-    for j, round_first, firsts in rounds:
-        assert round_first == j * ranks * width
+    rounds = column_chunks(n, ranks)
+    covered = []
+    expect_first = 0
+    for j, w, round_first, firsts in rounds:
+        assert round_first == expect_first and w % 256 == 0
         # ncclAllGather puts rank r's block at offset r * count: the chunks of a round must lie in rank order, side by side
-        assert firsts == [round_first + r * width for r in range(ranks)]
-        seen += [c for f in firsts for c in range(f, f + width, width)]
-    assert sorted(seen) == list(range(0, n, width))
-    assert len(rounds) >= 4 or width == 256
+        assert firsts == [round_first + r * w for r in range(ranks)]
+        covered += [(f, f + w) for f in firsts]
+        expect_first += ranks * w
+    assert expect_first == n
+    covered.sort()
+    assert covered[0][0] == 0 and all(a[1] == b[0] for a, b in zip(covered, covered[1:])) and covered[-1][1] == n
+    per_rank = [sum(w for _, w, _, _ in rounds)] * ranks
+    assert sum(per_rank) == n
+
+
+def test_last_rounds_shrink_so_little_of_the_gather_is_exposed():
+    widths = round_widths(32768, 8)
+    assert widths == [2048, 1024, 512, 256, 256] and sum(widths) * 8 == 32768
+    assert round_widths(32768, 1) == [2048] * 16
 
 
 def test_uneven_split_is_refused():
     with pytest.raises(AssertionError):
-        column_chunks(1000, 3, 256)
+        column_chunks(1000, 3)
 
 
 WORKER = r'''
 import os, sys, hashlib
 sys.path.insert(0, sys.argv[1])
 import torch.distributed as dist
-from vulkanizer_b200.multi_gpu_bench import column_chunks, pick_width
+from vulkanizer_b200.multi_gpu_bench import column_chunks, round_widths
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 dist.init_process_group("gloo", rank=rank, world_size=world)
 box = [bytes(range(128)) if rank == 0 else None]          # stands in for ncclGetUniqueId on rank 0
 dist.broadcast_object_list(box, src=0)
 assert box[0] == bytes(range(128))
-rounds = column_chunks(8192, world, pick_width(8192, world))
-mine = [firsts[rank] for _, _, firsts in rounds]
+rounds = column_chunks(8192, world)
+mine = [(firsts[rank], w) for _, w, _, firsts in rounds]
 gathered = [None] * world
 dist.all_gather_object(gathered, mine)
 flat = sorted(c for part in gathered for c in part)
-assert flat == list(range(0, 8192, pick_width(8192, world))), flat
-assert all(set(gathered[a]).isdisjoint(gathered[b]) for a in range(world) for b in range(a))
+assert flat[0][0] == 0 and all(a[0] + a[1] == b[0] for a, b in zip(flat, flat[1:])) and flat[-1][0] + flat[-1][1] == 8192, flat
 dist.barrier()
 dist.destroy_process_group()
 print("rank", rank, "ok")

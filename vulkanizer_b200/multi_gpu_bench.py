@@ -20,18 +20,34 @@ import statistics
 import time
 
 
-def column_chunks(n: int, ranks: int, width: int):
-    """Rounds of `ranks` chunks of `width` columns: [(round, first column of the round, first column of chunk of rank r for r in ranks)]."""
-    assert n % (ranks * width) == 0, "the column count must be a multiple of ranks x chunk width"
-    return [(j, j * ranks * width, [(j * ranks + r) * width for r in range(ranks)]) for j in range(n // (ranks * width))]
+def round_widths(n: int, ranks: int):
+    """Chunk widths (columns per rank) of the successive rounds. Wide chunks first: 2048 columns are 1024 tile pairs of
+    256 x 256, 13.8 waves over 74 CTA pairs, so almost no SM idles at the end of a chunk. The last rounds shrink
+    (1024, 512, 256, 256) because the gather of the final round cannot hide behind a product: the smaller it is, the less
+    of it is exposed at the end of the step."""
+    per_rank = n // ranks
+    assert n % ranks == 0 and per_rank % 256 == 0, "the column count must be a multiple of 256 x ranks"
+    if ranks == 1:
+        return [min(2048, per_rank)] * (per_rank // min(2048, per_rank))
+    tail = [1024, 512, 256, 256]
+    if per_rank < sum(tail) or (per_rank - sum(tail)) % 2048:
+        width = 256
+        while width * 2 <= per_rank // 4 and per_rank % (width * 2) == 0 and width < 1024:
+            width *= 2
+        return [width] * (per_rank // width)
+    return [2048] * ((per_rank - sum(tail)) // 2048) + tail
 
 
-def pick_width(n: int, ranks: int) -> int:
-    """1024 columns fill the 148 SMs almost evenly (1024 tiles of 128 x 256 = 6.9 waves); smaller when that leaves under four rounds."""
-    width = 1024
-    while width > 256 and n // (ranks * width) < 4:
-        width //= 2
-    return width
+def column_chunks(n: int, ranks: int, widths=None):
+    """Rounds of `ranks` chunks side by side: [(round, width, first column of the round, [first column of rank r's chunk])].
+    Chunk c of a round belongs to rank c, so the round's columns lie in rank order, the layout ncclAllGather produces."""
+    widths = widths or round_widths(n, ranks)
+    assert sum(widths) * ranks == n, "the rounds must cover every column exactly once"
+    rounds, first = [], 0
+    for j, w in enumerate(widths):
+        rounds.append((j, w, first, [first + r * w for r in range(ranks)]))
+        first += ranks * w
+    return rounds
 
 
 def run(args):
@@ -52,8 +68,8 @@ def run(args):
 
     size = int(os.environ.get("VKZB_BENCH_SIZE", "32768"))
     m = n = k = size
-    width = pick_width(n, world)
-    rounds = column_chunks(n, world, width)
+    rounds = column_chunks(n, world)
+    mine_cols = sum(w for _, w, _, _ in rounds)  # columns this rank computes
 
     # the communicator id travels through the process group
     box = [capi.NcclComm.unique_id() if rank == 0 else None]
@@ -68,10 +84,15 @@ def run(args):
     for first in range(0, m * k, step_elems):
         cnt = min(step_elems, m * k - first)
         A[first:first + cnt] = torch.randn(cnt, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
-    Bmine = torch.empty(len(rounds) * width * k, dtype=torch.bfloat16, device="cuda")  # the rank's chunks, one after another
-    for j, _, firsts in rounds:
-        gen.manual_seed(5 * 100003 + firsts[rank] // width)
-        Bmine[j * width * k:(j + 1) * width * k] = torch.randn(width * k, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    Bmine = torch.empty(mine_cols * k, dtype=torch.bfloat16, device="cuda")  # the rank's chunks, one after another
+    b_offset = []  # element offset of round j's chunk inside Bmine
+    off = 0
+    for j, w, _, firsts in rounds:
+        b_offset.append(off)
+        for c0 in range(0, w, 256):  # every 256-column block of B has its own seed, whatever the chunking
+            gen.manual_seed(5 * 100003 + (firsts[rank] + c0) // 256)
+            Bmine[off + c0 * k:off + (c0 + 256) * k] = torch.randn(256 * k, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        off += w * k
     D = torch.zeros(m * n, dtype=torch.float32, device="cuda")  # column-major m x n, ldd = m: 4 GiB at full size
 
     lt = capi.CublasLt()
@@ -80,14 +101,14 @@ def run(args):
     events = [torch.cuda.Event() for _ in rounds]
 
     def step():
-        for j, round_first, firsts in rounds:
+        for j, w, round_first, firsts in rounds:
             mine = D.data_ptr() + 4 * firsts[rank] * m
-            lt.matmul(capi.OP_T, capi.OP_N, m, width, k, 1.0, A.data_ptr(), bf16, k, Bmine.data_ptr() + 2 * j * width * k, bf16, k, 0.0,
+            lt.matmul(capi.OP_T, capi.OP_N, m, w, k, 1.0, A.data_ptr(), bf16, k, Bmine.data_ptr() + 2 * b_offset[j], bf16, k, 0.0,
                       mine, f32, m, mine, f32, m, stream=compute.cuda_stream)
             if world > 1:
                 events[j].record(compute)
                 gather.wait_event(events[j])
-                comm.all_gather(mine, D.data_ptr() + 4 * round_first * m, width * m, "float32", gather.cuda_stream)
+                comm.all_gather(mine, D.data_ptr() + 4 * round_first * m, w * m, "float32", gather.cuda_stream)
         if world > 1:
             compute.wait_stream(gather)  # the step ends when every rank's columns have arrived
 
@@ -119,9 +140,9 @@ def run(args):
     check_ok = True
     if world > 1:
         other = (rank + 1) % world
-        j, _, firsts = rounds[-1]
-        gen.manual_seed(5 * 100003 + firsts[other] // width)
-        Bother = torch.randn(width * k, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16).view(width, k)
+        j, w, _, firsts = rounds[-1]
+        gen.manual_seed(5 * 100003 + firsts[other] // 256)
+        Bother = torch.randn(256 * k, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16).view(256, k)
         rows = torch.arange(0, m, 997, device="cuda")
         want = (A.view(m, k)[rows].float() @ Bother[:8].float().T)  # (rows, 8 columns)
         got = D.view(n, m)[firsts[other]:firsts[other] + 8][:, rows].T
@@ -133,7 +154,7 @@ def run(args):
     # end to end: the rank's inputs come from pinned host memory, its own columns of D go back
     hostA = torch.empty(m * k, dtype=torch.bfloat16).pin_memory()
     hostB = torch.empty(Bmine.numel(), dtype=torch.bfloat16).pin_memory()
-    hostD = torch.empty(len(rounds) * width * m, dtype=torch.float32).pin_memory()
+    hostD = torch.empty(mine_cols * m, dtype=torch.float32).pin_memory()
     hostA.copy_(A)
     hostB.copy_(Bmine)
     e2e_steps = 2
@@ -144,8 +165,8 @@ def run(args):
             Bmine.copy_(hostB, non_blocking=True)
         step()
         with torch.cuda.stream(compute):
-            for j, _, firsts in rounds:
-                hostD[j * width * m:(j + 1) * width * m].copy_(D[firsts[rank] * m:(firsts[rank] + width) * m], non_blocking=True)
+            for j, w, _, firsts in rounds:
+                hostD[b_offset[j] // k * m:(b_offset[j] // k + w) * m].copy_(D[firsts[rank] * m:(firsts[rank] + w) * m], non_blocking=True)
 
     step_e2e()
     torch.cuda.synchronize()
@@ -170,7 +191,7 @@ def run(args):
             "data": "synthetic",
             "config": {"workload": "cfg5b_bf16_32768_nsharded", "call": "cublasLtMatmul + ncclAllGather", "opA": "T", "opB": "N", "m": m, "n": n,
                        "k": k, "a_b_type": "bf16", "c_type": "f32", "alpha": 1, "beta": 0, "seed": 5, "parallelism": f"n-sharded x{world}",
-                       "chunk_columns": width, "rounds": len(rounds),
+                       "chunk_columns": [w for _, w, _, _ in rounds], "rounds": len(rounds),
                        "l2": "operands of one step hold 8 GiB > L2, no flush", "timing": "CUDA events on the compute stream, maximum over ranks"},
             "roofline": {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak, "traffic": None,
                          "peak_source": f"{peak_kind}: cuBLAS bf16 sustained x {world} GPUs (the step is a long loop of GEMMs)",
