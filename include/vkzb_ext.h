@@ -7,6 +7,7 @@
 #ifndef VKZB_EXT_H
 #define VKZB_EXT_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -34,6 +35,19 @@ int vkzbLastPath(void);
  * the word with a blocking copy, so call it after synchronising the stream. Returns -1 on a CUDA error.
  */
 int vkzbDeviceStatus(void);
+
+/*
+ * Output mirrors: after this call every GEMM issued through `handle` (cuBLAS or cuBLASLt entry point) whose result matrix
+ * lies inside [localBase, localBase + bytes) writes each tile of the result, as it is produced, to the same offset in
+ * `count` other buffers as well (at most 7). With the buffers being the other GPUs' copies of the matrix (addresses from
+ * vkzbNcclExchangeBuffer of this repository's libnccl.so.2) an N-sharded GEMM leaves the whole matrix on every GPU without
+ * a separate all-gather: the NVLink traffic is spread over the GEMM instead of following it.
+ * Only the tensor-core kernel with bulk (TMA) stores can do this: D, every mirror, the leading dimension and the column
+ * length must be multiples of 16 bytes. A call that cannot honour the mirrors answers CUBLAS_STATUS_NOT_SUPPORTED instead
+ * of skipping them. count = 0 switches mirroring off. The caller orders the ranks around the GEMM (vkzbNcclBarrier).
+ * Exported by libcublas.so.12 and libcublasLt.so.12 alike (a handle belongs to the library that created it).
+ */
+int vkzbSetOutputMirrors(void* handle, const void* localBase, size_t bytes, int count, void* const* mirrorBases);
 
 #ifdef __cplusplus
 }

@@ -90,6 +90,15 @@ ncclResult_t ncclGather(const void* sendbuff, void* recvbuff, size_t count, nccl
 ncclResult_t ncclGroupStart(void);                                                                  /* nccl.cpp:717 */
 ncclResult_t ncclGroupEnd(void);                                                                    /* nccl.cpp:723 */
 
+/* ---- extensions: no counterpart in the reference. They let a GEMM write its result tiles straight into every rank's copy
+ * of the matrix (vkzbSetOutputMirrors in vkzb_ext.h), which removes the separate gather altogether. ---- */
+/* Collective, blocking on the host, touches no stream: each rank hands in one cudaMalloc'ed buffer; peers[r] receives an
+ * address through which this process reaches rank r's buffer (peers[own rank] = buffer). Valid until the communicator goes. */
+ncclResult_t vkzbNcclExchangeBuffer(ncclComm_t comm, void* buffer, void** peers);
+/* A barrier across the ranks, asynchronous on `stream`: later work on any rank's stream starts only after every rank's
+ * stream has reached its barrier (so every earlier write into peer memory has landed). */
+ncclResult_t vkzbNcclBarrier(ncclComm_t comm, cudaStream_t stream);
+
 /* Not served yet, answering ncclInvalidUsage like the reference's stubs (src/nccl/nccl_stubs.cpp:30-36): ncclSend, ncclRecv,
  * ncclCommSplit, ncclCommInitRankScalable, ncclRedOpCreatePreMulSum, ncclRedOpDestroy, ncclGroupSimulateEnd and the 17 names
  * of nccl_stubs.cpp:11-27. */

@@ -107,6 +107,36 @@ def main():
             comm.all_gather(src.data_ptr(), dst.data_ptr(), big, "float32", s)
         stream.synchronize()
         assert torch.equal(dst.view(nranks, big)[:, ::4096].cpu(), torch.arange(1, nranks + 1, dtype=torch.float32)[:, None].expand(nranks, big // 4096))
+    # a GEMM whose tiles are written to every rank's copy of D as they are produced (output mirrors): rank r computes
+    # columns [r * w, (r + 1) * w) of D = A^T B, and afterwards every rank holds all of D
+    from oracle import pyoracle as orc
+    m, k, w = 384, 192, 256
+    lt = capi.CublasLt()
+    A, av = orc.fill_lcg("f16", m * k, 1)
+    Bfull, bv = orc.fill_lcg("f16", k * w * nranks, 2)
+    dA = torch.from_numpy(A.view(np.int16)).cuda()
+    dB = torch.from_numpy(Bfull.view(np.int16)).cuda()
+    D = torch.full((m * w * nranks,), -1.0, device="cuda")
+    peers = comm.exchange_buffer(D.data_ptr())
+    lt.set_output_mirrors(D.data_ptr(), D.numel() * 4, [peers[p] for p in range(nranks) if p != rank])
+    with torch.cuda.stream(stream):
+        comm.barrier(s)
+        mine = D.data_ptr() + 4 * rank * w * m
+        lt.matmul(capi.OP_T, capi.OP_N, m, w, k, 1.0, dA.data_ptr(), capi.CUDA_R_16F, k, dB.data_ptr() + 2 * rank * w * k, capi.CUDA_R_16F, k, 0.0,
+                  mine, capi.CUDA_R_32F, m, mine, capi.CUDA_R_32F, m, stream=s)
+        comm.barrier(s)
+        stream.synchronize()
+    want = (av.reshape(m, k).astype(np.float64) @ bv.reshape(w * nranks, k).astype(np.float64).T).T  # [col, row]
+    assert np.allclose(D.cpu().numpy().reshape(w * nranks, m), want, atol=1e-3), "mirrored tiles did not arrive on every rank"
+    # a result the bulk stores cannot write (column length not a multiple of 16 bytes) must be refused, not silently left unmirrored
+    status = lt.matmul(capi.OP_T, capi.OP_N, m - 2, w, k, 1.0, dA.data_ptr(), capi.CUDA_R_16F, k, dB.data_ptr(), capi.CUDA_R_16F, k, 0.0,
+                       mine, capi.CUDA_R_32F, m, mine, capi.CUDA_R_32F, m, stream=s, check=False)
+    assert status == (capi.STATUS_NOT_SUPPORTED if nranks > 1 else capi.STATUS_SUCCESS), status
+    lt.set_output_mirrors(0, 0, [])
+    torch.cuda.synchronize()
+    comm.barrier(s)
+    torch.cuda.synchronize()
+    lt.destroy()
     assert comm.async_error() == 0
     comm.destroy()
     print(f"rank {rank} ok", flush=True)

@@ -30,10 +30,11 @@ def test_partition_covers_every_column_once_in_gather_order(n, ranks):
     assert sum(per_rank) == n
 
 
-def test_last_rounds_shrink_so_little_of_the_gather_is_exposed():
-    widths = round_widths(32768, 8)
-    assert widths == [2048, 1024, 512, 256, 256] and sum(widths) * 8 == 32768
+def test_rounds_are_uniform_so_each_gather_hides_behind_the_next_product():
+    assert round_widths(32768, 8) == [1024] * 4
+    assert round_widths(32768, 2) == [1024] * 16
     assert round_widths(32768, 1) == [2048] * 16
+    assert round_widths(8192, 8) == [256] * 4
 
 
 def test_uneven_split_is_refused():

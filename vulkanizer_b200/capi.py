@@ -107,6 +107,7 @@ def cublas_library() -> C.CDLL:
         lib.vkzbLaunchCount.argtypes, lib.vkzbLaunchCount.restype = [], C.c_uint64
         lib.vkzbLastPath.argtypes, lib.vkzbLastPath.restype = [], _i
         lib.vkzbDeviceStatus.argtypes, lib.vkzbDeviceStatus.restype = [], _i
+        lib.vkzbSetOutputMirrors.argtypes, lib.vkzbSetOutputMirrors.restype = [_vp, _vp, _sz, _i, C.POINTER(_vp)], _i
         _cublas = lib
     return _cublas
 
@@ -139,6 +140,7 @@ def cublaslt_library() -> C.CDLL:
         lib.vkzbLaunchCount.argtypes, lib.vkzbLaunchCount.restype = [], C.c_uint64
         lib.vkzbLastPath.argtypes, lib.vkzbLastPath.restype = [], _i
         lib.vkzbDeviceStatus.argtypes, lib.vkzbDeviceStatus.restype = [], _i
+        lib.vkzbSetOutputMirrors.argtypes, lib.vkzbSetOutputMirrors.restype = [_vp, _vp, _sz, _i, C.POINTER(_vp)], _i
         _cublaslt = lib
     return _cublaslt
 
@@ -177,6 +179,8 @@ def nccl_library() -> C.CDLL:
             "ncclAlltoAll": coll + [_vp, _vp],
             "ncclGroupStart": [],
             "ncclGroupEnd": [],
+            "vkzbNcclExchangeBuffer": [_vp, _vp, C.POINTER(_vp)],
+            "vkzbNcclBarrier": [_vp, _vp],
         }
         for name, args in protos.items():
             fn = getattr(lib, name)
@@ -236,6 +240,15 @@ class NcclComm:
 
     def all_to_all(self, send, recv, count, dtype, stream=0):
         self._check("ncclAlltoAll", self.lib.ncclAlltoAll(send, recv, count, NCCL_TYPES[dtype], self.comm, stream), self.comm)
+
+    def exchange_buffer(self, ptr: int) -> list[int]:
+        """Addresses through which this process reaches each rank's buffer (extension vkzbNcclExchangeBuffer)."""
+        out = (_vp * self.nranks)()
+        self._check("vkzbNcclExchangeBuffer", self.lib.vkzbNcclExchangeBuffer(self.comm, ptr, out), self.comm)
+        return [int(out[i] or 0) for i in range(self.nranks)]
+
+    def barrier(self, stream=0):
+        self._check("vkzbNcclBarrier", self.lib.vkzbNcclBarrier(self.comm, stream), self.comm)
 
     def async_error(self) -> int:
         out = _i(0)
@@ -346,6 +359,14 @@ class Cublas:
     def launch_count(self) -> int:
         return self.lib.vkzbLaunchCount()
 
+    def set_output_mirrors(self, local_base: int, nbytes: int, mirrors: list[int]):
+        """Every later GEMM on this handle whose result lies in [local_base, local_base + nbytes) also writes it, tile by
+        tile, to the same offset in the `mirrors` buffers (extension vkzbSetOutputMirrors); an empty list switches it off."""
+        arr = (_vp * max(1, len(mirrors)))(*mirrors)
+        status = self.lib.vkzbSetOutputMirrors(self.handle, local_base, nbytes, len(mirrors), arr)
+        if status:
+            raise BlasError("vkzbSetOutputMirrors", status)
+
     def device_status(self) -> int:
         return self.lib.vkzbDeviceStatus()
 
@@ -424,3 +445,11 @@ class CublasLt:
 
     def launch_count(self) -> int:
         return self.lib.vkzbLaunchCount()
+
+    def set_output_mirrors(self, local_base: int, nbytes: int, mirrors: list[int]):
+        """Every later GEMM on this handle whose result lies in [local_base, local_base + nbytes) also writes it, tile by
+        tile, to the same offset in the `mirrors` buffers (extension vkzbSetOutputMirrors); an empty list switches it off."""
+        arr = (_vp * max(1, len(mirrors)))(*mirrors)
+        status = self.lib.vkzbSetOutputMirrors(self.handle, local_base, nbytes, len(mirrors), arr)
+        if status:
+            raise BlasError("vkzbSetOutputMirrors", status)

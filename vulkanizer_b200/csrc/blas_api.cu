@@ -132,6 +132,16 @@ static int accumulatorFor(int ta, int tb, int tc, cublasComputeType_t compute) {
 // Picks the kernel family and launches. `p` is complete except for the stream.
 cublasStatus_t dispatch(cublasHandle_t h, Problem& p) {
     p.stream = h->stream;
+    p.mirrorCount = 0;
+    if (h->mirrorCount > 0 && !p.epi.pointerArrays) {
+        const char* d = static_cast<const char*>(p.epi.D);
+        if (d >= h->mirrorLocal && d < h->mirrorLocal + h->mirrorBytes) {
+            p.mirrorCount = h->mirrorCount;
+            for (int i = 0; i < h->mirrorCount; ++i) p.mirrorD[i] = h->mirrorBase[i] + (d - h->mirrorLocal);
+            // only the tensor-core kernel with bulk stores can write mirrors; anything else must say so
+            if (p.k == 0 || p.n == 1 || p.m == 1 || forcedPath() != 0 || !ummaEligible(p) || !ummaCanMirror(p)) return CUBLAS_STATUS_NOT_SUPPORTED;
+        }
+    }
     int path;
     cudaError_t err;
     if (p.k == 0) {
@@ -541,6 +551,19 @@ cublasStatus_t cublasSgemv_v2_64(cublasHandle_t h, cublasOperation_t trans, int6
 uint64_t vkzbLaunchCount(void) { return g_launches.load(std::memory_order_relaxed); }
 int vkzbLastPath(void) { return t_lastPath; }
 int vkzbDeviceStatus(void) { return ummaDeviceStatus(); }
+
+int vkzbSetOutputMirrors(void* handle, const void* localBase, size_t bytes, int count, void* const* mirrorBases) {
+    auto* h = static_cast<cublasContext*>(handle);
+    if (!h) return CUBLAS_STATUS_NOT_INITIALIZED;
+    if (count < 0 || count > kMaxMirrors || (count > 0 && (!localBase || !mirrorBases || !bytes))) return CUBLAS_STATUS_INVALID_VALUE;
+    for (int i = 0; i < count; ++i)
+        if (!mirrorBases[i]) return CUBLAS_STATUS_INVALID_VALUE;
+    h->mirrorCount = count;
+    h->mirrorLocal = static_cast<const char*>(localBase);
+    h->mirrorBytes = bytes;
+    for (int i = 0; i < count; ++i) h->mirrorBase[i] = static_cast<char*>(mirrorBases[i]);
+    return CUBLAS_STATUS_SUCCESS;
+}
 
 }  // extern "C"
 #pragma GCC visibility pop

@@ -15,6 +15,11 @@ struct cublasContext {
     int device = 0;
     void* workspace = nullptr;
     size_t workspaceBytes = 0;
+    // output mirrors (vkzbSetOutputMirrors): results inside [mirrorLocal, mirrorLocal + mirrorBytes) are also written there
+    const char* mirrorLocal = nullptr;
+    size_t mirrorBytes = 0;
+    int mirrorCount = 0;
+    char* mirrorBase[vkzb::kMaxMirrors] = {};
 };
 
 namespace vkzb {

@@ -18,6 +18,8 @@ enum ScalarType : int { kScalarF32 = 0, kScalarF16 = 1, kScalarS32 = 2, kScalarF
 
 enum Activation : int { kActNone = 0, kActRelu = 1, kActGelu = 2 };
 
+constexpr int kMaxMirrors = 7;  // other buffers a result can be written to as well (the other GPUs of an 8-GPU box)
+
 __host__ __device__ inline int dtypeSize(int t) {
     return t == kF32 || t == kS32 ? 4 : t == kF64 ? 8 : t == kS8 ? 1 : 2;
 }
@@ -60,6 +62,8 @@ struct Problem {
     int accType = kF32;          // kF32, kS32 or kF64: the accumulator
     bool allowTf32 = false;      // handle asked for CUBLAS_TF32_TENSOR_OP_MATH or compute type FAST_TF32
     EpilogueArgs epi{};
+    int mirrorCount = 0;              // D is also written to these addresses (same layout), tile by tile
+    void* mirrorD[kMaxMirrors] = {};
     cudaStream_t stream = nullptr;
 };
 
@@ -70,6 +74,7 @@ cudaError_t launchGemv(const Problem& p);     // m = 1 or n = 1
 bool sgemmEligible(const Problem& p);
 cudaError_t launchSgemm(const Problem& p);    // fp32 FFMA
 bool ummaEligible(const Problem& p);
+bool ummaCanMirror(const Problem& p);          // D and the mirrors can be written with bulk stores
 cudaError_t launchUmma(const Problem& p);     // tcgen05 tensor cores
 int ummaDeviceStatus();
 

@@ -55,6 +55,11 @@ enum : unsigned { kStatusOk = 0, kStatusProducerWait = 1, kStatusMmaFullWait = 2
 
 __device__ unsigned g_ummaStatus;
 
+// Tensor maps of the buffers that receive a copy of every D tile (same shape and strides as D's map).
+struct MirrorMaps {
+    CUtensorMap map[kMaxMirrors];
+};
+
 struct UmmaArgs {
     int m, n, k, batch;
     int tilesM, tilesN, groupM;
@@ -75,6 +80,7 @@ struct UmmaArgs {
     int debugSkipLoad, debugSkipMma;  // measurement aids: main loop without its TMA loads / without its MMAs
     int debugEpi;                    // measurement aids for the staged epilogue: 1 no bulk store, 2 no shared-memory writes, 4 no fence
     int tmaStore;                   // D is 16-byte aligned in every dimension: results leave through shared memory and TMA
+    int mirrorCount;                // every bulk store of D is repeated into this many other buffers (peer GPUs)
     EpilogueArgs epi;
 };
 
@@ -142,13 +148,14 @@ __device__ __forceinline__ void tmaLoad3d(unsigned dst, const CUtensorMap* map, 
         : "memory");
 }
 
-// Shared memory -> global, asynchronous; elements outside the tensor are clipped by the hardware.
-__device__ __forceinline__ void tmaStore3d(const CUtensorMap* map, unsigned src, int c0, int c1, int c2) {
+// Shared memory -> global, asynchronous; elements outside the tensor are clipped by the hardware. The destination may be
+// this GPU's memory or a peer's (the copy then travels over NVLink).
+__device__ __forceinline__ void tmaStore3dIssue(const CUtensorMap* map, unsigned src, int c0, int c1, int c2) {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
                  ::"l"(reinterpret_cast<unsigned long long>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
                  : "memory");
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+__device__ __forceinline__ void tmaStoreCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Until at most `Pending` of this thread's bulk stores are still reading their shared-memory source.
 template <int Pending>
 __device__ __forceinline__ void tmaStoreWaitRead() {
@@ -335,8 +342,8 @@ __device__ __forceinline__ void drainAccumulator(const Epilogue<Acc>& epi, unsig
 // One staged step: 16 columns of this warp's rows, already in registers, through a shared-memory buffer to a bulk store.
 template <int MODE, int NB, typename Acc>
 __device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const unsigned (&v)[kStoreCols], int rowInTile, int row, bool rowOk,
-                                              int row0, int col, int count, int batchEntry, const CUtensorMap* mapD, unsigned char* staging,
-                                              unsigned& step, bool issuer, int group, int dbg) {
+                                              int row0, int col, int count, int batchEntry, const CUtensorMap* mapD, const MirrorMaps* mirrors,
+                                              int mirrorCount, unsigned char* staging, unsigned& step, bool issuer, int group, int dbg) {
     using Elem = std::conditional_t<MODE == kStoreF32, float, std::conditional_t<MODE == kStoreS32, int,
                  std::conditional_t<MODE == kStoreF16, __half, __nv_bfloat16>>>;
     const Acc alpha = epi.alpha, beta = epi.beta;
@@ -373,7 +380,10 @@ __device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const un
     if (!(dbg & 4)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     epilogueBarrier(group);
     if (issuer && !(dbg & 1)) {
-        tmaStore3d(mapD, smemAddr(buf - rowInTile), row0, col, batchEntry);
+        const unsigned src = smemAddr(buf - rowInTile);
+        tmaStore3dIssue(mapD, src, row0, col, batchEntry);
+        for (int q = 0; q < mirrorCount; ++q) tmaStore3dIssue(&mirrors->map[q], src, row0, col, batchEntry);  // the same block to every peer
+        tmaStoreCommit();
         // more buffers: after this step's store is on its way, make sure the buffer of the step AFTER the next one is
         // free; the other warps learn it at the next step's barrier, before they reach that buffer
         if constexpr (NB >= 3) tmaStoreWaitRead<NB - 2>();
@@ -387,7 +397,8 @@ __device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const un
 template <int BN, int MODE, int NB, typename Acc>
 __device__ __forceinline__ void drainAccumulatorStaged(const Epilogue<Acc>& epi, unsigned taddr, int rowInTile, int row, bool rowOk,
                                                        int row0, int col0, int n, int batchEntry, const CUtensorMap* mapD,
-                                                       unsigned char* staging, unsigned& step, bool issuer, int group, int dbg) {
+                                                       const MirrorMaps* mirrors, int mirrorCount, unsigned char* staging, unsigned& step,
+                                                       bool issuer, int group, int dbg) {
     constexpr int kStride = kStoreCols * kEpilogueGroups;  // columns between two steps of one group
     constexpr int kSteps = BN / kStride;                   // steps of one group per tile
     constexpr int kBatch = kSteps < 2 ? kSteps : 2;  // four at a time spill registers and run three times slower
@@ -403,8 +414,8 @@ __device__ __forceinline__ void drainAccumulatorStaged(const Epilogue<Acc>& epi,
         for (int b = 0; b < kBatch; ++b) {
             const int count = n - (col0 + c + b * kStride);
             if (count > 0)
-                stageAndStore<MODE, NB>(epi, v[b], rowInTile, row, rowOk, row0, col0 + c + b * kStride, count, batchEntry, mapD, staging, step, issuer,
-                                        group, dbg);
+                stageAndStore<MODE, NB>(epi, v[b], rowInTile, row, rowOk, row0, col0 + c + b * kStride, count, batchEntry, mapD, mirrors, mirrorCount, staging, step,
+                                        issuer, group, dbg);
         }
     }
 }
@@ -546,7 +557,7 @@ __device__ __forceinline__ void mmaIssuerLoop(const UmmaArgs& g, unsigned smemBa
 template <int BN, bool PAIR, bool WIDE>
 __global__ void __launch_bounds__(kThreads, 1)
 ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-               const __grid_constant__ CUtensorMap mapD) {
+               const __grid_constant__ CUtensorMap mapD, const __grid_constant__ MirrorMaps mirrors) {
     using Plan = SmemPlan<BN, PAIR, WIDE>;
     constexpr int kStages = Plan::kStages;
     extern __shared__ unsigned char smemRaw[];
@@ -645,7 +656,7 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                 Epilogue<int> epi;
                 epi.init(g.epi, t.batch);
                 if (g.tmaStore && epi.mode == kStoreS32 && !g.debugSkipStore)
-                    drainAccumulatorStaged<BN, kStoreS32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, g.debugEpi);
+                    drainAccumulatorStaged<BN, kStoreS32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                 else
                     drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
             } else {
@@ -653,11 +664,11 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                 epi.init(g.epi, t.batch);
                 const bool staged = g.tmaStore && !g.debugSkipStore;
                 if (staged && epi.mode == kStoreF32)
-                    drainAccumulatorStaged<BN, kStoreF32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, g.debugEpi);
+                    drainAccumulatorStaged<BN, kStoreF32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                 else if (staged && epi.mode == kStoreF16)
-                    drainAccumulatorStaged<BN, kStoreF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, g.debugEpi);
+                    drainAccumulatorStaged<BN, kStoreF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                 else if (staged && epi.mode == kStoreBF16)
-                    drainAccumulatorStaged<BN, kStoreBF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, g.debugEpi);
+                    drainAccumulatorStaged<BN, kStoreBF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                 else
                     drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
             }
@@ -761,8 +772,8 @@ int ummaKindOf(const Problem& p) {
 // How many two-CTA clusters of this kernel the device runs at once (shared memory allows one CTA per SM, and the two
 // CTAs of a cluster must sit in one GPC, so this can fall a little short of half the SM count).
 template <int BN, bool PAIR, bool WIDE>
-cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtensorMap& mapB, const CUtensorMap& mapD, int slot,
-                       cudaStream_t stream) {
+cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtensorMap& mapB, const CUtensorMap& mapD, const MirrorMaps& mirrors,
+                       int slot, cudaStream_t stream) {
     using Plan = SmemPlan<BN, PAIR, WIDE>;
     DeviceInfo& d = deviceInfo();
     if (!d.attrSet[slot]) {
@@ -788,7 +799,7 @@ cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtenso
     countLaunch();
     if (!PAIR) {
         const unsigned grid = unsigned(std::min<long long>(g.totalTiles, d.sms));
-        ummaGemmKernel<BN, PAIR, WIDE><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(g, mapA, mapB, mapD);
+        ummaGemmKernel<BN, PAIR, WIDE><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(g, mapA, mapB, mapD, mirrors);
         return cudaGetLastError();
     }
     cudaLaunchConfig_t config{};
@@ -800,7 +811,7 @@ cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtenso
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
     config.attrs = &attr, config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, ummaGemmKernel<BN, PAIR, WIDE>, g, mapA, mapB, mapD);
+    return cudaLaunchKernelEx(&config, ummaGemmKernel<BN, PAIR, WIDE>, g, mapA, mapB, mapD, mirrors);
 }
 
 int pairClusters() {  // before the first launch has asked the device: half the SMs
@@ -818,6 +829,18 @@ bool ummaEligible(const Problem& p) {
                (p.batch == 1 || stride == 0 || (stride * es) % 16 == 0);
     };
     return ok(p.A, p.lda, p.strideA) && ok(p.B, p.ldb, p.strideB);
+}
+
+bool ummaCanMirror(const Problem& p) {
+    const EpilogueArgs& e = p.epi;
+    const int esD = dtypeSize(e.typeD);
+    const auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+    if (e.pointerArrays || !aligned(e.D) || (e.ldd * esD) % 16 != 0 || ((long long)p.m * esD) % 16 != 0) return false;
+    if (p.batch > 1 && (e.strideD == 0 || (e.strideD * esD) % 16 != 0)) return false;
+    if (e.bias || e.activation != kActNone || e.roundBeforeBias || (e.typeC != e.typeD)) return false;  // the staged store forms only
+    for (int q = 0; q < p.mirrorCount; ++q)
+        if (!aligned(p.mirrorD[q])) return false;
+    return true;
 }
 
 cudaError_t launchUmma(const Problem& p) {
@@ -910,31 +933,40 @@ cudaError_t launchUmma(const Problem& p) {
                  (p.batch == 1 || (e.strideD * esD) % 16 == 0) && (p.batch == 1 || e.strideD != 0);
     static const int noTmaStore = [] { const char* v = std::getenv("VKZB_UMMA_DIRECT_STORE"); return v ? std::atoi(v) : 0; }();
     if (noTmaStore) g.tmaStore = 0;
+    MirrorMaps mirrors{};
+    g.mirrorCount = 0;
     if (g.tmaStore) {
         const CUtensorMapDataType dt = e.typeD == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : e.typeD == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                        : e.typeD == kS32 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
         const cuuint64_t dims[3] = {cuuint64_t(p.m), cuuint64_t(p.n), cuuint64_t(p.batch)};
         const cuuint64_t strides[2] = {cuuint64_t(e.ldd) * esD, p.batch > 1 ? cuuint64_t(e.strideD) * esD : cuuint64_t(e.ldd) * esD * cuuint64_t(p.n)};
         const cuuint32_t box[3] = {cuuint32_t(kBM), cuuint32_t(kStoreCols), 1}, ones[3] = {1, 1, 1};
-        if (encodeTiled()(&mapD, dt, 3, e.D, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            g.tmaStore = 0;
+        const auto encode = [&](CUtensorMap* map, void* base) {
+            return encodeTiled()(map, dt, 3, base, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                 CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+        };
+        if (!encode(&mapD, e.D)) g.tmaStore = 0;
+        for (int q = 0; g.tmaStore && q < p.mirrorCount; ++q) {
+            if (!encode(&mirrors.map[q], p.mirrorD[q])) return cudaErrorInvalidValue;
+            g.mirrorCount = q + 1;
+        }
     }
+    if (p.mirrorCount > 0 && g.mirrorCount != p.mirrorCount) return cudaErrorInvalidValue;  // never skip mirrors silently
 
     static const bool logChoice = [] { const char* v = std::getenv("VKZB_LOG"); return v && !std::strcmp(v, "debug"); }();
     if (logChoice)
         std::fprintf(stderr, "vkzb: umma tile %d x %d%s, %lld tiles, %d k slices, %s store\n", pair ? 256 : 128, bn, pair ? (wide ? " (two-CTA pairs, wide epilogue)" : " (two-CTA pairs)") : (wide ? " (wide epilogue)" : ""),
                      g.totalTiles, g.numKSlices, g.tmaStore ? "TMA" : "direct");
     if (wide) {
-        if (pair) return bn == 256 ? launchWith<256, true, true>(g, mapA, mapB, mapD, 8, p.stream) : launchWith<128, true, true>(g, mapA, mapB, mapD, 9, p.stream);
-        if (bn == 256) return launchWith<256, false, true>(g, mapA, mapB, mapD, 5, p.stream);
-        if (bn == 128) return launchWith<128, false, true>(g, mapA, mapB, mapD, 6, p.stream);
-        return launchWith<64, false, true>(g, mapA, mapB, mapD, 7, p.stream);
+        if (pair) return bn == 256 ? launchWith<256, true, true>(g, mapA, mapB, mapD, mirrors, 8, p.stream) : launchWith<128, true, true>(g, mapA, mapB, mapD, mirrors, 9, p.stream);
+        if (bn == 256) return launchWith<256, false, true>(g, mapA, mapB, mapD, mirrors, 5, p.stream);
+        if (bn == 128) return launchWith<128, false, true>(g, mapA, mapB, mapD, mirrors, 6, p.stream);
+        return launchWith<64, false, true>(g, mapA, mapB, mapD, mirrors, 7, p.stream);
     }
-    if (pair) return bn == 256 ? launchWith<256, true, false>(g, mapA, mapB, mapD, 3, p.stream) : launchWith<128, true, false>(g, mapA, mapB, mapD, 4, p.stream);
-    if (bn == 256) return launchWith<256, false, false>(g, mapA, mapB, mapD, 0, p.stream);
-    if (bn == 128) return launchWith<128, false, false>(g, mapA, mapB, mapD, 1, p.stream);
-    return launchWith<64, false, false>(g, mapA, mapB, mapD, 2, p.stream);
+    if (pair) return bn == 256 ? launchWith<256, true, false>(g, mapA, mapB, mapD, mirrors, 3, p.stream) : launchWith<128, true, false>(g, mapA, mapB, mapD, mirrors, 4, p.stream);
+    if (bn == 256) return launchWith<256, false, false>(g, mapA, mapB, mapD, mirrors, 0, p.stream);
+    if (bn == 128) return launchWith<128, false, false>(g, mapA, mapB, mapD, mirrors, 1, p.stream);
+    return launchWith<64, false, false>(g, mapA, mapB, mapD, mirrors, 2, p.stream);
 }
 
 int ummaDeviceStatus() {

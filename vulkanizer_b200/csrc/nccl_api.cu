@@ -83,7 +83,7 @@ struct Arena {
     unsigned status;
 };
 
-enum OpKind { kAllGather, kBroadcast, kAllReduce, kReduceScatter, kReduce, kGather, kAllToAll };
+enum OpKind { kAllGather, kBroadcast, kAllReduce, kReduceScatter, kReduce, kGather, kAllToAll, kBarrierOnly };
 
 }  // namespace
 
@@ -375,6 +375,8 @@ ncclResult_t runRound(Op& o, int round) {
             e = copyAsync(static_cast<char*>(o.recv) + size_t(p) * bytes, src, bytes, o.stream);
         }
         break;
+    case kBarrierOnly:
+        break;
     case kReduce:
     case kReduceScatter: {
         if (o.kind == kReduce && me != o.root) break;
@@ -462,13 +464,19 @@ ncclResult_t execute(std::vector<Op>& ops) {
             r = runRound(*o, 1);
         }
     }
-    if (r == ncclSuccess) r = barrier(all);
+    if (r == ncclSuccess) {
+        std::vector<Op*> closing;
+        for (Op& o : ops)
+            if (o.kind != kBarrierOnly) closing.push_back(&o);
+        r = barrier(closing);
+    }
     return r;
 }
 
 ncclResult_t submit(Op op) {
     if (!op.comm) return ncclInvalidArgument;
-    if (typeSize(op.type) == 0 || (!op.recv && op.count && !(op.kind == kReduce || op.kind == kGather))) return fail(op.comm, ncclInvalidArgument, "bad datatype or null buffer");
+    if (op.kind != kBarrierOnly && (typeSize(op.type) == 0 || (!op.recv && op.count && !(op.kind == kReduce || op.kind == kGather))))
+        return fail(op.comm, ncclInvalidArgument, "bad datatype or null buffer");
     if ((op.kind == kBroadcast || op.kind == kReduce || op.kind == kGather) && (op.root < 0 || op.root >= op.comm->nranks))
         return fail(op.comm, ncclInvalidArgument, "root out of range");
     if (unsigned(op.op) >= unsigned(ncclNumOps) && (op.kind == kAllReduce || op.kind == kReduce || op.kind == kReduceScatter))
@@ -737,6 +745,48 @@ ncclResult_t ncclGroupEnd(void) {
     const ncclResult_t r = execute(ops);
     cudaSetDevice(prev);
     return r;
+}
+
+
+// ---- extensions (include/vkzb_nccl.h): what a kernel that writes its results straight into its peers needs ----
+
+// Collective and blocking on the host only: every rank hands in one cudaMalloc'ed buffer and gets back, for each rank, an
+// address through which this process reaches that rank's buffer (its own for its own rank).
+ncclResult_t vkzbNcclExchangeBuffer(ncclComm_t comm, void* buffer, void** peers) {
+    if (!comm || !buffer || !peers) return ncclInvalidArgument;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(comm->device);
+    ncclResult_t result = ncclSuccess;
+    const uint64_t seq = ++comm->opSeq;
+    peers[comm->rank] = buffer;
+    if (comm->nranks > 1) {
+        RankSlot& slot = comm->shared->ranks[comm->rank];
+        OpPost& post = slot.posts[seq % kPostRing];
+        BufferPost none{};
+        post.recv = none;
+        if (!describeBuffer(buffer, post.send)) result = fail(comm, ncclInvalidArgument, "the buffer is not device memory that can be shared (cudaMalloc memory is)");
+        slot.postSeq.store(seq, std::memory_order_release);  // published even on failure, so the peers do not wait for it
+        if (result == ncclSuccess)
+            result = hostWait(comm, [&] {
+                for (int p = 0; p < comm->nranks; ++p)
+                    if (comm->shared->ranks[p].postSeq.load(std::memory_order_acquire) < seq) return false;
+                return true;
+            }, "the other ranks to hand in their buffer");
+        for (int p = 0; result == ncclSuccess && p < comm->nranks; ++p) {
+            if (p == comm->rank) continue;
+            peers[p] = mapPeerBuffer(comm, p, comm->shared->ranks[p].posts[seq % kPostRing].send);
+            if (!peers[p]) result = fail(comm, ncclUnhandledCudaError, "could not map a peer's buffer (cudaIpcOpenMemHandle)");
+        }
+    }
+    cudaSetDevice(prev);
+    return result;
+}
+
+// A barrier across the ranks, asynchronous on `stream` (on the host where ranks share a GPU): work enqueued after it on any
+// rank starts only when every rank's stream has reached it.
+ncclResult_t vkzbNcclBarrier(ncclComm_t comm, cudaStream_t stream) {
+    return submit({comm, kBarrierOnly, nullptr, nullptr, 0, ncclInt8, ncclSum, 0, stream});
 }
 
 // Not served yet (include/vkzb_nccl.h lists them): parameterless like the reference's stubs, so any signature binds.

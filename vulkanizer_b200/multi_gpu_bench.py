@@ -9,6 +9,12 @@ multiplied; A (2 GiB) is replicated, every rank ends with the whole of D. This i
 `partOf(g, rows=false, first, count)` (src/cublas/cublas.cpp:542-546) applied across GPUs, with the exchange step its
 libnccl surface provides (src/nccl/nccl.cpp:691-695). Strong scaling: the total work is fixed.
 
+Two ways of getting every rank's columns everywhere are built. Default ("fused"): each rank multiplies its whole column
+block in one cublasLtMatmul call whose epilogue stores every finished tile not only to its own D but, through peer-mapped
+addresses (vkzbNcclExchangeBuffer + vkzbSetOutputMirrors), to the other ranks' D as well, so the NVLink traffic is spread
+over the whole product and nothing is left to gather; barriers of libnccl.so.2 order the ranks around the step.
+VKZB_BENCH_GATHER=nccl: the block-cyclic, chunk-pipelined products + ncclAllGather described above.
+
 torch.distributed (gloo) is only the plumbing: it carries the 128-byte communicator id, the barrier around the timed region and
 the maximum over the ranks' device times. All GPU work goes through this repository's libcublasLt.so.12 and libnccl.so.2.
 """
@@ -21,21 +27,26 @@ import time
 
 
 def round_widths(n: int, ranks: int):
-    """Chunk widths (columns per rank) of the successive rounds. Wide chunks first: 2048 columns are 1024 tile pairs of
-    256 x 256, 13.8 waves over 74 CTA pairs, so almost no SM idles at the end of a chunk. The last rounds shrink
-    (1024, 512, 256, 256) because the gather of the final round cannot hide behind a product: the smaller it is, the less
-    of it is exposed at the end of the step."""
+    forced = os.environ.get("VKZB_BENCH_WIDTHS")  # e.g. "1024,1024,1024,512,256,256": an experiment knob
+    if forced:
+        return [int(w) for w in forced.split(",")]
+    return default_round_widths(n, ranks)
+
+
+def default_round_widths(n: int, ranks: int):
+    """Chunk widths (columns per rank) of the successive rounds: uniform, 1024 columns where the share allows four rounds.
+    1024 columns are 512 tile pairs of 256 x 256, 6.9 waves over 74 CTA pairs, so almost no SM idles at the end of a
+    chunk; and with equal chunks the gather of round j (about 0.8 of a chunk's product time over NVLink) always hides
+    behind the product of round j + 1. Only the last round's gather is exposed. (Rounds that shrink towards the end were
+    measured slower: a wide round's gather outlasts the narrower product after it.)"""
     per_rank = n // ranks
     assert n % ranks == 0 and per_rank % 256 == 0, "the column count must be a multiple of 256 x ranks"
     if ranks == 1:
         return [min(2048, per_rank)] * (per_rank // min(2048, per_rank))
-    tail = [1024, 512, 256, 256]
-    if per_rank < sum(tail) or (per_rank - sum(tail)) % 2048:
-        width = 256
-        while width * 2 <= per_rank // 4 and per_rank % (width * 2) == 0 and width < 1024:
-            width *= 2
-        return [width] * (per_rank // width)
-    return [2048] * ((per_rank - sum(tail)) // 2048) + tail
+    width = 1024
+    while width > 256 and (per_rank % width or per_rank // width < 4):
+        width //= 2
+    return [width] * (per_rank // width)
 
 
 def column_chunks(n: int, ranks: int, widths=None):
@@ -68,7 +79,15 @@ def run(args):
 
     size = int(os.environ.get("VKZB_BENCH_SIZE", "32768"))
     m = n = k = size
-    rounds = column_chunks(n, world)
+    # fused (default): one product per rank whose tiles go straight to every rank's D; nccl: chunked products + ncclAllGather
+    fused = world > 1 and os.environ.get("VKZB_BENCH_GATHER", "fused") != "nccl"
+    # (fused: still 2048 columns per call. One call over a rank's whole share ran a quarter slower at 2 GPUs: over tens of
+    # milliseconds the CTAs of one persistent kernel drift apart along k and stop finding each other's operand slices in L2.)
+    fused_width = int(os.environ.get("VKZB_BENCH_FUSED_WIDTH", "2048"))
+    rounds = column_chunks(n, world, None)
+    if fused:
+        per_rank, w = n // world, min(fused_width, n // world)
+        rounds = [(j, w, None, [r * per_rank + j * w for r in range(world)]) for j in range(per_rank // w)]
     mine_cols = sum(w for _, w, _, _ in rounds)  # columns this rank computes
 
     # the communicator id travels through the process group
@@ -100,22 +119,33 @@ def run(args):
     bf16, f32 = capi.CUDA_R_16BF, capi.CUDA_R_32F
     events = [torch.cuda.Event() for _ in rounds]
 
+    no_gemm, no_gather = bool(os.environ.get("VKZB_BENCH_NO_GEMM")), bool(os.environ.get("VKZB_BENCH_NO_GATHER"))  # experiment knobs
+
+    if fused:
+        peers = comm.exchange_buffer(D.data_ptr())
+        lt.set_output_mirrors(D.data_ptr(), D.numel() * 4, [peers[p] for p in range(world) if p != rank])
+
     def step():
+        if fused:
+            comm.barrier(compute.cuda_stream)  # nobody still reads the D this step overwrites
         for j, w, round_first, firsts in rounds:
             mine = D.data_ptr() + 4 * firsts[rank] * m
-            lt.matmul(capi.OP_T, capi.OP_N, m, w, k, 1.0, A.data_ptr(), bf16, k, Bmine.data_ptr() + 2 * b_offset[j], bf16, k, 0.0,
-                      mine, f32, m, mine, f32, m, stream=compute.cuda_stream)
-            if world > 1:
+            if not no_gemm:
+                lt.matmul(capi.OP_T, capi.OP_N, m, w, k, 1.0, A.data_ptr(), bf16, k, Bmine.data_ptr() + 2 * b_offset[j], bf16, k, 0.0,
+                          mine, f32, m, mine, f32, m, stream=compute.cuda_stream)
+            if world > 1 and not no_gather and not fused:
                 events[j].record(compute)
                 gather.wait_event(events[j])
                 comm.all_gather(mine, D.data_ptr() + 4 * round_first * m, w * m, "float32", gather.cuda_stream)
-        if world > 1:
+        if fused:
+            comm.barrier(compute.cuda_stream)  # every rank's product is finished, so every tile has landed here
+        elif world > 1:
             compute.wait_stream(gather)  # the step ends when every rank's columns have arrived
 
     for _ in range(max(3, args.warmup)):
         step()
     torch.cuda.synchronize()
-    assert lt.last_path() == capi.PATH_UMMA
+    assert no_gemm or lt.last_path() == capi.PATH_UMMA
     launches0 = lt.launch_count()
     sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
     dist.barrier()
@@ -138,7 +168,7 @@ def run(args):
 
     # a spot check that the gather delivered every rank's columns: column sums of a few remote chunks against a local product
     check_ok = True
-    if world > 1:
+    if world > 1 and not (no_gemm or no_gather):
         other = (rank + 1) % world
         j, w, _, firsts = rounds[-1]
         gen.manual_seed(5 * 100003 + firsts[other] // 256)
@@ -189,8 +219,8 @@ def run(args):
             "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": "cfg5b_bf16_32768_nsharded", "call": "cublasLtMatmul + ncclAllGather", "opA": "T", "opB": "N", "m": m, "n": n,
-                       "k": k, "a_b_type": "bf16", "c_type": "f32", "alpha": 1, "beta": 0, "seed": 5, "parallelism": f"n-sharded x{world}",
+            "config": {"workload": "cfg5b_bf16_32768_nsharded", "call": "cublasLtMatmul with output mirrors (tiles stored to every rank over NVLink)" if fused else "cublasLtMatmul + ncclAllGather", "opA": "T", "opB": "N", "m": m, "n": n,
+                       "k": k, "a_b_type": "bf16", "c_type": "f32", "alpha": 1, "beta": 0, "seed": 5, "parallelism": f"n-sharded x{world}", "gather": "fused into the GEMM epilogue" if fused else ("none" if world == 1 else "ncclAllGather, chunk-pipelined"),
                        "chunk_columns": [w for _, w, _, _ in rounds], "rounds": len(rounds),
                        "l2": "operands of one step hold 8 GiB > L2, no flush", "timing": "CUDA events on the compute stream, maximum over ranks"},
             "roofline": {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak, "traffic": None,
@@ -202,6 +232,10 @@ def run(args):
             "gpu_launches": launches * world, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    if fused:
+        lt.set_output_mirrors(0, 0, [])
+    torch.cuda.synchronize()
+    dist.barrier()
     comm.destroy()
     lt.destroy()
     dist.barrier()
