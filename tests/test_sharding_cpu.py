@@ -31,7 +31,8 @@ def test_partition_covers_every_column_once_in_gather_order(n, ranks):
 
 
 def test_rounds_are_uniform_so_each_gather_hides_behind_the_next_product():
-    assert round_widths(32768, 8) == [1024] * 4
+    assert round_widths(32768, 8) == [512] * 8
+    assert round_widths(32768, 4) == [1024] * 8
     assert round_widths(32768, 2) == [1024] * 16
     assert round_widths(32768, 1) == [2048] * 16
     assert round_widths(8192, 8) == [256] * 4

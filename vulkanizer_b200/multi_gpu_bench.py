@@ -43,7 +43,7 @@ def default_round_widths(n: int, ranks: int):
     assert n % ranks == 0 and per_rank % 256 == 0, "the column count must be a multiple of 256 x ranks"
     if ranks == 1:
         return [min(2048, per_rank)] * (per_rank // min(2048, per_rank))
-    width = 1024
+    width = 1024 if ranks < 8 else 512  # 8 GPUs: the link is busy most of the step, and 512 measured 4 % faster than 1024
     while width > 256 and (per_rank % width or per_rank // width < 4):
         width //= 2
     return [width] * (per_rank // width)
@@ -80,7 +80,14 @@ def run(args):
     size = int(os.environ.get("VKZB_BENCH_SIZE", "32768"))
     m = n = k = size
     # fused (default): one product per rank whose tiles go straight to every rank's D; nccl: chunked products + ncclAllGather
-    fused = world > 1 and os.environ.get("VKZB_BENCH_GATHER", "fused") != "nccl"
+    # Which of the two is the default depends on how much of the step NVLink needs: every rank receives (G - 1) / G of D,
+    # 4 m n (G - 1) / G bytes at about 770 GB/s, against 2 m n k / G flop at about 1.45 PFLOP/s. Mirrored bulk stores reach
+    # about 640 GB/s and push back into the epilogue when the link is busy most of the step (8 GPUs: 4.9 ms of traffic in a
+    # 6.0 ms product, measured 9.1 ms fused against 8.3 ms chunk-pipelined), while the copy engines behind ncclAllGather
+    # reach 700 GB/s; below that (2 and 4 GPUs) the fused form wins because nothing is left over at the end of the step.
+    link_share = (4.0 * m * n * (world - 1) / world / 770e9) / (2.0 * m * n * k / world / 1.45e15) if world > 1 else 0.0
+    choice = os.environ.get("VKZB_BENCH_GATHER", "auto")
+    fused = world > 1 and (choice == "fused" or (choice == "auto" and link_share < 0.6))
     # (fused: still 2048 columns per call. One call over a rank's whole share ran a quarter slower at 2 GPUs: over tens of
     # milliseconds the CTAs of one persistent kernel drift apart along k and stop finding each other's operand slices in L2.)
     fused_width = int(os.environ.get("VKZB_BENCH_FUSED_WIDTH", "2048"))
