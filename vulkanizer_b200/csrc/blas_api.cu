@@ -132,6 +132,7 @@ static int accumulatorFor(int ta, int tb, int tc, cublasComputeType_t compute) {
 // Picks the kernel family and launches. `p` is complete except for the stream.
 cublasStatus_t dispatch(cublasHandle_t h, Problem& p) {
     p.stream = h->stream;
+    p.scratch = h->scratch, p.scratchBytes = h->scratchBytes;
     p.mirrorCount = 0;
     if (h->mirrorCount > 0 && !p.epi.pointerArrays) {
         const char* d = static_cast<const char*>(p.epi.D);
@@ -253,12 +254,20 @@ cublasStatus_t cublasCreate_v2(cublasHandle_t* handle) {
     cudaGetDevice(&h->device);
     envLevel();
     forcedPath();
+    // scratch for split-k partial sums: 8 MiB of partial tiles behind the arrival counters, which start at zero
+    h->scratchBytes = kSplitKCounters * sizeof(unsigned) + (size_t(8) << 20);
+    if (cudaMalloc(&h->scratch, h->scratchBytes) != cudaSuccess || cudaMemset(h->scratch, 0, kSplitKCounters * sizeof(unsigned)) != cudaSuccess) {
+        cudaGetLastError();
+        if (h->scratch) cudaFree(h->scratch);
+        h->scratch = nullptr, h->scratchBytes = 0;  // products simply are not split
+    }
     *handle = h;
     return CUBLAS_STATUS_SUCCESS;
 }
 
 cublasStatus_t cublasDestroy_v2(cublasHandle_t handle) {
     if (!handle) return CUBLAS_STATUS_NOT_INITIALIZED;
+    if (handle->scratch) cudaFree(handle->scratch);
     delete handle;
     return CUBLAS_STATUS_SUCCESS;
 }

@@ -15,6 +15,10 @@ struct cublasContext {
     int device = 0;
     void* workspace = nullptr;
     size_t workspaceBytes = 0;
+    // Scratch memory owned by the handle (allocated at creation, like cuBLAS's own workspace): partial sums of split-k
+    // products. One handle, one stream at a time: two calls that overlap on the GPU through the same handle would share it.
+    void* scratch = nullptr;
+    size_t scratchBytes = 0;
     // output mirrors (vkzbSetOutputMirrors): results inside [mirrorLocal, mirrorLocal + mirrorBytes) are also written there
     const char* mirrorLocal = nullptr;
     size_t mirrorBytes = 0;

@@ -64,6 +64,8 @@ struct Problem {
     EpilogueArgs epi{};
     int mirrorCount = 0;              // D is also written to these addresses (same layout), tile by tile
     void* mirrorD[kMaxMirrors] = {};
+    void* scratch = nullptr;          // the handle's scratch memory (split-k partial sums); calls sharing it must not overlap
+    size_t scratchBytes = 0;
     cudaStream_t stream = nullptr;
 };
 
@@ -72,7 +74,11 @@ cudaError_t launchScale(const Problem& p);    // k = 0: D = act(beta * C + bias)
 cudaError_t launchGeneric(const Problem& p);  // any types / leading dimensions / pointer arrays
 cudaError_t launchGemv(const Problem& p);     // m = 1 or n = 1
 bool sgemmEligible(const Problem& p);
-cudaError_t launchSgemm(const Problem& p);    // fp32 FFMA
+cudaError_t launchSgemm(const Problem& p);    // fp32 FFMA (split along k through p.scratch when the product is small)
+constexpr int kSplitKCounters = 4096;          // arrival counters at the start of split-k scratch memory
+size_t sgemmSplitKScratchBytes(int m, int n, int splits);
+int sgemmSplitKPlan(const Problem& p, size_t scratchBytes);
+cudaError_t launchSgemmSplitK(const Problem& p, int splits, void* scratch);
 bool ummaEligible(const Problem& p);
 bool ummaCanMirror(const Problem& p);          // D and the mirrors can be written with bulk stores
 cudaError_t launchUmma(const Problem& p);     // tcgen05 tensor cores

@@ -6,6 +6,8 @@
 // shared memory k-major ([k][m] and [k][n]) so the inner product reads two float4 of each per k; the next k slice
 // is fetched into registers while the current one is multiplied (two shared buffers, one barrier per slice).
 // Accumulation is plain fp32 with k ascending, so results stay within 1e-5 of an fp64 reference.
+#include <cstdlib>
+
 #include "epilogue.cuh"
 
 namespace vkzb {
@@ -20,6 +22,11 @@ struct SgemmArgs {
     int m, n, k;
     int batchOffset;
     EpilogueArgs epi;
+    // split-k (one batch entry only): blockIdx.z is the slice of k, kPer its length; partial tiles and per-tile arrival
+    // counters live in scratch memory
+    int splits, kPer;
+    float* partials;
+    unsigned* counters;
 };
 
 // Fetches this thread's part of a BMN x BK tile of an operand into registers.
@@ -86,7 +93,11 @@ struct TileLoader {
 };
 
 // BM x BN tile per CTA, (BM/16) x (BN/16) results per thread as 4-wide groups 64 (or 32) apart.
-template <int BM, int BN, bool A_MCONTIG, bool B_NCONTIG>
+// SPLITK: the k range is cut into g.splits slices, one CTA each, for products too small to fill the SMs otherwise (512^3 is
+// 64 tiles of 64 x 64 for 148 SMs, and each would walk all of k alone). A CTA leaves its partial tile in scratch memory and
+// counts itself in; the last one to arrive for a tile adds the partial tiles in slice order, so the result does not depend
+// on which CTA came last, applies alpha and beta, and resets the counter for the next call.
+template <int BM, int BN, bool A_MCONTIG, bool B_NCONTIG, bool SPLITK = false>
 __global__ void __launch_bounds__(kThreads) sgemmKernel(const SgemmArgs g) {
     constexpr int TM = BM / 16, TN = BN / 16;        // 8 x 8 for 128 x 128, 4 x 4 for 64 x 64
     constexpr int GM = TM / 4, GN = TN / 4;          // float4 groups per thread
@@ -95,11 +106,13 @@ __global__ void __launch_bounds__(kThreads) sgemmKernel(const SgemmArgs g) {
     __shared__ __align__(16) float sA[2][BK * kPitchA];
     __shared__ __align__(16) float sB[2][BK * kPitchB];
 
-    const long long entry = (long long)blockIdx.z + g.batchOffset;
+    const long long entry = SPLITK ? 0 : (long long)blockIdx.z + g.batchOffset;
     const float* A = g.A + entry * g.strideA;
     const float* B = g.B + entry * g.strideB;
     const int row0 = blockIdx.x * BM, col0 = blockIdx.y * BN;
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    const int kBegin = SPLITK ? int(blockIdx.z) * g.kPer : 0;
+    const int kEnd = SPLITK ? min(g.k, kBegin + g.kPer) : g.k;
 
     const bool vecA = (reinterpret_cast<uintptr_t>(A) & 15) == 0 && g.lda % 4 == 0;
     const bool vecB = (reinterpret_cast<uintptr_t>(B) & 15) == 0 && g.ldb % 4 == 0;
@@ -108,8 +121,8 @@ __global__ void __launch_bounds__(kThreads) sgemmKernel(const SgemmArgs g) {
     TileLoader<BN, BK, B_NCONTIG> lb;
     float acc[TM][TN] = {};
 
-    la.fetch(A, g.lda, row0, g.m, 0, g.k, vecA);
-    lb.fetch(B, g.ldb, col0, g.n, 0, g.k, vecB);
+    la.fetch(A, g.lda, row0, g.m, kBegin, kEnd, vecA);
+    lb.fetch(B, g.ldb, col0, g.n, kBegin, kEnd, vecB);
     la.commit(sA[0]);
     lb.commit(sB[0]);
     __syncthreads();
@@ -121,11 +134,11 @@ __global__ void __launch_bounds__(kThreads) sgemmKernel(const SgemmArgs g) {
     constexpr int kFlush = 4;
     float part[kTwoLevel ? TM : 1][kTwoLevel ? TN : 1] = {};
     int buf = 0, sinceFlush = 0;
-    for (int k0 = 0; k0 < g.k; k0 += BK) {
-        const bool more = k0 + BK < g.k;
+    for (int k0 = kBegin; k0 < kEnd; k0 += BK) {
+        const bool more = k0 + BK < kEnd;
         if (more) {
-            la.fetch(A, g.lda, row0, g.m, k0 + BK, g.k, vecA);
-            lb.fetch(B, g.ldb, col0, g.n, k0 + BK, g.k, vecB);
+            la.fetch(A, g.lda, row0, g.m, k0 + BK, kEnd, vecA);
+            lb.fetch(B, g.ldb, col0, g.n, k0 + BK, kEnd, vecB);
         }
         const float* a = sA[buf];
         const float* b = sB[buf];
@@ -161,6 +174,41 @@ __global__ void __launch_bounds__(kThreads) sgemmKernel(const SgemmArgs g) {
             __syncthreads();
             buf ^= 1;
         }
+    }
+
+    if constexpr (SPLITK) {
+        __shared__ unsigned arrivedBefore;
+        const unsigned tile = blockIdx.x + blockIdx.y * gridDim.x, tiles = gridDim.x * gridDim.y;
+        constexpr int kPerTile = BM * BN;
+        // element (i, j) of thread t at (i * TN + j) * kThreads + t: consecutive threads, consecutive addresses
+        float* mine = g.partials + (size_t(blockIdx.z) * tiles + tile) * kPerTile;
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+            for (int j = 0; j < TN; ++j) mine[(i * TN + j) * kThreads + threadIdx.x] = acc[i][j];
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) arrivedBefore = atomicAdd(&g.counters[tile], 1u);
+        __syncthreads();
+        if (arrivedBefore + 1 < unsigned(g.splits)) return;
+        __threadfence();  // the other slices' partial tiles are complete and visible
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+            for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+        for (int z = 0; z < g.splits; ++z) {  // slice order; the loads of one slice are independent of each other
+            const float* part = g.partials + (size_t(z) * tiles + tile) * kPerTile + threadIdx.x;
+            float v[TM][TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) v[i][j] = __ldcg(part + (i * TN + j) * kThreads);
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] += v[i][j];
+        }
+        if (threadIdx.x == 0) g.counters[tile] = 0;  // ready for the next call on this scratch memory
     }
 
     Epilogue<float> epi;
@@ -206,7 +254,47 @@ bool sgemmEligible(const Problem& p) {
            (reinterpret_cast<uintptr_t>(p.A) & 3) == 0 && (reinterpret_cast<uintptr_t>(p.B) & 3) == 0;
 }
 
+// Scratch memory of the split-k form: kSplitKCounters arrival counters (zero between calls), then the partial tiles.
+size_t sgemmSplitKScratchBytes(int m, int n, int splits) {
+    const size_t tiles = size_t((m + 63) / 64) * ((n + 63) / 64);
+    return kSplitKCounters * sizeof(unsigned) + size_t(splits) * tiles * 64 * 64 * sizeof(float);
+}
+
+// How many slices of k a product should be cut into (1: do not split). Splitting pays when the 64 x 64 tiles alone leave
+// most SMs idle and k is long enough to share out; the partial tiles must fit the scratch memory.
+int sgemmSplitKPlan(const Problem& p, size_t scratchBytes) {
+    if (p.batch != 1 || scratchBytes == 0) return 1;
+    static const int forced = [] { const char* v = std::getenv("VKZB_SGEMM_SPLITS"); return v ? std::atoi(v) : 0; }();  // experiment knob
+    if (forced > 0) return sgemmSplitKScratchBytes(p.m, p.n, forced) <= scratchBytes && (long long)((p.m + 63) / 64) * ((p.n + 63) / 64) <= kSplitKCounters ? forced : 1;
+    const long long tiles = (long long)((p.m + 63) / 64) * ((p.n + 63) / 64);
+    if (tiles > kSplitKCounters || tiles * 2 > smCount() || p.k < 256) return 1;  // measured: below k = 256 the hand-over costs more than it saves
+    int splits = int(std::min<long long>(std::min<long long>(8, 2LL * smCount() / tiles), p.k / 64));
+    while (splits > 1 && sgemmSplitKScratchBytes(p.m, p.n, splits) > scratchBytes) --splits;
+    return splits;
+}
+
+cudaError_t launchSgemmSplitK(const Problem& p, int splits, void* scratch) {
+    SgemmArgs g{static_cast<const float*>(p.A), static_cast<const float*>(p.B), p.lda, p.ldb, 0, 0, p.m, p.n, p.k, 0, p.epi};
+    g.splits = splits;
+    g.kPer = ((p.k + splits - 1) / splits + 15) / 16 * 16;  // whole shared-memory fills
+    g.splits = (p.k + g.kPer - 1) / g.kPer;
+    g.counters = static_cast<unsigned*>(scratch);
+    g.partials = reinterpret_cast<float*>(g.counters + kSplitKCounters);
+    const dim3 grid((p.m + 63) / 64, (p.n + 63) / 64, g.splits);
+    const bool am = !p.transA, bn = p.transB;
+    if (am && bn) sgemmKernel<64, 64, true, true, true><<<grid, kThreads, 0, p.stream>>>(g);
+    else if (am) sgemmKernel<64, 64, true, false, true><<<grid, kThreads, 0, p.stream>>>(g);
+    else if (bn) sgemmKernel<64, 64, false, true, true><<<grid, kThreads, 0, p.stream>>>(g);
+    else sgemmKernel<64, 64, false, false, true><<<grid, kThreads, 0, p.stream>>>(g);
+    countLaunch();
+    return cudaGetLastError();
+}
+
 cudaError_t launchSgemm(const Problem& p) {
+    if (p.scratch) {
+        const int splits = sgemmSplitKPlan(p, p.scratchBytes);
+        if (splits > 1) return launchSgemmSplitK(p, splits, p.scratch);
+    }
     SgemmArgs g{static_cast<const float*>(p.A), static_cast<const float*>(p.B), p.lda, p.ldb, p.strideA, p.strideB,
                 p.m, p.n, p.k, 0, p.epi};
     // 128 x 128 tiles once they fill the machine; 64 x 64 below that so small products still spread over the SMs

@@ -109,6 +109,7 @@ cublasStatus_t cublasLtCreate(cublasLtHandle_t* lightHandle) {
 
 cublasStatus_t cublasLtDestroy(cublasLtHandle_t lightHandle) {
     if (!lightHandle) return CUBLAS_STATUS_NOT_INITIALIZED;
+    if (lightHandle->scratch) cudaFree(lightHandle->scratch);
     delete lightHandle;
     return CUBLAS_STATUS_SUCCESS;
 }
@@ -343,6 +344,7 @@ cublasStatus_t cublasLtMatmul(cublasLtHandle_t h, cublasLtMatmulDesc_t desc, con
         return CUBLAS_STATUS_INVALID_VALUE;
 
     cublasContext call = *h;  // the handle itself stays as it is: only this call runs on `stream`
+    call.scratch = nullptr, call.scratchBytes = 0;  // a light handle carries no split-k scratch (its products are not split)
     call.stream = stream;
     return dispatch(&call, p);
 }
