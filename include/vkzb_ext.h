@@ -10,6 +10,10 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#ifndef VKZB_HAVE_CUDA_TYPES
+typedef struct CUstream_st* cudaStream_t;
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -48,6 +52,28 @@ int vkzbDeviceStatus(void);
  * Exported by libcublas.so.12 and libcublasLt.so.12 alike (a handle belongs to the library that created it).
  */
 int vkzbSetOutputMirrors(void* handle, const void* localBase, size_t bytes, int count, void* const* mirrorBases);
+
+/*
+ * cublasSgemm for callers that may not allocate device memory. No counterpart in the reference.
+ *
+ * Who needs it: a process that gives all device memory to its own pool at start-up, or that is in a phase where cudaMalloc
+ * is unacceptable because it synchronises the device. Such a caller cannot create a cuBLAS handle here (creation allocates
+ * the scratch memory of the split-k kernel), so this entry point takes no handle and runs the same split-k FFMA kernel on a
+ * scratch array built into the library image. It calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ * C = alpha op(A) op(B) + beta C, fp32, column-major, alpha and beta on the host, asynchronous on `stream`; transa / transb
+ * are cublasOperation_t values; the return value is a cublasStatus_t value.
+ * Limit: the built-in array holds 4096 counters and 4 MiB of partial tiles, enough for results of up to 256 tiles of
+ * 64 x 64 (m * n up to about 2^20, e.g. 1024 x 1024); k is cut into up to 8 slices as far as that room allows. A larger
+ * result is refused with CUBLAS_STATUS_INVALID_VALUE and a line on stderr; k = 0 and matrix-vector shapes answer
+ * CUBLAS_STATUS_NOT_SUPPORTED (use the handle-based entry points for those).
+ * The first call on each device looks up the array's device address (the device must be current); make that call before
+ * starting a stream capture. Every call on a device shares the one array, which keeps what the last call left in it (the
+ * kernel clears the counters it used): two calls that overlap on the GPU would corrupt each other, so issue them on one
+ * stream or order them yourself. Every GPU that loads the library carries the array (about 4 MiB) until the process ends.
+ */
+int vkzbSgemmStaticScratch(cudaStream_t stream, int transa, int transb, int m, int n, int k, const float* alpha, const float* A,
+                           int lda, const float* B, int ldb, const float* beta, float* C, int ldc);
 
 #ifdef __cplusplus
 }

@@ -108,6 +108,8 @@ def cublas_library() -> C.CDLL:
         lib.vkzbLastPath.argtypes, lib.vkzbLastPath.restype = [], _i
         lib.vkzbDeviceStatus.argtypes, lib.vkzbDeviceStatus.restype = [], _i
         lib.vkzbSetOutputMirrors.argtypes, lib.vkzbSetOutputMirrors.restype = [_vp, _vp, _sz, _i, C.POINTER(_vp)], _i
+        lib.vkzbSgemmStaticScratch.argtypes = [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _i]
+        lib.vkzbSgemmStaticScratch.restype = _i
         _cublas = lib
     return _cublas
 

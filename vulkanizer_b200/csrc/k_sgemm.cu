@@ -6,6 +6,7 @@
 // shared memory k-major ([k][m] and [k][n]) so the inner product reads two float4 of each per k; the next k slice
 // is fetched into registers while the current one is multiplied (two shared buffers, one barrier per slice).
 // Accumulation is plain fp32 with k ascending, so results stay within 1e-5 of an fp64 reference.
+#include <cstdio>
 #include <cstdlib>
 
 #include "epilogue.cuh"
@@ -313,3 +314,69 @@ cudaError_t launchSgemm(const Problem& p) {
 }
 
 }  // namespace vkzb
+
+// ---- the split-k product for callers that may not allocate ---------------------------------------------------------------
+//
+// Some users of this library hand every byte of device memory to their own pool when they start (an inference server
+// sized to the model it serves) or run in a phase where cudaMalloc is off limits because it synchronises the whole device
+// (a latency-bound serving loop). They cannot create a cuBLAS handle, whose creation allocates the split-k scratch, and
+// they cannot let a call allocate on their behalf. For them the same kernel runs on scratch memory that is part of the
+// library image: a file-scope device array, present on every GPU that loads the library for as long as the process lives.
+
+namespace {
+// Room for the arrival counters and 4 MiB of partial tiles: products of up to 256 tiles of 64 x 64 (m * n up to about one
+// million results, for instance 1024 x 1024), cut into as many k slices as still fit.
+constexpr size_t kStaticPartialBytes = size_t(4) << 20;
+constexpr size_t kStaticScratchBytes = vkzb::kSplitKCounters * sizeof(unsigned) + kStaticPartialBytes;
+static __device__ __align__(256) unsigned char g_staticSplitKScratch[kStaticScratchBytes];  // zero at load: the counters start at zero
+
+constexpr int kMaxDevices = 64;
+void* g_staticScratchAddress[kMaxDevices] = {};  // the array's address on each device, looked up once
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int vkzbSgemmStaticScratch(cudaStream_t stream, int transa, int transb, int m, int n, int k,
+                                                                             const float* alpha, const float* A, int lda, const float* B,
+                                                                             int ldb, const float* beta, float* C, int ldc) {
+    using namespace vkzb;
+    enum { kSuccess = 0, kNotInitialized = 1, kInvalidValue = 7, kExecutionFailed = 13, kNotSupported = 15 };  // cublasStatus_t values
+    if (m < 0 || n < 0 || k < 0 || !alpha || !beta || unsigned(transa) > 2u || unsigned(transb) > 2u) return kInvalidValue;
+    const int rowsA = transa == 0 ? m : k, rowsB = transb == 0 ? k : n;
+    if (lda < std::max(1, rowsA) || ldb < std::max(1, rowsB) || ldc < std::max(1, m)) return kInvalidValue;
+    if (m == 0 || n == 0) return kSuccess;
+    if (k == 0 || m == 1 || n == 1) return kNotSupported;  // this entry point is the tiled split-k product only
+    const long long tiles = (long long)((m + 63) / 64) * ((n + 63) / 64);
+    if (tiles > kSplitKCounters || sgemmSplitKScratchBytes(m, n, 1) > kStaticScratchBytes) {
+        std::fprintf(stderr, "vkzbSgemmStaticScratch: a %d x %d result needs %zu bytes of scratch memory, the built-in array holds %zu "
+                             "(products of up to 256 tiles of 64 x 64)\n", m, n, sgemmSplitKScratchBytes(m, n, 1), kStaticScratchBytes);
+        return kInvalidValue;
+    }
+    // Set-up, once per device, with that device current: in host code the array's name is only a stand-in, so its device
+    // address has to be asked for. The first call on a device does this.
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return kNotInitialized;
+    if (!g_staticScratchAddress[device]) {
+        void* address = nullptr;
+        if (cudaGetSymbolAddress(&address, g_staticSplitKScratch) != cudaSuccess || !address) {
+            cudaGetLastError();
+            return kNotInitialized;
+        }
+        g_staticScratchAddress[device] = address;
+    }
+    Problem p;
+    p.transA = transa != 0, p.transB = transb != 0;
+    p.m = m, p.n = n, p.k = k, p.batch = 1;
+    p.A = A, p.B = B, p.typeA = p.typeB = kF32;
+    p.lda = lda, p.ldb = ldb;
+    p.accType = kF32;
+    p.epi.D = C, p.epi.C = C;
+    p.epi.ldd = p.epi.ldc = ldc;
+    p.epi.typeD = p.epi.typeC = kF32;
+    p.epi.scalars.type = kScalarF32;
+    p.epi.scalars.alphaHost = double(*alpha), p.epi.scalars.betaHost = double(*beta);
+    p.stream = stream;
+    if (!sgemmEligible(p)) return kInvalidValue;  // A and B must be 4-byte aligned
+    int splits = int(std::min<long long>(std::min<long long>(8, std::max<long long>(1, 2LL * smCount() / tiles)), std::max(1, k / 64)));
+    while (splits > 1 && sgemmSplitKScratchBytes(m, n, splits) > kStaticScratchBytes) --splits;
+    return launchSgemmSplitK(p, splits, g_staticScratchAddress[device]) == cudaSuccess ? kSuccess : kExecutionFailed;
+}
+
