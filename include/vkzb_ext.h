@@ -34,8 +34,9 @@ uint64_t vkzbLaunchCount(void);
 /* VKZB_PATH_* of the most recent GEMM call made on this thread. */
 int vkzbLastPath(void);
 /*
- * Device-side status word of the tcgen05 kernels for the current device: 0 while every bounded wait
- * (mbarrier phase, TMEM allocation) completed; otherwise a code naming the wait that gave up. Reads
+ * Device-side status word of the tcgen05 and matrix-vector kernels for the current device: 0 while every bounded
+ * wait (mbarrier phase, TMEM allocation) completed; otherwise a code naming the wait that gave up (1-4: tcgen05
+ * kernel roles, 16: a bulk copy of the matrix-vector kernel). Reads
  * the word with a blocking copy, so call it after synchronising the stream. Returns -1 on a CUDA error.
  */
 int vkzbDeviceStatus(void);

@@ -55,6 +55,13 @@ CASES = [
     Case("gemv strided batched f16", T, N, 129, 1, 128, F16, F16, F16, 1.0, 0.0, 9, C16),
     Case("gemv f16 aligned rows", T, N, 100, 1, 203, F16, F16, F32, 1.0, 0.5, 3, C32, True),
     Case("gemv f16 long rows", T, N, 33, 1, 3000, F16, F32, F16, 1.0, 0.0, 1, C32, True),
+    Case("gemv bulk f16 one piece", T, N, 300, 1, 4096, F16, F16, F16, 1.0, 0.5, 1, C32, True),
+    Case("gemv bulk bf16 three pieces", T, N, 1000, 1, 11008, BF16, BF16, F32, 0.5, 0.0, 1, C32, True),
+    Case("gemv bulk f16 one chunk", T, N, 77, 1, 8, F16, F16, F32, 1.0, 0.0, 1, C32, True),
+    Case("gemv bulk f16 ragged piece", T, N, 150, 1, 4104, F16, F16, F16, -1.0, 0.0, 1, C32, True),
+    Case("gemv bulk bf16 fewer rows than SMs", T, N, 3, 1, 24064, BF16, BF16, BF16, 1.0, 1.0, 1, C32, True),
+    Case("gemv bulk f16 many short rows", T, N, 5000, 1, 520, F16, F16, F16, 1.0, 0.0, 1, C32, True),
+    Case("gemv bulk m=1 NN f16", N, N, 1, 500, 1024, F16, F16, F16, 1.0, 0.0, 1, C32, True),
     Case("gemv pointer batched", T, N, 100, 1, 64, F32, F32, F32, 1.0, 0.0, -6),
     Case("gemv m=1 pointer batched", N, N, 1, 100, 64, F32, F32, F32, 1.0, 0.0, -4),
     Case("k = 0 scales C", N, N, 10, 10, 0, F32, F32, F32, 1.0, 3.0),

@@ -559,7 +559,10 @@ cublasStatus_t cublasSgemv_v2_64(cublasHandle_t h, cublasOperation_t trans, int6
 // ---- extensions (include/vkzb_ext.h) ----
 uint64_t vkzbLaunchCount(void) { return g_launches.load(std::memory_order_relaxed); }
 int vkzbLastPath(void) { return t_lastPath; }
-int vkzbDeviceStatus(void) { return ummaDeviceStatus(); }
+int vkzbDeviceStatus(void) {
+    const int umma = ummaDeviceStatus();
+    return umma ? umma : gemvDeviceStatus();
+}
 
 int vkzbSetOutputMirrors(void* handle, const void* localBase, size_t bytes, int count, void* const* mirrorBases) {
     auto* h = static_cast<cublasContext*>(handle);

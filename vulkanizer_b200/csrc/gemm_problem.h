@@ -83,6 +83,7 @@ bool ummaEligible(const Problem& p);
 bool ummaCanMirror(const Problem& p);          // D and the mirrors can be written with bulk stores
 cudaError_t launchUmma(const Problem& p);     // tcgen05 tensor cores
 int ummaDeviceStatus();
+int gemvDeviceStatus();                      // 0, or 16 after a bulk copy of the matrix-vector kernel never arrived
 
 void countLaunch(int n = 1);
 

@@ -4,11 +4,20 @@
 // M is `rows` x `len` with arbitrary row and column strides, v has stride incv, y stride incy, each of
 // f32 / f16 / bf16 (int8 with int32 sums), batches by stride or by pointer arrays.
 //
-// The work is one pass over M, so the kernel is bound by HBM bandwidth. When rows are contiguous along
-// the reduction (op(A) = A^T for n = 1) and 16-byte aligned, one warp streams one row with 128-bit loads,
-// eight loads in flight per lane, fp32 partial sums per lane and a shuffle tree at the end; no shared memory,
-// no block-level barrier. Any other layout takes the strided kernel (a thread per row, coalesced when the
-// rows are interleaved in memory).
+// The work is one pass over M, so the kernel is bound by HBM bandwidth, and at decode sizes (tens of megabytes, ten
+// microseconds) by how quickly a launch gets its whole share of the matrix in flight. When rows are contiguous along the
+// reduction (op(A) = A^T for n = 1), 16-byte aligned and 16-bit, gemvRowsBulk runs one block of 16 warps per SM; each warp
+// owns an 8 KB shared-memory stage that bulk asynchronous copies fill (one instruction moves a whole piece of a row and
+// signals an mbarrier), so a warp has 8 KB on the way instead of the 2 KB its registers could hold, and the vector sits in
+// shared memory. Measured, a launch costs  t = t0 + bytes / 6.1..6.5 TB/s  with t0 = 3.0 us, the time a chain of dependent
+// 8 x 8 products takes per launch (2.0 us with programmatic stream serialisation, which this kernel asks for): the stream
+// rate is the copy bandwidth of the part, and at 4096 x 4096 (33 MB) t0 is a quarter of the time.
+// gemvRowsVec16 (a warp per row, 128-bit loads into registers, no shared memory) serves batches and rows the bulk copy
+// cannot take. Any other layout takes the scalar or the strided kernel (a thread per row, coalesced when the rows are
+// interleaved in memory).
+#include <cstdio>
+#include <cstdlib>
+
 #include "epilogue.cuh"
 
 namespace vkzb {
@@ -25,6 +34,7 @@ struct GemvArgs {
     int pointerArrays;
     int yIsRow;  // y^T = v^T M^T (the m = 1 case): element r of y is C(0, r)
     int batchOffset;
+    int overlap;  // bulk kernel: launched with programmatic stream serialisation (1), and asks L2 for its first rows before the wait (2)
     EpilogueArgs epi;
 };
 
@@ -74,7 +84,18 @@ __device__ __forceinline__ uint4 streamLoad(const void* p) {
 }
 
 constexpr int kWarpsPerBlock = 8;
-constexpr int kUnroll = 8;  // 16-byte loads in flight per lane: a row of 4096 halves is two trips to memory
+
+// A launch with programmatic stream serialisation lets blocks of this kernel become resident while the kernel before it in
+// the stream drains; they wait here until that kernel has completed and its writes are visible. Without the launch
+// attribute both instructions do nothing.
+__device__ __forceinline__ void waitForPriorKernel() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void releaseNextKernel() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Only a hint may come before that wait: it moves no data into the kernel, so it is right whatever the kernel before still
+// writes, and the loads after the wait find the bytes in L2.
+__device__ __forceinline__ void prefetchToL2(const void* p, unsigned bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+constexpr int kUnroll = 4;  // 16-byte loads in flight per lane (measured: 4 beats 1, 2, 8 and 16 from 4096 to 32000 rows)
 
 // One warp per row; M and v both 16-bit of the same type, rows contiguous and 16-byte aligned, incv = 1.
 template <bool BF16>
@@ -97,7 +118,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) gemvRowsVec16(const GemvA
         for (int u = 0; u < kUnroll; ++u) acc[u] = dot8<BF16>(a[u], __ldg(vec + c + 32 * u), acc[u]);
     }
     for (; c < chunks; c += 32) acc[0] = dot8<BF16>(streamLoad(mrow + c), __ldg(vec + c), acc[0]);
-    float sum = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+    float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     // the ragged end of a row whose length is not a multiple of 8
     for (int i = chunks * 8 + lane; i < g.len; i += 32)
         sum = fmaf(loadAs<float>(M, row * g.rowStride + i, g.typeM), loadAs<float>(v, i, g.typeV), sum);
@@ -108,6 +129,203 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) gemvRowsVec16(const GemvA
         epi.init(g.epi, entry);
         storeY(epi, g.yIsRow, row, sum);
     }
+}
+
+// ---- bulk-copy kernel --------------------------------------------------------------------------------------------
+
+constexpr int kBulkWarps = 16;  // at most
+constexpr int kPieceBytes = 8192;                   // one ring stage: a row of 4096 halves, or a piece of a longer one
+constexpr int kSharedLimit = 227 * 1024;
+constexpr unsigned long long kBulkWaitLimitNs = 2000000000ull;
+
+__device__ unsigned g_gemvStatus;  // 0, or 1 once a wait for a bulk copy ran out of time (the launch's result is then incomplete)
+
+__device__ __forceinline__ unsigned sharedAddr(const void* p) { return unsigned(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void bulkLoad(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// True once the phase with `parity` has completed; false after two seconds, with the status word set.
+__device__ __forceinline__ bool bulkWait(unsigned bar, unsigned parity) {
+    unsigned long long start = 0;
+    for (unsigned spins = 0;; ++spins) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((spins & 255u) == 255u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (start == 0) start = now;
+            else if (now - start > kBulkWaitLimitNs) {
+                atomicExch(&g_gemvStatus, 1u);
+                return false;
+            }
+        }
+    }
+}
+
+// One block per SM, rows dealt to blocks in equal contiguous shares and to a block's warps in turn. A warp owns `stages`
+// ring stages and their mbarriers: lane 0 issues the copies, all lanes wait, multiply the piece with the matching piece of
+// the vector (shared memory, loaded once per block) and, after __syncwarp, lane 0 refills the stage. No block-level barrier
+// after start-up. Needs len % 8 == 0 and everything the 128-bit register kernel needs.
+//
+// The launch allows programmatic stream serialisation: when the kernel before this one in the stream lets its successor
+// start early (this kernel does), a block becomes resident as soon as an SM has room, sets up its barriers, asks L2 for its
+// first rows and only then waits for the kernel before it to complete; every load of data comes after that wait.
+struct BulkShape {
+    int warps, stages, pieceBytes, pieces, vectorBytes, prefetchRows;
+    size_t sharedBytes() const { return size_t(vectorBytes) + size_t(warps) * stages * (pieceBytes + 8) + 8; }
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(kBulkWarps * 32) gemvRowsBulk(const GemvArgs g, const BulkShape shape) {
+    extern __shared__ __align__(128) unsigned char shared[];
+    const int stages = shape.stages, warps = shape.warps, pieceBytes = shape.pieceBytes, pieces = shape.pieces;
+    unsigned char* vecShared = shared;
+    unsigned char* ring = shared + shape.vectorBytes;  // a multiple of 128
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const unsigned barBase = sharedAddr(ring + size_t(warps) * stages * pieceBytes);
+    const unsigned vecBar = barBase + 8u * warps * stages;
+    const int rowBytes = g.len * 2;
+    const int firstRow = int((long long)g.rows * blockIdx.x / gridDim.x);
+    const int endRow = int((long long)g.rows * (blockIdx.x + 1) / gridDim.x);
+    const char* M = static_cast<const char*>(g.M);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i <= warps * stages; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(barBase + 8u * i) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (g.overlap) {
+        if (lane == 0)
+            for (int row = firstRow + warp, n = 0; row < endRow && n < shape.prefetchRows; row += warps, ++n)
+                prefetchToL2(M + (long long)row * g.rowStride * 2, unsigned(rowBytes));
+        waitForPriorKernel();
+        releaseNextKernel();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // the vector goes in pieces as well: one copy moves at most what the mbarrier's byte counter can take
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(vecBar), "r"(unsigned(rowBytes)) : "memory");
+        for (int at = 0; at < rowBytes; at += 8192)
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             sharedAddr(vecShared + at)),
+                         "l"(static_cast<const char*>(g.v) + at), "r"(unsigned(min(8192, rowBytes - at))), "r"(vecBar)
+                         : "memory");
+    }
+    const int myRows = (endRow - firstRow - warp + warps - 1) / warps;  // rows firstRow + warp, + warps, ...
+    if (myRows <= 0) return;
+    const int items = myRows * pieces;
+    unsigned char* myRing = ring + size_t(warp) * stages * pieceBytes;
+    const unsigned myBars = barBase + 8u * warp * stages;
+
+    const auto issue = [&](int item) {  // lane 0 only
+        const int r = item / pieces, piece = item - r * pieces;
+        const int row = firstRow + warp + r * warps;
+        const int stage = item % stages;
+        bulkLoad(sharedAddr(myRing + stage * pieceBytes), M + ((long long)row * g.rowStride * 2 + (long long)piece * pieceBytes),
+                 unsigned(min(pieceBytes, rowBytes - piece * pieceBytes)), myBars + 8u * stage);
+    };
+    if (lane == 0)
+        for (int i = 0; i < min(stages, items); ++i) issue(i);
+    if (!bulkWait(vecBar, 0)) return;
+
+    Epilogue<float> epi;
+    epi.init(g.epi, 0);
+    float acc[4] = {};
+    int piece = 0, r = 0;
+    for (int item = 0; item < items; ++item) {
+        const int stage = item % stages;
+        if (!bulkWait(myBars + 8u * stage, unsigned(item / stages) & 1u)) return;
+        const uint4* a = reinterpret_cast<const uint4*>(myRing + stage * pieceBytes);
+        const uint4* x = reinterpret_cast<const uint4*>(vecShared + piece * pieceBytes);
+        const int chunks = min(pieceBytes, rowBytes - piece * pieceBytes) / 16;
+        int c = lane;
+        if (chunks == kPieceBytes / 16) {
+#pragma unroll
+            for (int q = 0; q < kPieceBytes / 16 / 128; ++q) {
+                uint4 av[4], xv[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) av[u] = a[lane + 128 * q + 32 * u], xv[u] = x[lane + 128 * q + 32 * u];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[u] = dot8<BF16>(av[u], xv[u], acc[u]);
+            }
+            c = chunks;
+        }
+        for (; c + 96 < chunks; c += 128) {
+            uint4 av[4], xv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) av[u] = a[c + 32 * u], xv[u] = x[c + 32 * u];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[u] = dot8<BF16>(av[u], xv[u], acc[u]);
+        }
+        for (; c < chunks; c += 32) acc[0] = dot8<BF16>(a[c], x[c], acc[0]);
+        __syncwarp();
+        if (lane == 0 && item + stages < items) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the reads above come before the copy that overwrites them
+            issue(item + stages);
+        }
+        if (++piece == pieces) {
+            float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+            if (lane == 0) storeY(epi, g.yIsRow, firstRow + warp + r * warps, sum);
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+            piece = 0;
+            ++r;
+        }
+    }
+}
+
+// How the bulk kernel is laid out for rows of `len` 16-bit values; warps = 0 when it cannot take the shape.
+// Measured on 4096 x 4096 to 32000 x 4096: 16 warps with one stage each beat 8 x 3, 12 x 2, 20 x 1 and 24 x 1.
+BulkShape bulkShape(int len) {
+    BulkShape shape{};
+    if (len % 8 != 0) return shape;
+    const int rowBytes = len * 2;
+    shape.vectorBytes = (rowBytes + 127) / 128 * 128;
+    shape.pieces = (rowBytes + kPieceBytes - 1) / kPieceBytes;
+    shape.pieceBytes = ((rowBytes + shape.pieces - 1) / shape.pieces + 511) / 512 * 512;  // equal pieces, whole warp-wide trips
+    shape.stages = 1;
+    shape.prefetchRows = 2;
+    for (shape.warps = 16; shape.warps >= 8; shape.warps -= 4)
+        if (shape.sharedBytes() <= size_t(kSharedLimit)) return shape;
+    shape.warps = 0;  // a vector too long to sit in shared memory beside the ring
+    return shape;
+}
+
+template <bool BF16>
+cudaError_t launchBulk(const Problem& p, const GemvArgs& g, const BulkShape& shape) {
+    static bool prepared[64] = {};
+    int device = 0, sms = 0;
+    if (cudaError_t e = cudaGetDevice(&device); e != cudaSuccess) return e;
+    if (cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device); e != cudaSuccess) return e;
+    if (device < 64 && !prepared[device]) {
+        if (cudaError_t e = cudaFuncSetAttribute(gemvRowsBulk<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSharedLimit); e != cudaSuccess)
+            return e;
+        prepared[device] = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(std::min(sms, g.rows));
+    cfg.blockDim = dim3(shape.warps * 32);
+    cfg.dynamicSmemBytes = shape.sharedBytes();
+    cfg.stream = p.stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = g.overlap ? 1 : 0;
+    countLaunch();
+    return cudaLaunchKernelEx(&cfg, gemvRowsBulk<BF16>, g, shape);
 }
 
 // One warp per row, any types, rows contiguous (colStride = 1) but not necessarily aligned.
@@ -206,6 +424,11 @@ cudaError_t launchGemv(const Problem& p) {
     const bool vec16 = rowMajor && p.accType == kF32 && !p.pointerArrays && g.typeM == g.typeV &&
                        (g.typeM == kF16 || g.typeM == kBF16) && g.incv == 1 && g.len >= 8 && aligned16(g.M) &&
                        aligned16(g.v) && g.rowStride % 8 == 0 && g.strideM % 8 == 0 && g.strideV % 8 == 0;
+    static const char* overlapEnv = std::getenv("VKZB_GEMV_OVERLAP");  // 0: plain launches, no start before the prior kernel ends
+    g.overlap = overlapEnv ? std::atoi(overlapEnv) : 2;
+    static const char* kernelEnv = std::getenv("VKZB_GEMV_KERNEL");  // "rows": never the bulk-copy kernel (for experiments)
+    const BulkShape shape = vec16 && p.batch == 1 && !(kernelEnv && kernelEnv[0] == 'r') ? bulkShape(g.len) : BulkShape{};
+    if (shape.warps) return g.typeM == kBF16 ? launchBulk<true>(p, g, shape) : launchBulk<false>(p, g, shape);
     if (vec16) {
         for (int first = 0; first < p.batch; first += kMaxGridY) {
             g.batchOffset = first;
@@ -220,6 +443,12 @@ cudaError_t launchGemv(const Problem& p) {
     if (p.accType == kF64) return launchTyped<double>(p, g, rowMajor);
     if (p.accType == kS32) return launchTyped<int>(p, g, rowMajor);
     return launchTyped<float>(p, g, rowMajor);
+}
+
+int gemvDeviceStatus() {
+    unsigned status = 0;
+    if (cudaMemcpyFromSymbol(&status, g_gemvStatus, sizeof status) != cudaSuccess) return -1;
+    return status ? 16 : 0;
 }
 
 }  // namespace vkzb
