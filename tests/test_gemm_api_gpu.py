@@ -120,6 +120,10 @@ S8_CASES = [
     ("tt aligned", T, T, 160, 144, 320, 0, 1, 0, 1),
     ("tn unaligned ld (generic kernel)", T, N, 70, 33, 129, 3, 1, 1, 1),
     ("gemv int8", T, N, 300, 1, 512, 0, 1, 0, 1),
+    # few tiles and a long k: the tensor-core kernel splits along k and sums the parts through scratch memory
+    ("tn split along k, tile pairs", T, N, 512, 512, 4096, 0, 1, 0, 1),
+    ("nn split along k with beta", N, N, 256, 128, 4096, 0, 2, -1, 1),
+    ("tn split along k, ragged and batched", T, N, 200, 96, 2048, 0, 1, 1, 3),
 ]
 
 

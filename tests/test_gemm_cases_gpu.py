@@ -38,6 +38,9 @@ CASES = [
     Case("coop bf16 NT -> bf16 large", N, T, 1030, 640, 48, BF16, BF16, BF16, 0.5, 0.0, 1, C32, True),
     Case("coop f16 TN long k f32 C", T, N, 264, 136, 4104, F16, F16, F32, 1.0, 0.5, 1, C32, True),
     Case("coop f16 NN long k", N, N, 264, 200, 4104, F16, F16, F16, 1.0, 0.0, 1, C32, True),
+    Case("split along k f16 TN f32 C beta", T, N, 256, 300, 4096, F16, F16, F32, 1.0, 0.5, 1, C32, True),
+    Case("split along k bf16 NN -> bf16", N, N, 512, 256, 2048, BF16, BF16, BF16, 0.5, 0.0, 1, C32, True),
+    Case("split along k f16 TN odd rows (direct stores)", T, N, 250, 130, 3072, F16, F16, F16, 1.0, 0.0, 1, C32, True),
     Case("gemmEx f16 tn odd ld", T, N, 130, 129, 37, F16, F16, F32, 1.0, 0.25),
     Case("gemmEx bf16 -> f32", N, N, 50, 70, 90, BF16, BF16, F32, 1.0, 0.0),
     Case("gemmEx f16 x f32", T, N, 33, 31, 100, F16, F32, F32, 1.0, 0.0),

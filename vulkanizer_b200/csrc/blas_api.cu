@@ -254,8 +254,8 @@ cublasStatus_t cublasCreate_v2(cublasHandle_t* handle) {
     cudaGetDevice(&h->device);
     envLevel();
     forcedPath();
-    // scratch for split-k partial sums: 8 MiB of partial tiles behind the arrival counters, which start at zero
-    h->scratchBytes = kSplitKCounters * sizeof(unsigned) + (size_t(8) << 20);
+    // scratch for split-k partial sums: 64 MiB of partial tiles behind the arrival counters, which start at zero
+    h->scratchBytes = kSplitKCounters * sizeof(unsigned) + (size_t(64) << 20);
     if (cudaMalloc(&h->scratch, h->scratchBytes) != cudaSuccess || cudaMemset(h->scratch, 0, kSplitKCounters * sizeof(unsigned)) != cudaSuccess) {
         cudaGetLastError();
         if (h->scratch) cudaFree(h->scratch);

@@ -78,9 +78,17 @@ struct UmmaArgs {
     int batchMulA, batchMulB;       // 0: the operand is shared by every batch entry
     int debugSkipStore;             // measurement aid: run everything but the global stores
     int debugSkipLoad, debugSkipMma;  // measurement aids: main loop without its TMA loads / without its MMAs
+    int debugSplit;                  // measurement aids for the split hand-over: 1 no stores of the accumulator, 2 no fence, 4 no loads of the others
     int debugEpi;                    // measurement aids for the staged epilogue: 1 no bulk store, 2 no shared-memory writes, 4 no fence
     int tmaStore;                   // D is 16-byte aligned in every dimension: results leave through shared memory and TMA
     int mirrorCount;                // every bulk store of D is repeated into this many other buffers (peer GPUs)
+    // Split along k: a unit of work is (tile, split); the splits of a tile run on different CTAs at the same time, each
+    // over its share of the k slices. All but the last to finish leave their accumulator in scratch memory; the last adds
+    // them to its own, in split order, and writes D.
+    int splits;                     // 1: no split
+    long long totalUnits;           // totalTiles * splits
+    unsigned* splitCounters;        // arrivals per half-tile slot; all zero between launches
+    unsigned* splitPartials;        // [slot][split][column / 4][row][4] 32-bit accumulators
     EpilogueArgs epi;
 };
 
@@ -249,6 +257,16 @@ __device__ __forceinline__ void tmemLoad32(unsigned taddr, unsigned (&r)[32]) {
 }
 
 __device__ __forceinline__ void tmemWaitLoads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The reverse of a 16-column load: thread i of the warp writes row i, columns c .. c + 15; complete when it returns.
+__device__ __forceinline__ void tmemStore16(unsigned taddr, const unsigned (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+        "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 // The same load without the wait: the values may be used only after tmemWaitLoads().
 __device__ __forceinline__ void tmemLoad16Issue(unsigned taddr, unsigned (&r)[16]) {
     asm volatile(
@@ -391,6 +409,38 @@ __device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const un
     ++step;
 }
 
+// 16 columns of this lane's row: the sum over all splits in split order, `own` standing in for this CTA's split.
+// `first` holds the same columns of split `firstOther` (the lowest split that is not this CTA's), loaded by the caller
+// while it waited for TMEM; further splits are fetched here.
+template <typename Acc>
+__device__ __forceinline__ void splitSum(unsigned (&own)[kStoreCols], const uint4 (&first)[4], int firstOther, const uint4* slotBase, size_t tileV4,
+                                         int col, int splits, int split) {
+    Acc sum[kStoreCols];
+#pragma unroll
+    for (int j = 0; j < kStoreCols; ++j) sum[j] = Acc(0);
+#pragma unroll 1
+    for (int s = 0; s < splits; ++s) {
+        if (s == split) {
+#pragma unroll
+            for (int j = 0; j < kStoreCols; ++j) sum[j] += accumulatorValue<Acc>(own[j]);
+        } else {
+            uint4 t[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) t[q] = s == firstOther ? first[q] : __ldcg(slotBase + size_t(s) * tileV4 + size_t(col / 4 + q) * kBM);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                sum[4 * q] += accumulatorValue<Acc>(t[q].x), sum[4 * q + 1] += accumulatorValue<Acc>(t[q].y);
+                sum[4 * q + 2] += accumulatorValue<Acc>(t[q].z), sum[4 * q + 3] += accumulatorValue<Acc>(t[q].w);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kStoreCols; ++j) {
+        if constexpr (std::is_same_v<Acc, int>) own[j] = unsigned(sum[j]);
+        else own[j] = __float_as_uint(sum[j]);
+    }
+}
+
 // The accumulator in staged steps, kBatch at a time: a TMEM load takes long to deliver, so the
 // loads of several steps are issued together and waited for once (one load per wait left the epilogue waiting on TMEM
 // for more than half of its time).
@@ -418,6 +468,96 @@ __device__ __forceinline__ void drainAccumulatorStaged(const Epilogue<Acc>& epi,
                                         issuer, group, dbg);
         }
     }
+}
+
+// The same after a split along k, by the split that writes D: the other splits' accumulators (splitBase: this lane's row in
+// the tile's scratch slot) are added on the way, their first loads travelling while TMEM delivers. Out of line, so that its
+// registers are not the main path's.
+template <int BN, int MODE, int NB, typename Acc>
+__device__ __noinline__ void drainAccumulatorStagedSplit(const Epilogue<Acc>& epi, unsigned taddr, int rowInTile, int row, bool rowOk, int row0,
+                                                         int col0, int n, int batchEntry, const CUtensorMap* mapD, unsigned char* staging,
+                                                         unsigned& step, bool issuer, int group, const uint4* splitBase, int splits, int split) {
+    const size_t tileV4 = size_t(BN) * kBM / 4;
+    const int firstOther = split == 0 ? 1 : 0;
+#pragma unroll 1
+    for (int c = group * kStoreCols; c < BN; c += kStoreCols * kEpilogueGroups) {
+        const int count = n - (col0 + c);
+        if (count <= 0) break;
+        unsigned v[kStoreCols];
+        uint4 first[4];
+        tmemLoad16Issue(taddr + c, v);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) first[q] = __ldcg(splitBase + size_t(firstOther) * tileV4 + size_t(c / 4 + q) * kBM);
+        tmemWaitLoads();
+        splitSum<Acc>(v, first, firstOther, splitBase, tileV4, c, splits, split);
+        stageAndStore<MODE, NB>(epi, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, nullptr, 0, staging, step, issuer, group, 0);
+    }
+}
+
+// Barrier among all eight epilogue warps (hardware barrier 3).
+__device__ __forceinline__ void epilogueBarrierAll() { asm volatile("bar.sync 3, %0;" ::"n"(32 * kEpilogueWarps) : "memory"); }
+
+// The hand-over between the splits of a tile. Scratch memory holds, per half-tile slot and split, this CTA's 128 rows by BN
+// columns of 32-bit accumulators as 16-byte groups of 4 columns, lane = row: group (column / 4) of row r is uint4 number
+// (column / 4) * 128 + r, so a warp moves 512 contiguous bytes per access.
+//
+// splitDump, run by all epilogue warps once this CTA's accumulator is complete: write the accumulator to this split's place
+// and count the split in. Returns true in the split that finds all others counted already: that one sums the accumulators
+// in split order (its own from TMEM: the order of the additions does not depend on who came last, so the result is the same
+// from run to run) and writes D. The others are done with the tile. Nobody waits for anybody.
+template <int BN>
+__device__ __noinline__ bool splitDump(unsigned* counters, unsigned* partials, int splits, unsigned taddr, long long slot, int split, int quarter,
+                                       int lane, int group, volatile int* lastFlag, int dbg) {
+    constexpr int kStride = kStoreCols * kEpilogueGroups, kSteps = BN / kStride, kBatch = kSteps < 4 ? kSteps : 4;
+    uint4* mine = reinterpret_cast<uint4*>(partials + (size_t(slot) * splits + split) * (size_t(BN) * kBM)) + quarter * 32 + lane;
+#pragma unroll 1
+    for (int c = group * kStoreCols; c < BN; c += kBatch * kStride) {
+        unsigned v[kBatch][kStoreCols];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) tmemLoad16Issue(taddr + c + b * kStride, v[b]);
+        tmemWaitLoads();
+        if (!(dbg & 1))
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                __stcg(mine + size_t((c + b * kStride) / 4 + q) * kBM, make_uint4(v[b][4 * q], v[b][4 * q + 1], v[b][4 * q + 2], v[b][4 * q + 3]));
+    }
+    if (!(dbg & 2)) __threadfence();
+    epilogueBarrierAll();
+    if (threadIdx.x == 64) {
+        const unsigned before = atomicAdd(counters + slot, 1u);
+        const bool last = before == unsigned(splits - 1);
+        if (last) counters[slot] = 0;  // every split has arrived: ready for the next launch
+        __threadfence();
+        *lastFlag = last;
+    }
+    epilogueBarrierAll();
+    return *lastFlag != 0;
+}
+
+// For the store paths that read TMEM themselves (direct stores): the last split puts the sum back into TMEM first.
+template <int BN, typename Acc>
+__device__ __noinline__ void splitSumToTmem(const unsigned* partials, int splits, unsigned taddr, long long slot, int split, int quarter, int lane,
+                                            int group) {
+    const size_t tileV4 = size_t(BN) * kBM / 4;
+    const uint4* slotBase = reinterpret_cast<const uint4*>(partials) + size_t(slot) * splits * tileV4 + quarter * 32 + lane;
+    const int firstOther = split == 0 ? 1 : 0;
+#pragma unroll 1
+    for (int c = group * kStoreCols; c < BN; c += kStoreCols * kEpilogueGroups) {
+        unsigned own[kStoreCols];
+        uint4 first[4];
+        tmemLoad16Issue(taddr + c, own);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) first[q] = __ldcg(slotBase + size_t(firstOther) * tileV4 + size_t(c / 4 + q) * kBM);
+        tmemWaitLoads();
+        splitSum<Acc>(own, first, firstOther, slotBase, tileV4, c, splits, split);
+        tmemStore16(taddr + c, own);
+    }
+    // the store paths divide the columns between the groups differently: both groups' sums are in TMEM before either reads
+    tcgen05FenceBefore();
+    epilogueBarrierAll();
+    tcgen05FenceAfter();
 }
 
 // Tile number -> (batch entry, tile row, tile column). Tiles are numbered so that consecutive numbers, which run
@@ -472,11 +612,13 @@ __device__ __forceinline__ void producerLoop(const UmmaArgs& g, const CUtensorMa
     const int slices = g.numKSlices, sliceElems = g.sliceElems;
     int stage = 0;
     unsigned phase = 0;
-    for (long long tile = firstUnit; tile < g.totalTiles; tile += unitStride) {
-        const TileCoord t = tileCoord(g, tile);
+    for (long long unit = firstUnit; unit < g.totalUnits; unit += unitStride) {
+        const int split = int(unit % g.splits);
+        const TileCoord t = tileCoord(g, unit / g.splits);
         const int row0 = t.row * kTileRows + int(ctaRank) * kBM, col0 = t.col * BN + int(ctaRank) * Plan::kCtaB;
         const int batchA = t.batch * g.batchMulA, batchB = t.batch * g.batchMulB;
-        for (int ks = 0; ks < slices; ++ks) {
+        const int ksEnd = int((long long)slices * (split + 1) / g.splits);
+        for (int ks = int((long long)slices * split / g.splits); ks < ksEnd; ++ks) {
             if (!mbarWait(emptyBar + 8 * stage, phase ^ 1, abortFlag, kStatusProducerWait)) return;
             const unsigned bar = fullBarLeader + 8 * stage;
             if (leader) mbarArriveExpectTx(fullBar + 8 * stage, unsigned(Plan::kStageBytes) * (PAIR ? 2u : 1u));
@@ -522,19 +664,21 @@ __device__ __forceinline__ void mmaIssuerLoop(const UmmaArgs& g, unsigned smemBa
     int stage = 0;
     unsigned phase = 0, tileCount = 0;
     bool ok = true;
-    for (long long tile = firstUnit; ok && tile < g.totalTiles; tile += unitStride, ++tileCount) {
+    for (long long unit = firstUnit; ok && unit < g.totalUnits; unit += unitStride, ++tileCount) {
         const unsigned acc = tileCount & 1, accPhase = (tileCount >> 1) & 1;
         if (!(ok = mbarWait(accEmptyBar + 8 * acc, accPhase ^ 1, abortFlag, kStatusMmaTmemWait))) break;
         tcgen05FenceAfter();
         const unsigned tmemD = tmemBase + acc * BN;
-        for (int ks = 0; ks < slices; ++ks) {
+        const int split = int(unit % g.splits);
+        const int ksBegin = int((long long)slices * split / g.splits), ksEnd = int((long long)slices * (split + 1) / g.splits);
+        for (int ks = ksBegin; ks < ksEnd; ++ks) {
             if (!skipLoad && !(ok = mbarWait(fullBar + 8 * stage, phase, abortFlag, kStatusMmaFullWait))) break;
             tcgen05FenceAfter();
             const unsigned addrA = smemBase + stage * Plan::kStageBytes, addrB = addrA + kStageABytes;
             const unsigned long long descA = hi | (((addrA & 0x3FFFFu) >> 4) | lboA), descB = hi | (((addrB & 0x3FFFFu) >> 4) | lboB);
             if (electOne()) {
                 if (!skipMma) {
-                    ummaIssueFixed<KIND, PAIR>(tmemD, descA, descB, idesc, ks != 0 ? 1u : 0u);
+                    ummaIssueFixed<KIND, PAIR>(tmemD, descA, descB, idesc, ks != ksBegin ? 1u : 0u);
 #pragma unroll
                     for (int j = 1; j < kMmasPerStage; ++j)  // the low word cannot carry into the high one: addresses stay below 2^14 units
                         ummaIssueFixed<KIND, PAIR>(tmemD, descA + j * stepA, descB + j * stepB, idesc, 1u);
@@ -638,7 +782,8 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
         unsigned tileCount = 0, storeStep = 0;
         const bool issuer = threadIdx.x == 64 + 128 * group;  // first lane of the group's first warp owns its bulk stores
         bool ok = true;
-        for (long long tile = firstUnit; ok && tile < g.totalTiles; tile += unitStride, ++tileCount) {
+        for (long long unit = firstUnit; ok && unit < g.totalUnits; unit += unitStride, ++tileCount) {
+            const long long tile = unit / g.splits;
             const TileCoord t = tileCoord(g, tile);
             const unsigned acc = tileCount & 1, accPhase = (tileCount >> 1) & 1;
             if (lane == 0) mbarWait(accFullBar + 8 * acc, accPhase, abortFlag, kStatusEpilogueWait);  // one poller per warp
@@ -652,25 +797,50 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
             const unsigned taddr = tmemBase + acc * BN + (unsigned(quarter * 32) << 16);
             const bool rowOk = row < g.m;
             const int rowInTile = quarter * 32 + lane;
+            // After a split along k: hand the accumulator over. True when this CTA goes on to write D; `splitBase` is then
+            // set for the staged stores, which add the other splits' accumulators on their way, while for the direct
+            // stores the sum has been put back into TMEM.
+            const uint4* splitBase = nullptr;
+            const int split = int(unit % g.splits);
+            const auto handOver = [&](bool staged, auto accTag) {
+                if (g.splits == 1) return true;
+                const long long slot = PAIR ? tile * 2 + ctaRank : tile;
+                if (!splitDump<BN>(g.splitCounters, g.splitPartials, g.splits, taddr, slot, split, quarter, lane, group, abortFlag + 1, g.debugSplit)) return false;
+                if (staged && (g.debugSplit & 4)) return true;
+                if (staged) splitBase = reinterpret_cast<const uint4*>(g.splitPartials) + size_t(slot) * g.splits * (size_t(BN) * kBM / 4) + rowInTile;
+                else splitSumToTmem<BN, decltype(accTag)>(g.splitPartials, g.splits, taddr, slot, split, quarter, lane, group);
+                return true;
+            };
             if (g.kind == kKindI8) {
                 Epilogue<int> epi;
                 epi.init(g.epi, t.batch);
-                if (g.tmaStore && epi.mode == kStoreS32 && !g.debugSkipStore)
-                    drainAccumulatorStaged<BN, kStoreS32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
-                else
+                const bool staged = g.tmaStore && epi.mode == kStoreS32 && !g.debugSkipStore;
+                if (!handOver(staged, int(0))) {
+                    // another split of this tile writes D
+                } else if (staged) {
+                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreS32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else drainAccumulatorStaged<BN, kStoreS32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
+                } else {
                     drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
+                }
             } else {
                 Epilogue<float> epi;
                 epi.init(g.epi, t.batch);
-                const bool staged = g.tmaStore && !g.debugSkipStore;
-                if (staged && epi.mode == kStoreF32)
-                    drainAccumulatorStaged<BN, kStoreF32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
-                else if (staged && epi.mode == kStoreF16)
-                    drainAccumulatorStaged<BN, kStoreF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
-                else if (staged && epi.mode == kStoreBF16)
-                    drainAccumulatorStaged<BN, kStoreBF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
-                else
+                const bool staged = g.tmaStore && !g.debugSkipStore && epi.mode != kStoreSlow;
+                if (!handOver(staged, float(0))) {
+                    // another split of this tile writes D
+                } else if (staged && epi.mode == kStoreF32) {
+                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else drainAccumulatorStaged<BN, kStoreF32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
+                } else if (staged && epi.mode == kStoreF16) {
+                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else drainAccumulatorStaged<BN, kStoreF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
+                } else if (staged && epi.mode == kStoreBF16) {
+                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreBF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else drainAccumulatorStaged<BN, kStoreBF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
+                } else {
                     drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
+                }
             }
             tcgen05FenceBefore();
             __syncwarp();
@@ -798,12 +968,12 @@ cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtenso
     }
     countLaunch();
     if (!PAIR) {
-        const unsigned grid = unsigned(std::min<long long>(g.totalTiles, d.sms));
+        const unsigned grid = unsigned(std::min<long long>(g.totalUnits, d.sms));
         ummaGemmKernel<BN, PAIR, WIDE><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(g, mapA, mapB, mapD, mirrors);
         return cudaGetLastError();
     }
     cudaLaunchConfig_t config{};
-    config.gridDim = dim3(2u * unsigned(std::min<long long>(g.totalTiles, d.clusters[slot])));
+    config.gridDim = dim3(2u * unsigned(std::min<long long>(g.totalUnits, d.clusters[slot])));
     config.blockDim = dim3(kThreads);
     config.dynamicSmemBytes = Plan::kDynamicBytes;
     config.stream = stream;
@@ -854,6 +1024,8 @@ cudaError_t launchUmma(const Problem& p) {
     const int mnBoxElems = kSliceBytes / es;  // an MN-major operand arrives in boxes of 128 bytes of m or n
     static const int forcedBn = [] { const char* v = std::getenv("VKZB_UMMA_BN"); return v ? std::atoi(v) : 0; }();
     static const int forcedPair = [] { const char* v = std::getenv("VKZB_UMMA_PAIR"); return v ? std::atoi(v) : -1; }();
+    static const int forcedSplits = [] { const char* v = std::getenv("VKZB_UMMA_SPLITS"); return v ? std::atoi(v) : 0; }();
+    const long long kSlices = (p.k + kSliceBytes / es - 1) / (kSliceBytes / es);
     int bn = 0;
     bool pair = false;
     long long best = -1;
@@ -867,7 +1039,7 @@ cudaError_t launchUmma(const Problem& p) {
             const long long units = (long long)((p.m + (usePair ? 255 : 127)) / (usePair ? 256 : 128)) * ((p.n + cand - 1) / cand) * p.batch;
             const long long slots = usePair ? pairClusters() : d.sms;
             // plus a fixed cost per tile, in k slices: filling the pipeline and the accumulator hand-over (dearer between two CTAs)
-            const long long slicesPerTile = (p.k + kSliceBytes / es - 1) / (kSliceBytes / es) + (usePair ? 6 : 3);
+            const long long slicesPerTile = kSlices + (usePair ? 6 : 3);
             const long long cost = (units + slots - 1) / slots * slicesPerTile * (kBM + ctaB);
             if (best < 0 || cost < best) best = cost, bn = cand, pair = usePair != 0;
         }
@@ -885,6 +1057,29 @@ cudaError_t launchUmma(const Problem& p) {
     g.tilesM = tilesM, g.tilesN = (p.n + bn - 1) / bn;
     g.groupM = pair ? 8 : 16;  // about as many tile rows as tile columns among the tiles in flight
     g.totalTiles = (long long)g.tilesM * g.tilesN * p.batch;
+    // Splitting along k through the handle's scratch memory. Measured, it pays for a small result with a long k, where the
+    // tiles leave most SMs idle (4096 x 16 x 11008 f16: 50 -> 27 us; 512 x 512 x 16384 int8: 37 -> 19 us), and costs
+    // time once the accumulators that travel through scratch memory are megabytes (4096 x 512 x 11008: 31 -> 43 us; that
+    // main loop is bound by fetching its operands, which a split does not speed up). So: results of at most 2 MiB of
+    // accumulators, all units in one wave, at least 8 k slices per split, as many splits (up to 4) as that allows.
+    int splits = 1;
+    {
+        const long long halfTiles = g.totalTiles * (pair ? 2 : 1), slots = pair ? pairClusters() : d.sms;
+        const size_t room = p.scratch && p.scratchBytes > kSplitKCounters * sizeof(unsigned) ? p.scratchBytes - kSplitKCounters * sizeof(unsigned) : 0;
+        const auto allowed = [&](int s) {
+            return p.mirrorCount == 0 && kSlices / s >= 8 && halfTiles <= kSplitKCounters && size_t(halfTiles) * s * bn * kBM * 4 <= room;
+        };
+        if (forcedSplits > 1) {
+            if (allowed(forcedSplits)) splits = forcedSplits;
+        } else if (!forcedSplits && (long long)p.m * p.n * p.batch * 4 <= (2 << 20)) {
+            for (int s = 4; s > 1 && splits == 1; --s)
+                if (g.totalTiles * s <= slots && allowed(s)) splits = s;
+        }
+    }
+    g.splits = splits;
+    g.totalUnits = g.totalTiles * splits;
+    g.splitCounters = static_cast<unsigned*>(p.scratch);
+    g.splitPartials = static_cast<unsigned*>(p.scratch) + kSplitKCounters;
     g.sliceElems = kSliceBytes / es;
     g.numKSlices = (p.k + g.sliceElems - 1) / g.sliceElems;
     g.kind = kind;
@@ -913,6 +1108,7 @@ cudaError_t launchUmma(const Problem& p) {
     g.debugSkipStore = skipStore || (debugBits & 1);
     g.debugSkipLoad = (debugBits & 2) != 0, g.debugSkipMma = (debugBits & 4) != 0;
     g.debugEpi = (debugBits >> 5) & 7;
+    g.debugSplit = (debugBits >> 8) & 7;
 
     CUtensorMap mapA, mapB;
     const long long batchA = g.batchMulA ? p.batch : 1, batchB = g.batchMulB ? p.batch : 1;
@@ -955,8 +1151,8 @@ cudaError_t launchUmma(const Problem& p) {
 
     static const bool logChoice = [] { const char* v = std::getenv("VKZB_LOG"); return v && !std::strcmp(v, "debug"); }();
     if (logChoice)
-        std::fprintf(stderr, "vkzb: umma tile %d x %d%s, %lld tiles, %d k slices, %s store\n", pair ? 256 : 128, bn, pair ? (wide ? " (two-CTA pairs, wide epilogue)" : " (two-CTA pairs)") : (wide ? " (wide epilogue)" : ""),
-                     g.totalTiles, g.numKSlices, g.tmaStore ? "TMA" : "direct");
+        std::fprintf(stderr, "vkzb: umma tile %d x %d%s, %lld tiles, %d k slices in %d splits, %s store\n", pair ? 256 : 128, bn, pair ? (wide ? " (two-CTA pairs, wide epilogue)" : " (two-CTA pairs)") : (wide ? " (wide epilogue)" : ""),
+                     g.totalTiles, g.numKSlices, splits, g.tmaStore ? "TMA" : "direct");
     if (wide) {
         if (pair) return bn == 256 ? launchWith<256, true, true>(g, mapA, mapB, mapD, mirrors, 8, p.stream) : launchWith<128, true, true>(g, mapA, mapB, mapD, mirrors, 9, p.stream);
         if (bn == 256) return launchWith<256, false, true>(g, mapA, mapB, mapD, mirrors, 5, p.stream);
