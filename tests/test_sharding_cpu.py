@@ -7,7 +7,7 @@ from pathlib import Path
 
 import pytest
 
-from vulkanizer_b200.multi_gpu_bench import column_chunks, round_widths
+from vulkanizer_b200.multi_gpu_bench import column_chunks, round_widths, shard
 
 ROOT = Path(__file__).resolve().parents[1]
 
@@ -30,6 +30,14 @@ def test_partition_covers_every_column_once_in_gather_order(n, ranks):
     assert sum(per_rank) == n
 
 
+@pytest.mark.parametrize("units, ranks", [(256, 1), (256, 2), (256, 8), (256, 3), (5, 8), (0, 4)])
+def test_batch_entries_are_dealt_in_contiguous_shares_that_differ_by_at_most_one(units, ranks):
+    shares = [shard(units, ranks, r) for r in range(ranks)]
+    assert shares[0][0] == 0 and sum(c for _, c in shares) == units
+    assert all(a[0] + a[1] == b[0] for a, b in zip(shares, shares[1:]))
+    assert max(c for _, c in shares) - min(c for _, c in shares) <= 1
+
+
 def test_rounds_are_uniform_so_each_gather_hides_behind_the_next_product():
     assert round_widths(32768, 8) == [512] * 8
     assert round_widths(32768, 4) == [1024] * 8
@@ -47,7 +55,7 @@ WORKER = r'''
 import os, sys, hashlib
 sys.path.insert(0, sys.argv[1])
 import torch.distributed as dist
-from vulkanizer_b200.multi_gpu_bench import column_chunks, round_widths
+from vulkanizer_b200.multi_gpu_bench import column_chunks, round_widths, shard
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 dist.init_process_group("gloo", rank=rank, world_size=world)
 box = [bytes(range(128)) if rank == 0 else None]          # stands in for ncclGetUniqueId on rank 0

@@ -61,7 +61,127 @@ def column_chunks(n: int, ranks: int, widths=None):
     return rounds
 
 
+def shard(units: int, ranks: int, rank: int):
+    """First unit and number of units of `rank` when `units` independent units are dealt to `ranks` ranks in contiguous shares
+    that differ by at most one (the shape of k0zi/Vulkanizer's partOf, src/cublas/cublas.cpp:542-546)."""
+    first = units * rank // ranks
+    return first, units * (rank + 1) // ranks - first
+
+
+def run_batch_sharded(args):
+    """The batched attention-score product (256 entries of 1024 x 1024 x 128, fp16 in, fp32 out) with its batch entries dealt
+    to the ranks: entries [r * 256 / G, (r + 1) * 256 / G) on rank r, operands resident per shard, no data-path collective
+    (k0zi/Vulkanizer cuts batches the same way, src/cublas/cublas.cpp:542-546). Time = common start to the last rank done."""
+    import torch
+    import torch.distributed as dist
+
+    from bench import WORKLOADS, ClockSampler, measured_peaks, physical_gpu_index, FALLBACK_PEAKS, host_operand
+    from vulkanizer_b200 import capi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.cuda.set_device(local)
+    torch.zeros(1, device="cuda")
+    name = "cfg4_f16_tn_batched_qk"
+    spec = WORKLOADS[name]
+    m, n, k, batch = spec["m"], spec["n"], spec["k"], spec["batch"]
+    first, count = shard(batch, world, rank)
+    sA, sB, sC = k * m, k * n, m * n
+    # the rank's own entries of the same seeded operands every rank count would produce
+    hostA = host_operand(torch, spec, sA * count, first * sA)
+    hostB = host_operand(torch, spec, sB * count, batch * sA + first * sB)
+    hostC = torch.empty(sC * count, dtype=torch.float32).pin_memory()
+    copies = max(2, int(2 * (126 << 20) // max(1, (sA + sB) * 2 * count + sC * 4 * count)) + 2)  # more than L2 between reuses
+    dAs = [hostA.cuda() for _ in range(copies)]
+    dBs = [hostB.cuda() for _ in range(copies)]
+    dCs = [torch.zeros(sC * count, dtype=torch.float32, device="cuda") for _ in range(copies)]
+    blas = capi.Cublas()
+    stream = torch.cuda.Stream()
+    blas.set_stream(stream.cuda_stream)
+
+    def call(i):
+        blas.gemm_strided_batched_ex(capi.OP_T, capi.OP_N, m, n, k, spec["alpha"], dAs[i % copies].data_ptr(), capi.CUDA_R_16F, k, sA,
+                                     dBs[i % copies].data_ptr(), capi.CUDA_R_16F, k, sB, spec["beta"], dCs[i % copies].data_ptr(),
+                                     capi.CUDA_R_32F, m, sC, count, capi.COMPUTE_32F)
+
+    warmup = max(3, args.warmup)
+    with torch.cuda.stream(stream):
+        for i in range(warmup):
+            call(i)
+        stream.synchronize()
+    launches0 = blas.launch_count()
+    sampler = ClockSampler(physical_gpu_index(local))
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    with torch.cuda.stream(stream):
+        start.record(stream)
+        for i in range(args.steps):
+            call(i)
+        stop.record(stream)
+        stream.synchronize()
+    dist.barrier()
+    t1 = time.time()
+    clocks = sampler.stop(t0, t1)
+    ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    launches = blas.launch_count() - launches0
+    assert blas.device_status() == 0
+
+    def step_e2e():
+        dAs[0].copy_(hostA, non_blocking=True)
+        dBs[0].copy_(hostB, non_blocking=True)
+        call(0)
+        hostC.copy_(dCs[0], non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    with torch.cuda.stream(stream):
+        step_e2e()
+        stream.synchronize()
+        dist.barrier()
+        start.record(stream)
+        for _ in range(e2e_steps):
+            step_e2e()
+        stop.record(stream)
+        stream.synchronize()
+    e2e_ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64)
+    dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        peaks, kind = measured_peaks()
+        flops = 2.0 * m * n * k * batch
+        per_step_ms = float(ms.item()) / args.steps
+        algorithmic = (sA + sB) * 2 * batch + sC * 4 * batch
+        peak = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+        achieved = algorithmic / world / (per_step_ms * 1e-3) / 1e9  # per GPU: each shard is bound by its own HBM
+        line = {
+            "metric": "gemm_tflops", "value": flops / (per_step_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": per_step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic",
+            "config": {"workload": name, "call": "cublasGemmStridedBatchedEx", "opA": "T", "opB": "N", "m": m, "n": n, "k": k, "batch": batch,
+                       "a_b_type": "f16", "c_type": "f32", "alpha": spec["alpha"], "beta": 0.0, "seed": spec["seed"],
+                       "parallelism": f"batch-sharded x{world}", "entries_per_rank": count, "collective": "none",
+                       "l2": f"{copies} rotating operand sets per rank, no flush", "timing": "back-to-back calls, common start, max over ranks"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": f"{kind}: device copy bandwidth, per GPU", "kernel": "ummaGemmKernel", "kernel_ms": per_step_ms,
+                         "algorithmic_bytes": algorithmic // world},
+            "e2e": {"value": flops * e2e_steps / (float(e2e_ms.item()) * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": (sA + sB) * 2 * batch, "d2h_bytes_per_step": sC * 4 * batch},
+            "gpu_launches": launches * world, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    blas.destroy()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def run(args):
+    if args.workload == "cfg4_f16_tn_batched_qk":
+        return run_batch_sharded(args)
     import torch
     import torch.distributed as dist
 
