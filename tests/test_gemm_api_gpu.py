@@ -297,3 +297,27 @@ def test_operand_shared_by_every_batch_entry(cuda, blas):
     a = av.reshape(m, k).astype(np.float64)
     want = np.stack([(a @ bv.reshape(batch, n, k)[e].astype(np.float64).T).T for e in range(batch)])
     assert np.allclose(dC.download().reshape(batch, n, m), want, atol=1e-4)
+
+
+@pytest.mark.gpu
+def test_split_along_k_gives_the_same_bits_every_time(cuda, blas):
+    """A product that the tensor-core kernel splits along k (one tile pair, 128 k slices) sums its parts in split order, whichever
+    part finishes last: twenty runs give one result, bit for bit, and it matches the fp64 reference."""
+    import torch
+    m, n, k = 256, 256, 8192
+    A, av = orc.fill_lcg("f16", m * k, 31)
+    B, bv = orc.fill_lcg("f16", n * k, 32)
+    dA, dB = DeviceBuffer(cuda, A), DeviceBuffer(cuda, B)
+    first = None
+    for _ in range(20):
+        dC = DeviceBuffer(cuda, np.zeros(m * n, dtype=np.float32))
+        blas.gemm_ex(T, N, m, n, k, 1.0, dA.ptr, capi.CUDA_R_16F, k, dB.ptr, capi.CUDA_R_16F, k, 0.0, dC.ptr, capi.CUDA_R_32F, m)
+        got = dC.download()
+        assert blas.last_path() == capi.PATH_UMMA
+        if first is None:
+            first = got
+            want = (av.reshape(m, k).astype(np.float64) @ bv.reshape(n, k).astype(np.float64).T).T.reshape(-1)
+            assert np.max(np.abs(got - want) / np.maximum(1.0, np.abs(want))) <= 2e-3
+        else:
+            assert np.array_equal(got.view(np.uint32), first.view(np.uint32))
+    assert blas.device_status() == 0
