@@ -256,6 +256,19 @@ __device__ __forceinline__ void tmemLoad32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// 32 columns without the wait: the values may be used only after tmemWaitLoads().
+__device__ __forceinline__ void tmemLoad32Issue(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmemWaitLoads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // The reverse of a 16-column load: thread i of the warp writes row i, columns c .. c + 15; complete when it returns.
 __device__ __forceinline__ void tmemStore16(unsigned taddr, const unsigned (&r)[16]) {
@@ -358,14 +371,14 @@ __device__ __forceinline__ void drainAccumulator(const Epilogue<Acc>& epi, unsig
 // stores cannot. Two buffers per group alternate: a buffer is rewritten only after the bulk store that read it two steps
 // earlier has finished reading.
 // One staged step: 16 columns of this warp's rows, already in registers, through a shared-memory buffer to a bulk store.
-template <int MODE, int NB, typename Acc>
-__device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const unsigned (&v)[kStoreCols], int rowInTile, int row, bool rowOk,
+template <int MODE, int NB, int COLS, typename Acc>
+__device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const unsigned (&v)[COLS], int rowInTile, int row, bool rowOk,
                                               int row0, int col, int count, int batchEntry, const CUtensorMap* mapD, const MirrorMaps* mirrors,
                                               int mirrorCount, unsigned char* staging, unsigned& step, bool issuer, int group, int dbg) {
     using Elem = std::conditional_t<MODE == kStoreF32, float, std::conditional_t<MODE == kStoreS32, int,
                  std::conditional_t<MODE == kStoreF16, __half, __nv_bfloat16>>>;
     const Acc alpha = epi.alpha, beta = epi.beta;
-    Elem* buf = reinterpret_cast<Elem*>(staging + (step % NB + NB * group) * kStagingBufferBytes) + rowInTile;
+    Elem* buf = reinterpret_cast<Elem*>(staging + (step % NB + NB * group) * (kBM * COLS * 4)) + rowInTile;
     if constexpr (NB < 3) {  // two buffers: the one about to be rewritten is checked right here, and announced by a barrier
         if (issuer) tmaStoreWaitRead<1>();
         epilogueBarrier(group);
@@ -374,7 +387,7 @@ __device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const un
         if (epi.readC && rowOk) {
             const Elem* cin = reinterpret_cast<const Elem*>(epi.C) + (row + col * epi.ldc);
 #pragma unroll
-            for (int j = 0; j < kStoreCols; ++j) {
+            for (int j = 0; j < COLS; ++j) {
                 Acc r = alpha * accumulatorValue<Acc>(v[j]);
                 if (j < count) {
                     if constexpr (MODE == kStoreF32 || MODE == kStoreS32) r += beta * Acc(cin[j * epi.ldc]);
@@ -387,7 +400,7 @@ __device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const un
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < kStoreCols; ++j) {
+            for (int j = 0; j < COLS; ++j) {
                 const Acc r = alpha * accumulatorValue<Acc>(v[j]);
                 if constexpr (MODE == kStoreF32 || MODE == kStoreS32) buf[j * kBM] = r;
                 else if constexpr (MODE == kStoreF16) buf[j * kBM] = __float2half_rn(r);
@@ -464,9 +477,30 @@ __device__ __forceinline__ void drainAccumulatorStaged(const Epilogue<Acc>& epi,
         for (int b = 0; b < kBatch; ++b) {
             const int count = n - (col0 + c + b * kStride);
             if (count > 0)
-                stageAndStore<MODE, NB>(epi, v[b], rowInTile, row, rowOk, row0, col0 + c + b * kStride, count, batchEntry, mapD, mirrors, mirrorCount, staging, step,
+                stageAndStore<MODE, NB, kStoreCols>(epi, v[b], rowInTile, row, rowOk, row0, col0 + c + b * kStride, count, batchEntry, mapD, mirrors, mirrorCount, staging, step,
                                         issuer, group, dbg);
         }
+    }
+}
+
+// The wide-epilogue kernels (few k slices per tile, bound by writing D) take 32 columns per step: half as many barriers,
+// fences and bulk stores per tile, four staging buffers of 16 KiB per group (measured on 256 x [1024 x 1024 x 128], fp32 D:
+// 16 columns x 6 buffers 287 us, 32 x 3 243 us, 32 x 4 223 us; 16 x 6 with the next TMEM load in flight during a step 272 us).
+constexpr int kWideStoreCols = 32, kWideBuffers = 4;
+template <int BN, int MODE, typename Acc>
+__device__ __forceinline__ void drainAccumulatorStagedWide(const Epilogue<Acc>& epi, unsigned taddr, int rowInTile, int row, bool rowOk, int row0,
+                                                           int col0, int n, int batchEntry, const CUtensorMap* mapD, const MirrorMaps* mirrors,
+                                                           int mirrorCount, unsigned char* staging, unsigned& step, bool issuer, int group,
+                                                           int dbg) {
+#pragma unroll 1
+    for (int c = group * kWideStoreCols; c < BN; c += kWideStoreCols * kEpilogueGroups) {
+        const int count = n - (col0 + c);
+        if (count <= 0) break;
+        unsigned v[kWideStoreCols];
+        tmemLoad32Issue(taddr + c, v);
+        tmemWaitLoads();
+        stageAndStore<MODE, kWideBuffers, kWideStoreCols>(epi, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, mirrors, mirrorCount, staging,
+                                                         step, issuer, group, dbg);
     }
 }
 
@@ -490,7 +524,7 @@ __device__ __noinline__ void drainAccumulatorStagedSplit(const Epilogue<Acc>& ep
         for (int q = 0; q < 4; ++q) first[q] = __ldcg(splitBase + size_t(firstOther) * tileV4 + size_t(c / 4 + q) * kBM);
         tmemWaitLoads();
         splitSum<Acc>(v, first, firstOther, splitBase, tileV4, c, splits, split);
-        stageAndStore<MODE, NB>(epi, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, nullptr, 0, staging, step, issuer, group, 0);
+        stageAndStore<MODE, NB, kStoreCols>(epi, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, nullptr, 0, staging, step, issuer, group, 0);
     }
 }
 
@@ -579,14 +613,14 @@ __device__ __forceinline__ TileCoord tileCoord(const UmmaArgs& g, long long tile
 // PAIR: the kernel runs as clusters of two CTAs that share each MMA (M = 256): a CTA stages its own 128 rows of A and only
 // half of the tile's B columns, so a k slice costs it (128 + BN / 2) rows of 128 bytes from L2 instead of (128 + BN).
 // WIDE: for products with few k slices per tile the time goes into writing D, not into the main loop. Such launches
-// trade ring stages for epilogue buffers: six staging buffers per warp group instead of two keep enough bulk stores in
-// flight to cover the latency of a store (with two, a group can have 16 KiB on its way, about half of what HBM takes).
+// trade ring stages for epilogue buffers: 64 KiB of staging buffers per warp group instead of 16 KiB keep enough bulk stores
+// in flight to cover the latency of a store, and the steps are 32 columns wide (drainAccumulatorStagedWide).
 template <int BN, bool PAIR, bool WIDE>
 struct SmemPlan {
     static constexpr int kCtaB = PAIR ? BN / 2 : BN;  // B rows (tile columns) this CTA stages
     static constexpr int kStageBBytes = kCtaB * kSliceBytes;
     static constexpr int kStageBytes = kStageABytes + kStageBBytes;
-    static constexpr int kStagingBuffers = WIDE ? 6 : 2;  // per epilogue group
+    static constexpr int kStagingBuffers = WIDE ? 8 : 2;  // per epilogue group, in units of 8 KiB (the wide form uses them as four of 16 KiB)
     static constexpr int kStagingBytes = kEpilogueGroups * kStagingBuffers * kStagingBufferBytes;
     static constexpr int kOverhead = 1024 /* alignment slack */ + 256 /* barriers */;
     static constexpr int kStages = (kSmemTotal - kStagingBytes - kOverhead) / kStageBytes > 12 ? 12 : (kSmemTotal - kStagingBytes - kOverhead) / kStageBytes;
@@ -819,6 +853,7 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                     // another split of this tile writes D
                 } else if (staged) {
                     if (splitBase) drainAccumulatorStagedSplit<BN, kStoreS32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else if constexpr (WIDE) drainAccumulatorStagedWide<BN, kStoreS32>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                     else drainAccumulatorStaged<BN, kStoreS32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                 } else {
                     drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
@@ -831,12 +866,15 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                     // another split of this tile writes D
                 } else if (staged && epi.mode == kStoreF32) {
                     if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else if constexpr (WIDE) drainAccumulatorStagedWide<BN, kStoreF32>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                     else drainAccumulatorStaged<BN, kStoreF32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                 } else if (staged && epi.mode == kStoreF16) {
                     if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else if constexpr (WIDE) drainAccumulatorStagedWide<BN, kStoreF16>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                     else drainAccumulatorStaged<BN, kStoreF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                 } else if (staged && epi.mode == kStoreBF16) {
                     if (splitBase) drainAccumulatorStagedSplit<BN, kStoreBF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else if constexpr (WIDE) drainAccumulatorStagedWide<BN, kStoreBF16>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                     else drainAccumulatorStaged<BN, kStoreBF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                 } else {
                     drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
@@ -1067,7 +1105,7 @@ cudaError_t launchUmma(const Problem& p) {
         const long long halfTiles = g.totalTiles * (pair ? 2 : 1), slots = pair ? pairClusters() : d.sms;
         const size_t room = p.scratch && p.scratchBytes > kSplitKCounters * sizeof(unsigned) ? p.scratchBytes - kSplitKCounters * sizeof(unsigned) : 0;
         const auto allowed = [&](int s) {
-            return p.mirrorCount == 0 && kSlices / s >= 8 && halfTiles <= kSplitKCounters && size_t(halfTiles) * s * bn * kBM * 4 <= room;
+            return !wide && p.mirrorCount == 0 && kSlices / s >= 8 && halfTiles <= kSplitKCounters && size_t(halfTiles) * s * bn * kBM * 4 <= room;
         };
         if (forcedSplits > 1) {
             if (allowed(forcedSplits)) splits = forcedSplits;
@@ -1136,7 +1174,7 @@ cudaError_t launchUmma(const Problem& p) {
                                        : e.typeD == kS32 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
         const cuuint64_t dims[3] = {cuuint64_t(p.m), cuuint64_t(p.n), cuuint64_t(p.batch)};
         const cuuint64_t strides[2] = {cuuint64_t(e.ldd) * esD, p.batch > 1 ? cuuint64_t(e.strideD) * esD : cuuint64_t(e.ldd) * esD * cuuint64_t(p.n)};
-        const cuuint32_t box[3] = {cuuint32_t(kBM), cuuint32_t(kStoreCols), 1}, ones[3] = {1, 1, 1};
+        const cuuint32_t box[3] = {cuuint32_t(kBM), cuuint32_t(wide ? kWideStoreCols : kStoreCols), 1}, ones[3] = {1, 1, 1};
         const auto encode = [&](CUtensorMap* map, void* base) {
             return encodeTiled()(map, dt, 3, base, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
