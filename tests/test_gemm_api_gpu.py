@@ -321,3 +321,50 @@ def test_split_along_k_gives_the_same_bits_every_time(cuda, blas):
         else:
             assert np.array_equal(got.view(np.uint32), first.view(np.uint32))
     assert blas.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_matrix_vector_chain_between_copies_in_a_graph(cuda):
+    """The matrix-vector kernel is launched so that it may start while the kernel before it drains. A chain y1 = M1 x,
+    y2 = M2 y1, y3 = M3 y2 with a fill before it and a device-to-device copy in the middle, captured and replayed, must give
+    what stream order gives: every link reads what the link before it wrote."""
+    torch = cuda
+    n = 1024
+    rng = np.random.default_rng(7)
+    Ms = [torch.from_numpy((rng.standard_normal((n, n)) / 32).astype(np.float16)).cuda() for _ in range(3)]
+    x = torch.from_numpy(rng.standard_normal(n).astype(np.float16)).cuda()
+    ys = [torch.zeros(n, dtype=torch.float16, device="cuda") for _ in range(4)]
+    b = capi.Cublas()
+    stream = torch.cuda.Stream()
+    b.set_stream(stream.cuda_stream)
+
+    def link(M, v, y):  # y = M v with M row-major n x n, i.e. op(A) = A^T of the column-major n x n matrix holding M^T
+        b.gemm_ex(T, N, n, 1, n, 1.0, M.data_ptr(), capi.CUDA_R_16F, n, v.data_ptr(), capi.CUDA_R_16F, n, 0.0, y.data_ptr(), capi.CUDA_R_16F, n)
+        assert b.last_path() == capi.PATH_GEMV
+
+    def chain():
+        ys[0].fill_(0)
+        link(Ms[0], x, ys[0])
+        link(Ms[1], ys[0], ys[1])
+        ys[2].copy_(ys[1])
+        link(Ms[2], ys[2], ys[3])
+
+    with torch.cuda.stream(stream):
+        chain()
+        stream.synchronize()
+        eager = ys[3].clone()
+        for y in ys:
+            y.zero_()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            chain()
+        for _ in range(5):
+            graph.replay()
+        stream.synchronize()
+    want = x.double()
+    for M in Ms:
+        want = (M.double() @ want).half().double()
+    assert torch.equal(ys[3], eager)
+    assert torch.allclose(ys[3].double(), want, rtol=2e-2, atol=2e-2)
+    assert b.device_status() == 0
+    b.destroy()

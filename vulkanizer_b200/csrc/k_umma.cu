@@ -44,8 +44,8 @@ constexpr int kEpilogueGroups = 2;             // each group of 4 warps covers t
 constexpr int kEpilogueWarps = 4 * kEpilogueGroups;
 constexpr int kThreads = 32 * (2 + kEpilogueWarps);
 constexpr int kSmemTotal = 227 * 1024;      // dynamic shared memory a CTA may have on sm_100
-constexpr int kStoreCols = 16;                // columns per staged epilogue step
-constexpr int kStagingBufferBytes = kBM * kStoreCols * 4;             // 128 rows x 16 columns of 4 bytes
+constexpr int kStoreCols = 16;                // columns per chunk of the split hand-over
+constexpr int kStagingBufferBytes = kBM * kStoreCols * 4;             // the unit of epilogue staging memory: 128 rows x 16 columns of 4 bytes
 constexpr unsigned long long kWaitLimitNs = 4000000000ull;  // a wait longer than this is a lost signal
 
 enum UmmaKind : int { kKindF16 = 0, kKindTf32 = 1, kKindI8 = 2 };
@@ -422,84 +422,57 @@ __device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const un
     ++step;
 }
 
-// 16 columns of this lane's row: the sum over all splits in split order, `own` standing in for this CTA's split.
+// COLS columns of this lane's row: the sum over all splits in split order, `own` standing in for this CTA's split.
 // `first` holds the same columns of split `firstOther` (the lowest split that is not this CTA's), loaded by the caller
 // while it waited for TMEM; further splits are fetched here.
-template <typename Acc>
-__device__ __forceinline__ void splitSum(unsigned (&own)[kStoreCols], const uint4 (&first)[4], int firstOther, const uint4* slotBase, size_t tileV4,
+template <typename Acc, int COLS>
+__device__ __forceinline__ void splitSum(unsigned (&own)[COLS], const uint4 (&first)[COLS / 4], int firstOther, const uint4* slotBase, size_t tileV4,
                                          int col, int splits, int split) {
-    Acc sum[kStoreCols];
+    Acc sum[COLS];
 #pragma unroll
-    for (int j = 0; j < kStoreCols; ++j) sum[j] = Acc(0);
+    for (int j = 0; j < COLS; ++j) sum[j] = Acc(0);
 #pragma unroll 1
     for (int s = 0; s < splits; ++s) {
         if (s == split) {
 #pragma unroll
-            for (int j = 0; j < kStoreCols; ++j) sum[j] += accumulatorValue<Acc>(own[j]);
+            for (int j = 0; j < COLS; ++j) sum[j] += accumulatorValue<Acc>(own[j]);
         } else {
-            uint4 t[4];
+            uint4 t[COLS / 4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) t[q] = s == firstOther ? first[q] : __ldcg(slotBase + size_t(s) * tileV4 + size_t(col / 4 + q) * kBM);
+            for (int q = 0; q < COLS / 4; ++q) t[q] = s == firstOther ? first[q] : __ldcg(slotBase + size_t(s) * tileV4 + size_t(col / 4 + q) * kBM);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < COLS / 4; ++q) {
                 sum[4 * q] += accumulatorValue<Acc>(t[q].x), sum[4 * q + 1] += accumulatorValue<Acc>(t[q].y);
                 sum[4 * q + 2] += accumulatorValue<Acc>(t[q].z), sum[4 * q + 3] += accumulatorValue<Acc>(t[q].w);
             }
         }
     }
 #pragma unroll
-    for (int j = 0; j < kStoreCols; ++j) {
+    for (int j = 0; j < COLS; ++j) {
         if constexpr (std::is_same_v<Acc, int>) own[j] = unsigned(sum[j]);
         else own[j] = __float_as_uint(sum[j]);
     }
 }
 
-// The accumulator in staged steps, kBatch at a time: a TMEM load takes long to deliver, so the
-// loads of several steps are issued together and waited for once (one load per wait left the epilogue waiting on TMEM
-// for more than half of its time).
+// The accumulator in staged steps of 32 columns (one TMEM load, one barrier, one fence and one bulk store per step). Measured on
+// 256 x [1024 x 1024 x 128] with fp32 D, where the launch is bound by writing D: 16-column steps through 6 buffers per group
+// took 287 us, 32 x 3 243 us, 32 x 4 223 us (16 x 6 with the next TMEM load in flight during a step: 272 us). The kernels for
+// long k use two buffers per group and keep the shared memory for ring stages; with 32 columns per step they also stay
+// within their registers (the 16-column form, two loads per wait, spilled 700 bytes).
+constexpr int kStepCols = 32, kWideBuffers = 4;
 template <int BN, int MODE, int NB, typename Acc>
-__device__ __forceinline__ void drainAccumulatorStaged(const Epilogue<Acc>& epi, unsigned taddr, int rowInTile, int row, bool rowOk,
-                                                       int row0, int col0, int n, int batchEntry, const CUtensorMap* mapD,
-                                                       const MirrorMaps* mirrors, int mirrorCount, unsigned char* staging, unsigned& step,
-                                                       bool issuer, int group, int dbg) {
-    constexpr int kStride = kStoreCols * kEpilogueGroups;  // columns between two steps of one group
-    constexpr int kSteps = BN / kStride;                   // steps of one group per tile
-    constexpr int kBatch = kSteps < 2 ? kSteps : 2;  // four at a time spill registers and run three times slower
-#pragma unroll 1
-    for (int c = group * kStoreCols; c < BN; c += kBatch * kStride) {
-        if (n - (col0 + c) <= 0) break;
-        unsigned v[kBatch][kStoreCols];
-#pragma unroll
-        for (int b = 0; b < kBatch; ++b)
-            if (n - (col0 + c + b * kStride) > 0) tmemLoad16Issue(taddr + c + b * kStride, v[b]);
-        tmemWaitLoads();
-#pragma unroll
-        for (int b = 0; b < kBatch; ++b) {
-            const int count = n - (col0 + c + b * kStride);
-            if (count > 0)
-                stageAndStore<MODE, NB, kStoreCols>(epi, v[b], rowInTile, row, rowOk, row0, col0 + c + b * kStride, count, batchEntry, mapD, mirrors, mirrorCount, staging, step,
-                                        issuer, group, dbg);
-        }
-    }
-}
-
-// The wide-epilogue kernels (few k slices per tile, bound by writing D) take 32 columns per step: half as many barriers,
-// fences and bulk stores per tile, four staging buffers of 16 KiB per group (measured on 256 x [1024 x 1024 x 128], fp32 D:
-// 16 columns x 6 buffers 287 us, 32 x 3 243 us, 32 x 4 223 us; 16 x 6 with the next TMEM load in flight during a step 272 us).
-constexpr int kWideStoreCols = 32, kWideBuffers = 4;
-template <int BN, int MODE, typename Acc>
-__device__ __forceinline__ void drainAccumulatorStagedWide(const Epilogue<Acc>& epi, unsigned taddr, int rowInTile, int row, bool rowOk, int row0,
+__device__ __forceinline__ void drainAccumulatorStaged(const Epilogue<Acc>& epi, unsigned taddr, int rowInTile, int row, bool rowOk, int row0,
                                                            int col0, int n, int batchEntry, const CUtensorMap* mapD, const MirrorMaps* mirrors,
                                                            int mirrorCount, unsigned char* staging, unsigned& step, bool issuer, int group,
                                                            int dbg) {
 #pragma unroll 1
-    for (int c = group * kWideStoreCols; c < BN; c += kWideStoreCols * kEpilogueGroups) {
+    for (int c = group * kStepCols; c < BN; c += kStepCols * kEpilogueGroups) {
         const int count = n - (col0 + c);
         if (count <= 0) break;
-        unsigned v[kWideStoreCols];
+        unsigned v[kStepCols];
         tmemLoad32Issue(taddr + c, v);
         tmemWaitLoads();
-        stageAndStore<MODE, kWideBuffers, kWideStoreCols>(epi, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, mirrors, mirrorCount, staging,
+        stageAndStore<MODE, NB, kStepCols>(epi, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, mirrors, mirrorCount, staging,
                                                          step, issuer, group, dbg);
     }
 }
@@ -514,17 +487,17 @@ __device__ __noinline__ void drainAccumulatorStagedSplit(const Epilogue<Acc>& ep
     const size_t tileV4 = size_t(BN) * kBM / 4;
     const int firstOther = split == 0 ? 1 : 0;
 #pragma unroll 1
-    for (int c = group * kStoreCols; c < BN; c += kStoreCols * kEpilogueGroups) {
+    for (int c = group * kStepCols; c < BN; c += kStepCols * kEpilogueGroups) {
         const int count = n - (col0 + c);
         if (count <= 0) break;
-        unsigned v[kStoreCols];
-        uint4 first[4];
-        tmemLoad16Issue(taddr + c, v);
+        unsigned v[kStepCols];
+        uint4 first[kStepCols / 4];
+        tmemLoad32Issue(taddr + c, v);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) first[q] = __ldcg(splitBase + size_t(firstOther) * tileV4 + size_t(c / 4 + q) * kBM);
+        for (int q = 0; q < kStepCols / 4; ++q) first[q] = __ldcg(splitBase + size_t(firstOther) * tileV4 + size_t(c / 4 + q) * kBM);
         tmemWaitLoads();
-        splitSum<Acc>(v, first, firstOther, splitBase, tileV4, c, splits, split);
-        stageAndStore<MODE, NB, kStoreCols>(epi, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, nullptr, 0, staging, step, issuer, group, 0);
+        splitSum<Acc, kStepCols>(v, first, firstOther, splitBase, tileV4, c, splits, split);
+        stageAndStore<MODE, NB, kStepCols>(epi, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, nullptr, 0, staging, step, issuer, group, 0);
     }
 }
 
@@ -585,7 +558,7 @@ __device__ __noinline__ void splitSumToTmem(const unsigned* partials, int splits
 #pragma unroll
         for (int q = 0; q < 4; ++q) first[q] = __ldcg(slotBase + size_t(firstOther) * tileV4 + size_t(c / 4 + q) * kBM);
         tmemWaitLoads();
-        splitSum<Acc>(own, first, firstOther, slotBase, tileV4, c, splits, split);
+        splitSum<Acc, kStoreCols>(own, first, firstOther, slotBase, tileV4, c, splits, split);
         tmemStore16(taddr + c, own);
     }
     // the store paths divide the columns between the groups differently: both groups' sums are in TMEM before either reads
@@ -614,13 +587,13 @@ __device__ __forceinline__ TileCoord tileCoord(const UmmaArgs& g, long long tile
 // half of the tile's B columns, so a k slice costs it (128 + BN / 2) rows of 128 bytes from L2 instead of (128 + BN).
 // WIDE: for products with few k slices per tile the time goes into writing D, not into the main loop. Such launches
 // trade ring stages for epilogue buffers: 64 KiB of staging buffers per warp group instead of 16 KiB keep enough bulk stores
-// in flight to cover the latency of a store, and the steps are 32 columns wide (drainAccumulatorStagedWide).
+// in flight to cover the latency of a store, and the steps are 32 columns wide (drainAccumulatorStaged).
 template <int BN, bool PAIR, bool WIDE>
 struct SmemPlan {
     static constexpr int kCtaB = PAIR ? BN / 2 : BN;  // B rows (tile columns) this CTA stages
     static constexpr int kStageBBytes = kCtaB * kSliceBytes;
     static constexpr int kStageBytes = kStageABytes + kStageBBytes;
-    static constexpr int kStagingBuffers = WIDE ? 8 : 2;  // per epilogue group, in units of 8 KiB (the wide form uses them as four of 16 KiB)
+    static constexpr int kStagingBuffers = WIDE ? 2 * kWideBuffers : 4;  // per epilogue group, in units of 8 KiB: four or two steps of 32 columns
     static constexpr int kStagingBytes = kEpilogueGroups * kStagingBuffers * kStagingBufferBytes;
     static constexpr int kOverhead = 1024 /* alignment slack */ + 256 /* barriers */;
     static constexpr int kStages = (kSmemTotal - kStagingBytes - kOverhead) / kStageBytes > 12 ? 12 : (kSmemTotal - kStagingBytes - kOverhead) / kStageBytes;
@@ -852,9 +825,8 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                 if (!handOver(staged, int(0))) {
                     // another split of this tile writes D
                 } else if (staged) {
-                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreS32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
-                    else if constexpr (WIDE) drainAccumulatorStagedWide<BN, kStoreS32>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
-                    else drainAccumulatorStaged<BN, kStoreS32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
+                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreS32, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else drainAccumulatorStaged<BN, kStoreS32, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                 } else {
                     drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
                 }
@@ -865,17 +837,14 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                 if (!handOver(staged, float(0))) {
                     // another split of this tile writes D
                 } else if (staged && epi.mode == kStoreF32) {
-                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
-                    else if constexpr (WIDE) drainAccumulatorStagedWide<BN, kStoreF32>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
-                    else drainAccumulatorStaged<BN, kStoreF32, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
+                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF32, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else drainAccumulatorStaged<BN, kStoreF32, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                 } else if (staged && epi.mode == kStoreF16) {
-                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
-                    else if constexpr (WIDE) drainAccumulatorStagedWide<BN, kStoreF16>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
-                    else drainAccumulatorStaged<BN, kStoreF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
+                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF16, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else drainAccumulatorStaged<BN, kStoreF16, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                 } else if (staged && epi.mode == kStoreBF16) {
-                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreBF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
-                    else if constexpr (WIDE) drainAccumulatorStagedWide<BN, kStoreBF16>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
-                    else drainAccumulatorStaged<BN, kStoreBF16, Plan::kStagingBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
+                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreBF16, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else drainAccumulatorStaged<BN, kStoreBF16, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
                 } else {
                     drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
                 }
@@ -1174,7 +1143,7 @@ cudaError_t launchUmma(const Problem& p) {
                                        : e.typeD == kS32 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
         const cuuint64_t dims[3] = {cuuint64_t(p.m), cuuint64_t(p.n), cuuint64_t(p.batch)};
         const cuuint64_t strides[2] = {cuuint64_t(e.ldd) * esD, p.batch > 1 ? cuuint64_t(e.strideD) * esD : cuuint64_t(e.ldd) * esD * cuuint64_t(p.n)};
-        const cuuint32_t box[3] = {cuuint32_t(kBM), cuuint32_t(wide ? kWideStoreCols : kStoreCols), 1}, ones[3] = {1, 1, 1};
+        const cuuint32_t box[3] = {cuuint32_t(kBM), cuuint32_t(kStepCols), 1}, ones[3] = {1, 1, 1};
         const auto encode = [&](CUtensorMap* map, void* base) {
             return encodeTiled()(map, dt, 3, base, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
