@@ -1058,7 +1058,8 @@ cudaError_t launchUmma(const Problem& p) {
     static const int debugBits = [] { const char* v = std::getenv("VKZB_UMMA_DEBUG"); return v ? std::atoi(v) : 0; }();
 
     // few k slices per tile: the launch is bound by writing D, so it takes the variant with more epilogue buffers
-    const bool wide = forcedWide >= 0 ? forcedWide != 0 : (p.k + kSliceBytes / es - 1) / (kSliceBytes / es) <= 16;
+    // (measured at 4096 x 4096 x k, f16: k = 512, 8 slices, 29.1 us wide against 30.7; k = 1024, 16 slices, 38.8 against 35.4)
+    const bool wide = forcedWide >= 0 ? forcedWide != 0 : (p.k + kSliceBytes / es - 1) / (kSliceBytes / es) <= 8;
     UmmaArgs g{};
     g.m = p.m, g.n = p.n, g.k = p.k, g.batch = p.batch;
     g.tilesM = tilesM, g.tilesN = (p.n + bn - 1) / bn;
