@@ -99,57 +99,77 @@ def physical_gpu_index(local: int) -> int:
 # CPU arm: the reference's own code for this path on the host cores
 # ---------------------------------------------------------------------------------------------------------------------
 
-def cpu_reference_sample(size: int = 2048, reps: int = 3):
-    """fp16 TN size^3 through the reference's staged CPU GEMM (packTransposed -> hostGemm on all cores -> epilogue),
-    or through the C restatement when the compiled reference is absent. Returns (tflops, cores, kind, sample)."""
+def reference_sample_of(workload: str):
+    """Which bounded sample of `workload` the host cores are timed on: (operand type, opA, opB, size, scale of the normal
+    inputs). The reference's CPU GEMM takes f32, f16 and bf16; int8 operands go in as their values in f32 (timing only:
+    the reference has no int8 product)."""
+    spec = WORKLOADS.get(workload)
+    if workload == "cfg5b_bf16_32768_nsharded":
+        return "bf16", "T", "N", 2048, 1.0
+    if spec is None:
+        return "f16", "T", "N", 2048, 0.02
+    kind = "f32" if spec["ab"] in ("s8", "f32") else spec["ab"]
+    return kind, spec["ta"], spec["tb"], 2048 if spec["call"] != "sgemm" else 512, float(spec["dist"][1]) if spec["dist"][0] == "normal" else 1.0
+
+
+def cpu_reference_sample(size: int = 2048, reps: int = 3, kind: str = "f16", ta: str = "T", tb: str = "N", scale: float = 0.02):
+    """size^3 through the reference's staged CPU GEMM (packTransposed -> hostGemm on all cores -> epilogue), or through
+    the C restatement when the compiled reference is absent. Returns (tflops, cores, kind, sample)."""
     import numpy as np
     from oracle import pyoracle as orc
     from vulkanizer_b200 import synth
 
-    a = orc.to_storage(synth.normal(1, size * size, 0.02), "f16")
-    b = orc.to_storage(synth.normal(1, size * size, 0.02, first=size * size), "f16")
+    a = orc.to_storage(synth.normal(1, size * size, scale), kind)
+    b = orc.to_storage(synth.normal(1, size * size, scale, first=size * size), kind)
     c = np.zeros(size * size, dtype=np.float32)
+    code, opa, opb = orc.TYPE_CODE[kind], int(ta == "T"), int(tb == "T")
     ref = orc.reference()
     times = []
     if ref is not None:
         cores = ref.vkref_hardware_threads()
         for _ in range(reps + 1):
             t = time.perf_counter()
-            used = ref.vkref_staged_gemm(1, 0, size, size, size, 1.0, a.ctypes.data, 1, size, b.ctypes.data, 1, size, 0.0, c.ctypes.data, 0, size)
+            used = ref.vkref_staged_gemm(opa, opb, size, size, size, 1.0, a.ctypes.data, code, size, b.ctypes.data, code, size, 0.0, c.ctypes.data, 0, size)
             times.append(time.perf_counter() - t)
-        kind, cores = "reference", used or cores
+        how, cores = "reference", used or cores
     else:
         size = min(size, 512)
         a, b, c = a[:size * size], b[:size * size], c[:size * size]
         for _ in range(2):
             t = time.perf_counter()
-            orc.gemm_f32(True, False, size, size, size, 1, 1.0, a, "f16", size, 0, b, "f16", size, 0, 0.0, c, "f32", size, 0)
+            orc.gemm_f32(bool(opa), bool(opb), size, size, size, 1, 1.0, a, kind, size, 0, b, kind, size, 0, 0.0, c, "f32", size, 0)
             times.append(time.perf_counter() - t)
-        kind, cores = "port", 1
+        how, cores = "port", 1
     best = statistics.median(times[1:])
-    return 2.0 * size ** 3 / best / 1e12, cores, kind, f"fp16 TN {size}^3, alpha=1 beta=0, median of {len(times) - 1} runs after one warm-up"
+    return (2.0 * size ** 3 / best / 1e12, cores, how,
+            f"{kind} {ta}{tb} {size}^3, alpha=1 beta=0, median of {len(times) - 1} runs after one warm-up")
 
 
 def run_reference_arm(args):
+    """The reference's own CPU implementation of the path on the host cores, on a bounded sample of the workload the other arm
+    runs with the same arguments (one GPU: --workload or the headline configuration; several: the column-sharded product)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    workload = args.workload or ("cfg5b_bf16_32768_nsharded" if max(world, args.gpus) > 1 else "cfg2_f16_tn_8192")
+    kind, ta, tb, size, scale = reference_sample_of(workload)
     times = []
-    tf = cores = kind = sample = None
+    tf = cores = how = sample = None
     for _ in range(max(1, args.warmup // 3)):
-        cpu_reference_sample(1024, 1)
+        cpu_reference_sample(min(size, 1024), 1, kind, ta, tb, scale)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        tf, cores, kind, sample = cpu_reference_sample(2048, 1)
+        tf, cores, how, sample = cpu_reference_sample(size, 1, kind, ta, tb, scale)
         times.append(tf)
         if time.perf_counter() - t0 > 120:
             break
     value = statistics.median(times)
     line = {"impl": "reference", "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": len(times),
-            "warmup": args.warmup, "ms_per_step": 2.0 * 2048 ** 3 / value / 1e9, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "cfg2_f16_tn_8192 (bounded sample: 2048^3 per step on the host cores)", "m": 2048, "n": 2048, "k": 2048},
-            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+            "warmup": args.warmup, "ms_per_step": 2.0 * size ** 3 / value / 1e9, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": WORKLOADS.get(workload, {}).get("ab", "bf16"), "data": "synthetic",
+            "config": {"workload": f"{workload} (bounded sample: {size}^3 per step on the host cores)", "m": size, "n": size, "k": size},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": how, "sample": sample},
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
