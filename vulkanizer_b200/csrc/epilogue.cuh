@@ -88,8 +88,10 @@ struct Epilogue {
     long long ldd, ldc;
     Acc alpha, beta;
     int typeD, typeC, typeBias, activation, roundBeforeBias;
-    int mode;  // StoreMode
+    int mode;       // StoreMode
+    int typedMode;  // the StoreMode D and C alone ask for: what `mode` would be without bias, activation and the extra rounding
     bool readC;
+    bool post;      // bias, activation or the extra rounding follow alpha * acc + beta * C
 
     __device__ __forceinline__ void init(const EpilogueArgs& e, long long batchEntry) {
         const double a = readScalar(e.scalars.alphaDev, e.scalars.alphaHost, e.scalars.type);
@@ -108,10 +110,21 @@ struct Epilogue {
             C = static_cast<const char*>(e.C) + batchEntry * e.strideC * dtypeSize(e.typeC);
         }
         bias = e.bias ? static_cast<const char*>(e.bias) + batchEntry * e.biasStride * dtypeSize(e.typeBias) : nullptr;
-        const bool extras = bias || activation != kActNone || roundBeforeBias || (readC && typeC != typeD);
-        if constexpr (std::is_same_v<Acc, double>) mode = kStoreF64;
-        else if constexpr (std::is_same_v<Acc, int>) mode = typeD == kS32 && !extras ? kStoreS32 : kStoreSlow;
-        else mode = extras ? kStoreSlow : typeD == kF32 ? kStoreF32 : typeD == kF16 ? kStoreF16 : typeD == kBF16 ? kStoreBF16 : kStoreSlow;
+        post = bias || activation != kActNone || roundBeforeBias;
+        const bool mixed = readC && typeC != typeD;
+        if constexpr (std::is_same_v<Acc, double>) typedMode = kStoreF64;
+        else if constexpr (std::is_same_v<Acc, int>) typedMode = typeD == kS32 && !mixed ? kStoreS32 : kStoreSlow;
+        else typedMode = mixed ? kStoreSlow : typeD == kF32 ? kStoreF32 : typeD == kF16 ? kStoreF16 : typeD == kBF16 ? kStoreBF16 : kStoreSlow;
+        mode = post && !std::is_same_v<Acc, double> ? kStoreSlow : typedMode;
+    }
+
+    // What follows alpha * acc + beta * C when `post` is set, for one result of row `row` (float accumulators).
+    __device__ __forceinline__ float finish(float v, float biasValue) const {
+        if (roundBeforeBias) v = roundTo(v, typeD);
+        v += biasValue;
+        if (activation == kActRelu) v = fmaxf(v, 0.0f);
+        else if (activation == kActGelu) v = geluTanh(v);
+        return v;
     }
 
     // The general form: any C / D / bias types, bias, activation.

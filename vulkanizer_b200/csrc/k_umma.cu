@@ -501,6 +501,39 @@ __device__ __noinline__ void drainAccumulatorStagedSplit(const Epilogue<Acc>& ep
     }
 }
 
+// The same with a bias vector, an activation or the extra rounding after alpha * acc + beta * C (cublasLtMatmul epilogues): the
+// finished values go through the staged store as they are (alpha 1, no C). Out of line like the split form.
+template <int BN, int MODE, int NB>
+__device__ __noinline__ void drainAccumulatorStagedPost(const Epilogue<float>& epi, unsigned taddr, int rowInTile, int row, bool rowOk, int row0,
+                                                        int col0, int n, int batchEntry, const CUtensorMap* mapD, const MirrorMaps* mirrors,
+                                                        int mirrorCount, unsigned char* staging, unsigned& step, bool issuer, int group) {
+    using Elem = std::conditional_t<MODE == kStoreF32, float, std::conditional_t<MODE == kStoreF16, __half, __nv_bfloat16>>;
+    Epilogue<float> plain = epi;
+    plain.alpha = 1.0f, plain.readC = false;
+    const float biasValue = epi.bias && rowOk ? loadAs<float>(epi.bias, row, epi.typeBias) : 0.0f;
+#pragma unroll 1
+    for (int c = group * kStepCols; c < BN; c += kStepCols * kEpilogueGroups) {
+        const int count = n - (col0 + c);
+        if (count <= 0) break;
+        unsigned v[kStepCols];
+        tmemLoad32Issue(taddr + c, v);
+        tmemWaitLoads();
+        const Elem* cin = reinterpret_cast<const Elem*>(epi.C) + (row + (long long)(col0 + c) * epi.ldc);
+#pragma unroll
+        for (int j = 0; j < kStepCols; ++j) {
+            float r = epi.alpha * __uint_as_float(v[j]);
+            if (epi.readC && rowOk && j < count) {
+                if constexpr (MODE == kStoreF32) r += epi.beta * cin[j * epi.ldc];
+                else if constexpr (MODE == kStoreF16) r += epi.beta * __half2float(cin[j * epi.ldc]);
+                else r += epi.beta * __bfloat162float(cin[j * epi.ldc]);
+            }
+            v[j] = __float_as_uint(epi.finish(r, biasValue));
+        }
+        stageAndStore<MODE, NB, kStepCols>(plain, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, mirrors, mirrorCount, staging, step, issuer,
+                                           group, 0);
+    }
+}
+
 // Barrier among all eight epilogue warps (hardware barrier 3).
 __device__ __forceinline__ void epilogueBarrierAll() { asm volatile("bar.sync 3, %0;" ::"n"(32 * kEpilogueWarps) : "memory"); }
 
@@ -834,8 +867,17 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                 Epilogue<float> epi;
                 epi.init(g.epi, t.batch);
                 const bool staged = g.tmaStore && !g.debugSkipStore && epi.mode != kStoreSlow;
+                // bias, activation, extra rounding: staged as well when C and D alone would be (after a split the sum goes back to TMEM first)
+                const bool stagedPost = g.tmaStore && !g.debugSkipStore && epi.post && epi.typedMode != kStoreSlow;
+                constexpr int kBuffers = WIDE ? kWideBuffers : 2;
                 if (!handOver(staged, float(0))) {
                     // another split of this tile writes D
+                } else if (stagedPost && epi.typedMode == kStoreF32) {
+                    drainAccumulatorStagedPost<BN, kStoreF32, kBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
+                } else if (stagedPost && epi.typedMode == kStoreF16) {
+                    drainAccumulatorStagedPost<BN, kStoreF16, kBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
+                } else if (stagedPost && epi.typedMode == kStoreBF16) {
+                    drainAccumulatorStagedPost<BN, kStoreBF16, kBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else if (staged && epi.mode == kStoreF32) {
                     if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF32, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
                     else drainAccumulatorStaged<BN, kStoreF32, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
