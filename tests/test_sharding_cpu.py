@@ -82,3 +82,15 @@ def test_two_gloo_ranks_agree_on_partition_and_id(tmp_path):
     for r, p in enumerate(procs):
         out, _ = p.communicate(timeout=120)
         assert p.returncode == 0 and f"rank {r} ok" in out, out[-2000:]
+
+
+def test_reference_arm_samples_the_workload_the_other_arm_runs():
+    sys.path.insert(0, str(ROOT))
+    import bench
+
+    assert bench.reference_sample_of("cfg2_f16_tn_8192") == ("f16", "T", "N", 2048, 0.02)
+    assert bench.reference_sample_of("cfg2_bf16_tn_8192")[0] == "bf16"
+    assert bench.reference_sample_of("cfg5b_bf16_32768_nsharded") == ("bf16", "T", "N", 2048, 1.0)
+    kind, ta, tb, size, _ = bench.reference_sample_of("cfg1_sgemm_nn_512")
+    assert (kind, ta, tb, size) == ("f32", "N", "N", 512)
+    assert bench.reference_sample_of("cfg3_s8_tn_11008x512x4096")[0] == "f32"  # int8 values as f32: timing only
