@@ -99,10 +99,10 @@ struct TileLoader {
 // counts itself in; the last one to arrive for a tile adds the partial tiles in slice order, so the result does not depend
 // on which CTA came last, applies alpha and beta, and resets the counter for the next call.
 template <int BM, int BN, bool A_MCONTIG, bool B_NCONTIG, bool SPLITK = false>
-__global__ void __launch_bounds__(kThreads) sgemmKernel(const SgemmArgs g) {
+__global__ void __launch_bounds__(kThreads, 2) sgemmKernel(const SgemmArgs g) {
     constexpr int TM = BM / 16, TN = BN / 16;        // 8 x 8 for 128 x 128, 4 x 4 for 64 x 64
     constexpr int GM = TM / 4, GN = TN / 4;          // float4 groups per thread
-    constexpr int BK = BM >= 128 ? 8 : 16;           // k slice per shared-memory fill
+    constexpr int BK = 16;                           // k slice per shared-memory fill
     constexpr int kPitchA = BM + 4, kPitchB = BN + 4;
     __shared__ __align__(16) float sA[2][BK * kPitchA];
     __shared__ __align__(16) float sB[2][BK * kPitchB];
