@@ -73,6 +73,7 @@ struct UmmaArgs {
     unsigned kStepA, kStepB;        // descriptor start-address advance per MMA, in 16-byte units
     int mnMajorA, mnMajorB;
     int boxesA, boxesB;             // TMA boxes per stage
+    int chunkedA, chunkedB;         // the MN-major operand has a 4-d map: all its boxes of a stage arrive with one instruction
     int boxBytesA, boxBytesB;
     int boxElemsA, boxElemsB;       // elements of m / n per box when MN-major
     int batchMulA, batchMulB;       // 0: the operand is shared by every batch entry
@@ -230,6 +231,19 @@ __device__ __forceinline__ void tmaLoad3dPair(unsigned dst, const CUtensorMap* m
     asm volatile(
         "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(map)), "r"(clusterBar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+// The same for a 4-d map (an operand contiguous along m or n, viewed as chunks of 128 bytes: see encodeChunked).
+__device__ __forceinline__ void tmaLoad4d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tmaLoad4dPair(unsigned dst, const CUtensorMap* map, unsigned clusterBar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(map)), "r"(clusterBar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
 // Arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far have completed.
@@ -672,12 +686,20 @@ __device__ __forceinline__ void producerLoop(const UmmaArgs& g, const CUtensorMa
                 load(dstA, mapA, k0, row0, batchA);
                 load(dstB, mapB, k0, col0, batchB);
             } else {
-                if (g.mnMajorA) {
+                const auto loadChunks = [&](unsigned dst, const CUtensorMap* map, int mn0, int elems, int batchEntry) {
+                    if constexpr (PAIR) tmaLoad4dPair(dst, map, bar, 0, k0, mn0 / elems, batchEntry);
+                    else tmaLoad4d(dst, map, bar, 0, k0, mn0 / elems, batchEntry);
+                };
+                if (g.chunkedA) {
+                    loadChunks(dstA, mapA, row0, g.boxElemsA, batchA);
+                } else if (g.mnMajorA) {
                     for (int b = 0; b < g.boxesA; ++b) load(dstA + b * g.boxBytesA, mapA, row0 + b * g.boxElemsA, k0, batchA);
                 } else {
                     load(dstA, mapA, k0, row0, batchA);
                 }
-                if (g.mnMajorB) {
+                if (g.chunkedB) {
+                    loadChunks(dstB, mapB, col0, g.boxElemsB, batchB);
+                } else if (g.mnMajorB) {
                     for (int b = 0; b < g.boxesB; ++b) load(dstB + b * g.boxBytesB, mapB, col0 + b * g.boxElemsB, k0, batchB);
                 } else {
                     load(dstB, mapB, k0, col0, batchB);
@@ -978,6 +1000,27 @@ bool encodeOperand(CUtensorMap* map, const void* base, int type, long long inner
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// A 4-d map over an operand that is contiguous along m or n (`inner`), for extents that are whole chunks of 128 bytes:
+// (element in chunk, k, chunk, batch entry). A box of `chunks` chunks by `boxOuter` rows of k lands in shared memory chunk after
+// chunk, each as boxOuter rows of 128 bytes: the layout the per-chunk 3-d boxes produce, with one instruction instead of
+// `chunks` (the producer's instruction count, not its bytes, is what a stage of MN-major operands costs more).
+bool encodeChunked(CUtensorMap* map, const void* base, int type, long long inner, long long outer, long long ld, long long batch,
+                   long long batchStride, unsigned chunkElems, unsigned boxOuter, unsigned chunks) {
+    const int es = elemSizeOf(type);
+    const CUtensorMapDataType dt = type == kF16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                   : type == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                   : type == kF32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                   : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const cuuint64_t dims[4] = {cuuint64_t(chunkElems), cuuint64_t(outer), cuuint64_t(inner / chunkElems), cuuint64_t(batch)};
+    const cuuint64_t strides[3] = {cuuint64_t(ld) * es, cuuint64_t(chunkElems) * es,
+                                   batch > 1 ? cuuint64_t(batchStride) * es : cuuint64_t(ld) * es * cuuint64_t(outer)};
+    const cuuint32_t box[4] = {chunkElems, boxOuter, chunks, 1};
+    const cuuint32_t elemStrides[4] = {1, 1, 1, 1};
+    return encodeTiled()(map, dt, 4, const_cast<void*>(base), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int ummaKindOf(const Problem& p) {
     if (p.typeA != p.typeB) return -1;
     if ((p.typeA == kF16 || p.typeA == kBF16) && p.accType == kF32) return kKindF16;
@@ -1162,10 +1205,16 @@ cudaError_t launchUmma(const Problem& p) {
 
     CUtensorMap mapA, mapB;
     const long long batchA = g.batchMulA ? p.batch : 1, batchB = g.batchMulB ? p.batch : 1;
-    const bool okA = g.mnMajorA ? encodeOperand(&mapA, p.A, p.typeA, p.m, p.k, p.lda, batchA, p.strideA, g.boxElemsA, g.sliceElems)
-                                : encodeOperand(&mapA, p.A, p.typeA, p.k, p.m, p.lda, batchA, p.strideA, g.sliceElems, kBM);
-    const bool okB = g.mnMajorB ? encodeOperand(&mapB, p.B, p.typeB, p.n, p.k, p.ldb, batchB, p.strideB, g.boxElemsB, g.sliceElems)
-                                : encodeOperand(&mapB, p.B, p.typeB, p.k, p.n, p.ldb, batchB, p.strideB, g.sliceElems, ctaB);
+    static const bool noChunks = std::getenv("VKZB_UMMA_NO_CHUNKS") != nullptr;
+    g.chunkedA = g.mnMajorA && !noChunks && g.boxesA > 1 && p.m % g.boxElemsA == 0;
+    g.chunkedB = g.mnMajorB && !noChunks && g.boxesB > 1 && p.n % g.boxElemsB == 0;
+    // (a driver that refuses the 4-d view leaves the operand on its per-chunk boxes)
+    if (g.chunkedA && !encodeChunked(&mapA, p.A, p.typeA, p.m, p.k, p.lda, batchA, p.strideA, g.boxElemsA, g.sliceElems, g.boxesA)) g.chunkedA = 0;
+    if (g.chunkedB && !encodeChunked(&mapB, p.B, p.typeB, p.n, p.k, p.ldb, batchB, p.strideB, g.boxElemsB, g.sliceElems, g.boxesB)) g.chunkedB = 0;
+    const bool okA = g.chunkedA || (g.mnMajorA ? encodeOperand(&mapA, p.A, p.typeA, p.m, p.k, p.lda, batchA, p.strideA, g.boxElemsA, g.sliceElems)
+                                               : encodeOperand(&mapA, p.A, p.typeA, p.k, p.m, p.lda, batchA, p.strideA, g.sliceElems, kBM));
+    const bool okB = g.chunkedB || (g.mnMajorB ? encodeOperand(&mapB, p.B, p.typeB, p.n, p.k, p.ldb, batchB, p.strideB, g.boxElemsB, g.sliceElems)
+                                               : encodeOperand(&mapB, p.B, p.typeB, p.k, p.n, p.ldb, batchB, p.strideB, g.sliceElems, ctaB));
     if (!okA || !okB) return cudaErrorInvalidValue;
 
     // D through TMA when every address the bulk stores start at is 16-byte aligned; otherwise direct stores.
@@ -1201,8 +1250,8 @@ cudaError_t launchUmma(const Problem& p) {
 
     static const bool logChoice = [] { const char* v = std::getenv("VKZB_LOG"); return v && !std::strcmp(v, "debug"); }();
     if (logChoice)
-        std::fprintf(stderr, "vkzb: umma tile %d x %d%s, %lld tiles, %d k slices in %d splits, %s store\n", pair ? 256 : 128, bn, pair ? (wide ? " (two-CTA pairs, wide epilogue)" : " (two-CTA pairs)") : (wide ? " (wide epilogue)" : ""),
-                     g.totalTiles, g.numKSlices, splits, g.tmaStore ? "TMA" : "direct");
+        std::fprintf(stderr, "vkzb: umma tile %d x %d%s, %lld tiles, %d k slices in %d splits, %s store, chunked loads A %d B %d\n", pair ? 256 : 128, bn, pair ? (wide ? " (two-CTA pairs, wide epilogue)" : " (two-CTA pairs)") : (wide ? " (wide epilogue)" : ""),
+                     g.totalTiles, g.numKSlices, splits, g.tmaStore ? "TMA" : "direct", g.chunkedA, g.chunkedB);
     if (wide) {
         if (pair) return bn == 256 ? launchWith<256, true, true>(g, mapA, mapB, mapD, mirrors, 8, p.stream) : launchWith<128, true, true>(g, mapA, mapB, mapD, mirrors, 9, p.stream);
         if (bn == 256) return launchWith<256, false, true>(g, mapA, mapB, mapD, mirrors, 5, p.stream);
