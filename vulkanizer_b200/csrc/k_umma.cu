@@ -379,12 +379,12 @@ __device__ __forceinline__ void drainAccumulator(const Epilogue<Acc>& epi, unsig
     }
 }
 
-// The same through shared memory: each step's 128 x 16 block is laid out like the column-major D tile it belongs to
+// The same through shared memory: each step's 128 x COLS block is laid out like the column-major D tile it belongs to
 // (column pitch 128 elements; lane = row, so the writes are conflict-free), then one thread hands it to TMA, which
 // writes full lines, clips rows and columns outside D, and keeps many stores in flight where four warps of scalar
-// stores cannot. Two buffers per group alternate: a buffer is rewritten only after the bulk store that read it two steps
-// earlier has finished reading.
-// One staged step: 16 columns of this warp's rows, already in registers, through a shared-memory buffer to a bulk store.
+// stores cannot. The NB buffers of a group take turns: a buffer is rewritten only after the bulk store that read it NB
+// steps earlier has finished reading.
+// One staged step: COLS columns of this warp's rows, already in registers, through a shared-memory buffer to a bulk store.
 template <int MODE, int NB, int COLS, typename Acc>
 __device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const unsigned (&v)[COLS], int rowInTile, int row, bool rowOk,
                                               int row0, int col, int count, int batchEntry, const CUtensorMap* mapD, const MirrorMaps* mirrors,
