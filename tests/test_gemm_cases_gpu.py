@@ -65,6 +65,11 @@ CASES = [
     Case("gemv bulk bf16 fewer rows than SMs", T, N, 3, 1, 24064, BF16, BF16, BF16, 1.0, 1.0, 1, C32, True),
     Case("gemv bulk f16 many short rows", T, N, 5000, 1, 520, F16, F16, F16, 1.0, 0.0, 1, C32, True),
     Case("gemv bulk m=1 NN f16", N, N, 1, 500, 1024, F16, F16, F16, 1.0, 0.0, 1, C32, True),
+    Case("two columns on the matrix-vector kernel, f16", T, N, 300, 2, 4096, F16, F16, F16, 1.0, 0.0, 1, C32, True),
+    Case("two columns on the matrix-vector kernel, bf16 -> f32, beta", T, N, 1000, 2, 11008, BF16, BF16, F32, 0.5, -1.0, 1, C32, True),
+    Case("two columns on the matrix-vector kernel, ragged piece", T, N, 150, 2, 4104, F16, F16, F16, -1.0, 0.0, 1, C32, True),
+    Case("two columns on the matrix-vector kernel, short rows", T, N, 5000, 2, 520, F16, F16, F32, 1.0, 0.0, 1, C32, True),
+    Case("three columns stay on the tensor cores", T, N, 300, 3, 4096, F16, F16, F16, 1.0, 0.0, 1, C32, True),
     Case("gemv pointer batched", T, N, 100, 1, 64, F32, F32, F32, 1.0, 0.0, -6),
     Case("gemv m=1 pointer batched", N, N, 1, 100, 64, F32, F32, F32, 1.0, 0.0, -4),
     Case("k = 0 scales C", N, N, 10, 10, 0, F32, F32, F32, 1.0, 3.0),
@@ -104,13 +109,22 @@ def test_reference_case_table(cuda, blas, case):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("case", [c for c in CASES if c.aligned and c.type_a == c.type_b and c.type_a != F32 and c.m > 1 and c.n > 1],
+@pytest.mark.parametrize("case", [c for c in CASES if c.aligned and c.type_a == c.type_b and c.type_a != F32 and c.m > 1 and c.n > 2],
                          ids=str)
 def test_aligned_16bit_cases_run_on_tensor_cores(cuda, blas, case):
     """What the reference sends to its cooperative-matrix or f16 kernels (16-byte aligned f16 / bf16 operands) must take
     the tcgen05 kernel here, in every transpose combination, not the CUDA-core fallback."""
     *_, path = run_case(cuda, blas, case)
     assert path == capi.PATH_UMMA
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [c for c in CASES if c.name.startswith("two columns on the matrix-vector kernel")], ids=str)
+def test_two_column_products_stream_the_matrix_once(cuda, blas, case):
+    """n = 2 with a k-contiguous 16-bit A is bound by reading A: it takes the matrix-vector kernel with two right-hand sides."""
+    got, want, tol, before, path = run_case(cuda, blas, case)
+    check(case, got, want, tol, before)
+    assert path == capi.PATH_GEMV
 
 
 @pytest.mark.gpu

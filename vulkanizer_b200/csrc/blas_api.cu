@@ -148,7 +148,7 @@ cublasStatus_t dispatch(cublasHandle_t h, Problem& p) {
     if (p.k == 0) {
         path = VKZB_PATH_SCALE;
         err = launchScale(p);
-    } else if (p.n == 1 || p.m == 1) {
+    } else if (p.n == 1 || p.m == 1 || (forcedPath() == 0 && p.mirrorCount == 0 && gemvTakesFewColumns(p))) {
         path = VKZB_PATH_GEMV;
         err = launchGemv(p);
     } else if (forcedPath() == VKZB_PATH_GENERIC) {

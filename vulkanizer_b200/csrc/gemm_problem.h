@@ -72,7 +72,8 @@ struct Problem {
 // Kernel families (launchers return cudaError_t; the dispatch layer maps it to a cuBLAS status).
 cudaError_t launchScale(const Problem& p);    // k = 0: D = act(beta * C + bias)
 cudaError_t launchGeneric(const Problem& p);  // any types / leading dimensions / pointer arrays
-cudaError_t launchGemv(const Problem& p);     // m = 1 or n = 1
+bool gemvTakesFewColumns(const Problem& p);   // n = 2: two right-hand sides for which the matrix-vector kernel streams A once
+cudaError_t launchGemv(const Problem& p);     // m = 1 or n = 1 (or gemvTakesFewColumns)
 bool sgemmEligible(const Problem& p);
 cudaError_t launchSgemm(const Problem& p);    // fp32 FFMA (split along k through p.scratch when the product is small)
 constexpr int kSplitKCounters = 4096;          // arrival counters at the start of split-k scratch memory

@@ -34,6 +34,8 @@ struct GemvArgs {
     int pointerArrays;
     int yIsRow;  // y^T = v^T M^T (the m = 1 case): element r of y is C(0, r)
     int batchOffset;
+    int vectors;              // 1, or kMaxVectors right-hand sides sharing one pass over M (n = 2 of a GEMM)
+    long long vectorStride;   // elements between them (ldb); result (r, j) goes to C(r, j)
     int overlap;  // bulk kernel: launched with programmatic stream serialisation (1), and asks L2 for its first rows before the wait (2)
     EpilogueArgs epi;
 };
@@ -134,6 +136,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) gemvRowsVec16(const GemvA
 // ---- bulk-copy kernel --------------------------------------------------------------------------------------------
 
 constexpr int kBulkWarps = 16;  // at most
+constexpr int kMaxVectors = 2;  // measured (4096 x n x 4096 f16): n = 2 10.8 us here against 15.5 on the tensor cores, n = 3 12.9,
+                                // n = 4 14.7, and slower than the tensor cores from n = 3 on when the rows are 11008 long
 constexpr int kPieceBytes = 8192;                   // one ring stage: a row of 4096 halves, or a piece of a longer one
 constexpr int kSharedLimit = 227 * 1024;
 constexpr unsigned long long kBulkWaitLimitNs = 2000000000ull;
@@ -183,16 +187,16 @@ __device__ __forceinline__ bool bulkWait(unsigned bar, unsigned parity) {
 // start early (this kernel does), a block becomes resident as soon as an SM has room, sets up its barriers, asks L2 for its
 // first rows and only then waits for the kernel before it to complete; every load of data comes after that wait.
 struct BulkShape {
-    int warps, stages, pieceBytes, pieces, vectorBytes, prefetchRows;
-    size_t sharedBytes() const { return size_t(vectorBytes) + size_t(warps) * stages * (pieceBytes + 8) + 8; }
+    int warps, stages, pieceBytes, pieces, vectorBytes, prefetchRows, vectors;
+    size_t sharedBytes() const { return size_t(vectorBytes) * vectors + size_t(warps) * stages * (pieceBytes + 8) + 8; }
 };
 
-template <bool BF16>
+template <bool BF16, int NV>
 __global__ void __launch_bounds__(kBulkWarps * 32) gemvRowsBulk(const GemvArgs g, const BulkShape shape) {
     extern __shared__ __align__(128) unsigned char shared[];
     const int stages = shape.stages, warps = shape.warps, pieceBytes = shape.pieceBytes, pieces = shape.pieces;
     unsigned char* vecShared = shared;
-    unsigned char* ring = shared + shape.vectorBytes;  // a multiple of 128
+    unsigned char* ring = shared + shape.vectorBytes * NV;  // a multiple of 128
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const unsigned barBase = sharedAddr(ring + size_t(warps) * stages * pieceBytes);
     const unsigned vecBar = barBase + 8u * warps * stages;
@@ -215,12 +219,13 @@ __global__ void __launch_bounds__(kBulkWarps * 32) gemvRowsBulk(const GemvArgs g
     __syncthreads();
     if (threadIdx.x == 0) {
         // the vector goes in pieces as well: one copy moves at most what the mbarrier's byte counter can take
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(vecBar), "r"(unsigned(rowBytes)) : "memory");
-        for (int at = 0; at < rowBytes; at += 8192)
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                             sharedAddr(vecShared + at)),
-                         "l"(static_cast<const char*>(g.v) + at), "r"(unsigned(min(8192, rowBytes - at))), "r"(vecBar)
-                         : "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(vecBar), "r"(unsigned(rowBytes) * NV) : "memory");
+        for (int j = 0; j < NV; ++j)
+            for (int at = 0; at < rowBytes; at += 8192)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 sharedAddr(vecShared + j * shape.vectorBytes + at)),
+                             "l"(static_cast<const char*>(g.v) + j * g.vectorStride * 2 + at), "r"(unsigned(min(8192, rowBytes - at))), "r"(vecBar)
+                             : "memory");
     }
     const int myRows = (endRow - firstRow - warp + warps - 1) / warps;  // rows firstRow + warp, + warps, ...
     if (myRows <= 0) return;
@@ -241,45 +246,58 @@ __global__ void __launch_bounds__(kBulkWarps * 32) gemvRowsBulk(const GemvArgs g
 
     Epilogue<float> epi;
     epi.init(g.epi, 0);
-    float acc[4] = {};
+    float acc[NV][4] = {};
     int piece = 0, r = 0;
     for (int item = 0; item < items; ++item) {
         const int stage = item % stages;
         if (!bulkWait(myBars + 8u * stage, unsigned(item / stages) & 1u)) return;
         const uint4* a = reinterpret_cast<const uint4*>(myRing + stage * pieceBytes);
         const uint4* x = reinterpret_cast<const uint4*>(vecShared + piece * pieceBytes);
+        const int vectorChunks = shape.vectorBytes / 16;  // uint4 between two vectors in shared memory
         const int chunks = min(pieceBytes, rowBytes - piece * pieceBytes) / 16;
+        const auto fourChunks = [&](int c0) {  // chunks c0, c0 + 32, c0 + 64, c0 + 96 of the piece against every vector
+            uint4 av[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) av[u] = a[c0 + 32 * u];
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                uint4 xv[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) xv[u] = x[j * vectorChunks + c0 + 32 * u];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[j][u] = dot8<BF16>(av[u], xv[u], acc[j][u]);
+            }
+        };
         int c = lane;
         if (chunks == kPieceBytes / 16) {
 #pragma unroll
-            for (int q = 0; q < kPieceBytes / 16 / 128; ++q) {
-                uint4 av[4], xv[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) av[u] = a[lane + 128 * q + 32 * u], xv[u] = x[lane + 128 * q + 32 * u];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) acc[u] = dot8<BF16>(av[u], xv[u], acc[u]);
-            }
+            for (int q = 0; q < kPieceBytes / 16 / 128; ++q) fourChunks(lane + 128 * q);
             c = chunks;
         }
-        for (; c + 96 < chunks; c += 128) {
-            uint4 av[4], xv[4];
+        for (; c + 96 < chunks; c += 128) fourChunks(c);
+        for (; c < chunks; c += 32) {
+            const uint4 av = a[c];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) av[u] = a[c + 32 * u], xv[u] = x[c + 32 * u];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) acc[u] = dot8<BF16>(av[u], xv[u], acc[u]);
+            for (int j = 0; j < NV; ++j) acc[j][0] = dot8<BF16>(av, x[j * vectorChunks + c], acc[j][0]);
         }
-        for (; c < chunks; c += 32) acc[0] = dot8<BF16>(a[c], x[c], acc[0]);
         __syncwarp();
         if (lane == 0 && item + stages < items) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the reads above come before the copy that overwrites them
             issue(item + stages);
         }
         if (++piece == pieces) {
-            float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+            const int row = firstRow + warp + r * warps;
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
-            if (lane == 0) storeY(epi, g.yIsRow, firstRow + warp + r * warps, sum);
-            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+            for (int j = 0; j < NV; ++j) {
+                float sum = (acc[j][0] + acc[j][1]) + (acc[j][2] + acc[j][3]);
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+                if (lane == 0) {
+                    if (NV == 1) storeY(epi, g.yIsRow, row, sum);
+                    else epi.store(row, j, sum);
+                }
+                acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+            }
             piece = 0;
             ++r;
         }
@@ -288,8 +306,9 @@ __global__ void __launch_bounds__(kBulkWarps * 32) gemvRowsBulk(const GemvArgs g
 
 // How the bulk kernel is laid out for rows of `len` 16-bit values; warps = 0 when it cannot take the shape.
 // Measured on 4096 x 4096 to 32000 x 4096: 16 warps with one stage each beat 8 x 3, 12 x 2, 20 x 1 and 24 x 1.
-BulkShape bulkShape(int len) {
+BulkShape bulkShape(int len, int vectors) {
     BulkShape shape{};
+    shape.vectors = vectors;
     if (len % 8 != 0) return shape;
     const int rowBytes = len * 2;
     shape.vectorBytes = (rowBytes + 127) / 128 * 128;
@@ -303,14 +322,14 @@ BulkShape bulkShape(int len) {
     return shape;
 }
 
-template <bool BF16>
-cudaError_t launchBulk(const Problem& p, const GemvArgs& g, const BulkShape& shape) {
+template <bool BF16, int NV>
+cudaError_t launchBulkFor(const Problem& p, const GemvArgs& g, const BulkShape& shape) {
     static bool prepared[64] = {};
     int device = 0, sms = 0;
     if (cudaError_t e = cudaGetDevice(&device); e != cudaSuccess) return e;
     if (cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device); e != cudaSuccess) return e;
     if (device < 64 && !prepared[device]) {
-        if (cudaError_t e = cudaFuncSetAttribute(gemvRowsBulk<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSharedLimit); e != cudaSuccess)
+        if (cudaError_t e = cudaFuncSetAttribute(gemvRowsBulk<BF16, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSharedLimit); e != cudaSuccess)
             return e;
         prepared[device] = true;
     }
@@ -325,7 +344,16 @@ cudaError_t launchBulk(const Problem& p, const GemvArgs& g, const BulkShape& sha
     cfg.attrs = &attr;
     cfg.numAttrs = g.overlap ? 1 : 0;
     countLaunch();
-    return cudaLaunchKernelEx(&cfg, gemvRowsBulk<BF16>, g, shape);
+    return cudaLaunchKernelEx(&cfg, gemvRowsBulk<BF16, NV>, g, shape);
+}
+
+template <bool BF16>
+cudaError_t launchBulk(const Problem& p, const GemvArgs& g, const BulkShape& shape) {
+    switch (shape.vectors) {
+    case 1: return launchBulkFor<BF16, 1>(p, g, shape);
+    case 2: return launchBulkFor<BF16, 2>(p, g, shape);
+    default: return cudaErrorInvalidValue;
+    }
 }
 
 // One warp per row, any types, rows contiguous (colStride = 1) but not necessarily aligned.
@@ -398,11 +426,35 @@ cudaError_t launchTyped(const Problem& p, GemvArgs& g, bool rowMajor) {
 
 }  // namespace
 
+// A product with two columns whose matrix the bulk-copy kernel can stream: the columns of B are two right-hand sides of one
+// pass over A. (Below about 16 columns a GEMM is bound by reading A, and the tensor-core kernel takes half as long again for
+// that pass: 4096 x n x 4096 f16 took 15.5 us for n = 2 .. 64 against 9.5 us for n = 1. More than two right-hand sides make
+// this kernel's conversions and FMAs the bound.)
+bool gemvTakesFewColumns(const Problem& p) {
+    const auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+    static const bool disabled = std::getenv("VKZB_GEMV_NO_FEW_COLUMNS") != nullptr;
+    if (disabled || p.n < 2 || p.n > kMaxVectors || p.m < 64 || p.batch != 1 || p.pointerArrays || p.accType != kF32) return false;
+    if (!p.transA || p.transB || p.typeA != p.typeB || (p.typeA != kF16 && p.typeA != kBF16)) return false;
+    if (p.k < 8 || p.k % 8 != 0 || p.lda % 8 != 0 || p.ldb % 8 != 0 || !aligned16(p.A) || !aligned16(p.B)) return false;
+    return bulkShape(p.k, p.n).warps != 0;
+}
+
 cudaError_t launchGemv(const Problem& p) {
     GemvArgs g{};
     g.len = p.k;
     g.pointerArrays = p.pointerArrays;
     g.epi = p.epi;
+    g.vectors = 1;
+    if (p.n > 1 && p.m > 1) {  // gemvTakesFewColumns(p) holds
+        g.M = p.A, g.v = p.B, g.typeM = p.typeA, g.typeV = p.typeB;
+        g.rows = p.m, g.rowStride = p.lda, g.colStride = 1, g.incv = 1, g.yIsRow = 0;
+        g.vectors = p.n, g.vectorStride = p.ldb;
+        static const char* overlapEnv = std::getenv("VKZB_GEMV_OVERLAP");
+        g.overlap = overlapEnv ? std::atoi(overlapEnv) : 2;
+        const BulkShape shape = bulkShape(g.len, g.vectors);
+        if (!shape.warps) return cudaErrorInvalidValue;
+        return g.typeM == kBF16 ? launchBulk<true>(p, g, shape) : launchBulk<false>(p, g, shape);
+    }
     // Roles as in cublas.cpp:745-757: n = 1 keeps A as the matrix; m = 1 computes C^T = op(B)^T op(A)^T.
     if (p.n == 1) {
         g.M = p.A, g.v = p.B, g.typeM = p.typeA, g.typeV = p.typeB;
@@ -427,7 +479,7 @@ cudaError_t launchGemv(const Problem& p) {
     static const char* overlapEnv = std::getenv("VKZB_GEMV_OVERLAP");  // 0: plain launches, no start before the prior kernel ends
     g.overlap = overlapEnv ? std::atoi(overlapEnv) : 2;
     static const char* kernelEnv = std::getenv("VKZB_GEMV_KERNEL");  // "rows": never the bulk-copy kernel (for experiments)
-    const BulkShape shape = vec16 && p.batch == 1 && !(kernelEnv && kernelEnv[0] == 'r') ? bulkShape(g.len) : BulkShape{};
+    const BulkShape shape = vec16 && p.batch == 1 && !(kernelEnv && kernelEnv[0] == 'r') ? bulkShape(g.len, 1) : BulkShape{};
     if (shape.warps) return g.typeM == kBF16 ? launchBulk<true>(p, g, shape) : launchBulk<false>(p, g, shape);
     if (vec16) {
         for (int first = 0; first < p.batch; first += kMaxGridY) {
