@@ -7,8 +7,20 @@
  * cublasLtMatmul computes D = act(alpha op(A) op(B) + beta C + bias) in ONE kernel: bias, ReLU and
  * tanh-GELU run in the GEMM's epilogue (the reference runs a second pass over D, cublasLt.cpp:386-412),
  * and C is read in place of D when C != D (the reference copies C into D first, cublasLt.cpp:363-378).
- * C is never written. Supported: column order, f32/f16/bf16 matrices with f32 accumulation, int8
- * operands with int32 C/D, transc = N, epilogues DEFAULT, RELU, BIAS, RELU_BIAS, GELU, GELU_BIAS.
+ * C is never written. Supported: f32/f16/bf16 matrices with f32 accumulation, int8 operands with int32
+ * C/D (default epilogue), transc = N, column or row order per matrix (C and D in the same order).
+ * Epilogues: DEFAULT, RELU, BIAS, RELU_BIAS, GELU, GELU_BIAS as in the reference, and beyond it
+ * (the reference answers NOT_SUPPORTED, cublasLt.cpp:68-78) NVIDIA's auxiliary and backward forms,
+ * for D in column order:
+ *   RELU_AUX(_BIAS)   also writes a bit mask: bit (row + col * aux_ld) of the auxiliary matrix is 1 where
+ *                     the value before ReLU was > 0 (aux_ld counts bits, a multiple of 32, >= rows)
+ *   GELU_AUX(_BIAS)   also writes the value before GELU to the auxiliary matrix (aux_ld >= rows)
+ *   DRELU, DGELU      D = (alpha op(A) op(B) + beta C) * activation'(forward input), the mask or input
+ *                     matrix of the forward pass being read from the auxiliary pointer
+ *   DRELU_BGRAD, DGELU_BGRAD   the same, then bias[i] = sum over columns of D(i, :) (fp32 sums of the
+ *                     stored D, fixed order), written to the bias pointer
+ *   BGRADA, BGRADB    the plain product, and bias[i] = sum over k of op(A)(i, :) (length m), or
+ *                     bias[j] = sum over k of op(B)(:, j) (length n)
  * Anything else answers CUBLAS_STATUS_NOT_SUPPORTED from the heuristic, the check and the matmul alike.
  */
 #ifndef VKZB_CUBLASLT_H
@@ -59,7 +71,11 @@ typedef enum {
     CUBLASLT_MATMUL_DESC_EPILOGUE = 7,
     CUBLASLT_MATMUL_DESC_BIAS_POINTER = 8,
     CUBLASLT_MATMUL_DESC_BIAS_BATCH_STRIDE = 10,
+    CUBLASLT_MATMUL_DESC_EPILOGUE_AUX_POINTER = 11,
+    CUBLASLT_MATMUL_DESC_EPILOGUE_AUX_LD = 12,
+    CUBLASLT_MATMUL_DESC_EPILOGUE_AUX_BATCH_STRIDE = 13,
     CUBLASLT_MATMUL_DESC_SM_COUNT_TARGET = 15,
+    CUBLASLT_MATMUL_DESC_EPILOGUE_AUX_DATA_TYPE = 22,
     CUBLASLT_MATMUL_DESC_FAST_ACCUM = 25,
     CUBLASLT_MATMUL_DESC_BIAS_DATA_TYPE = 26
 } cublasLtMatmulDescAttributes_t;
@@ -70,7 +86,17 @@ typedef enum {
     CUBLASLT_EPILOGUE_BIAS = 4,
     CUBLASLT_EPILOGUE_RELU_BIAS = 6,
     CUBLASLT_EPILOGUE_GELU = 32,
-    CUBLASLT_EPILOGUE_GELU_BIAS = 36
+    CUBLASLT_EPILOGUE_GELU_BIAS = 36,
+    CUBLASLT_EPILOGUE_RELU_AUX = 130,
+    CUBLASLT_EPILOGUE_RELU_AUX_BIAS = 134,
+    CUBLASLT_EPILOGUE_DRELU = 136,
+    CUBLASLT_EPILOGUE_DRELU_BGRAD = 152,
+    CUBLASLT_EPILOGUE_GELU_AUX = 160,
+    CUBLASLT_EPILOGUE_GELU_AUX_BIAS = 164,
+    CUBLASLT_EPILOGUE_DGELU = 192,
+    CUBLASLT_EPILOGUE_DGELU_BGRAD = 208,
+    CUBLASLT_EPILOGUE_BGRADA = 256,
+    CUBLASLT_EPILOGUE_BGRADB = 512
 } cublasLtEpilogue_t;
 
 typedef enum {

@@ -58,9 +58,10 @@ int vkzbSetOutputMirrors(void* handle, const void* localBase, size_t bytes, int 
  * cublasSgemm for callers that may not allocate device memory. No counterpart in the reference.
  *
  * Who needs it: a process that gives all device memory to its own pool at start-up, or that is in a phase where cudaMalloc
- * is unacceptable because it synchronises the device. Such a caller cannot create a cuBLAS handle here (creation allocates
- * the scratch memory of the split-k kernel), so this entry point takes no handle and runs the same split-k FFMA kernel on a
- * scratch array built into the library image. It calls no cudaMalloc, cudaFree or other allocating routine.
+ * is unacceptable because it synchronises the device. A handle of this library allocates the scratch memory of its split-k
+ * kernels at the first call that splits, which such a caller cannot allow; this entry point takes no handle and runs the same
+ * split-k FFMA kernel on a scratch array built into the library image. It calls no cudaMalloc, cudaFree or other allocating
+ * routine (a test compares the driver's free-memory figure before and after).
  *
  * C = alpha op(A) op(B) + beta C, fp32, column-major, alpha and beta on the host, asynchronous on `stream`; transa / transb
  * are cublasOperation_t values; the return value is a cublasStatus_t value.
@@ -68,10 +69,13 @@ int vkzbSetOutputMirrors(void* handle, const void* localBase, size_t bytes, int 
  * 64 x 64 (m * n up to about 2^20, e.g. 1024 x 1024); k is cut into up to 8 slices as far as that room allows. A larger
  * result is refused with CUBLAS_STATUS_INVALID_VALUE and a line on stderr; k = 0 and matrix-vector shapes answer
  * CUBLAS_STATUS_NOT_SUPPORTED (use the handle-based entry points for those).
- * The first call on each device looks up the array's device address (the device must be current); make that call before
- * starting a stream capture. Every call on a device shares the one array, which keeps what the last call left in it (the
- * kernel clears the counters it used): two calls that overlap on the GPU would corrupt each other, so issue them on one
- * stream or order them yourself. Every GPU that loads the library carries the array (about 4 MiB) until the process ends.
+ * First call: the first call on each device (with that device current) asks the runtime for the array's device address. That
+ * makes the driver load the array's module onto the device, which is when its memory is reserved and which may synchronise the
+ * device, so make one call per device during start-up, and before starting any stream capture. Later calls do no set-up.
+ * Sharing: every call on a device uses the one array, which keeps what the last call left in it (each call clears the
+ * counters it is about to use, in stream order): two calls that overlap on the GPU would corrupt each other, so issue them on
+ * one stream or order them yourself. Only libcublas.so.12 carries the array (libcublasLt.so.12 does not), so a GPU holds one
+ * copy, 4 MiB + 16 KiB, from the first call until the process ends.
  */
 int vkzbSgemmStaticScratch(cudaStream_t stream, int transa, int transb, int m, int n, int k, const float* alpha, const float* A,
                            int lda, const float* B, int ldb, const float* beta, float* C, int ldc);

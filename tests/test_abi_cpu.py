@@ -80,7 +80,12 @@ def test_lt_descriptor_plumbing():
     assert lib.cublasLtMatmulDescGetAttribute(desc, capi.LT_DESC_TRANSA, C.addressof(out), 4, C.byref(written)) == 0
     assert out.value == capi.OP_T and written.value == 4
     assert lib.cublasLtMatmulDescSetAttribute(desc, capi.LT_DESC_TRANSA, C.addressof(val), 2) == capi.STATUS_INVALID_VALUE  # wrong size
-    assert lib.cublasLtMatmulDescSetAttribute(desc, 11, C.addressof(val), 4) == capi.STATUS_NOT_SUPPORTED  # aux pointer: not served
+    assert lib.cublasLtMatmulDescSetAttribute(desc, 11, C.addressof(val), 4) == capi.STATUS_INVALID_VALUE  # aux pointer: 8 bytes
+    ptr = C.c_void_p(0x1000)
+    assert lib.cublasLtMatmulDescSetAttribute(desc, capi.LT_DESC_AUX_POINTER, C.addressof(ptr), 8) == 0
+    back = C.c_void_p(0)
+    assert lib.cublasLtMatmulDescGetAttribute(desc, capi.LT_DESC_AUX_POINTER, C.addressof(back), 8, None) == 0 and back.value == 0x1000
+    assert lib.cublasLtMatmulDescSetAttribute(desc, 17, C.addressof(val), 8) == capi.STATUS_NOT_SUPPORTED  # A scale pointer (fp8): not served
     assert lib.cublasLtMatmulDescSetAttribute(desc, 15, C.addressof(val), 4) == 0  # SM count target: accepted hint
     # size query with a null buffer
     assert lib.cublasLtMatmulDescGetAttribute(desc, capi.LT_DESC_EPILOGUE, None, 0, C.byref(written)) == 0 and written.value == 4
@@ -93,7 +98,7 @@ def test_lt_descriptor_plumbing():
     assert lib.cublasLtMatmulPreferenceCreate(C.byref(pref)) == 0
     ws = C.c_uint64(1 << 20)
     assert lib.cublasLtMatmulPreferenceSetAttribute(pref, capi.LT_PREF_MAX_WORKSPACE_BYTES, C.addressof(ws), 8) == 0
-    # the heuristic refuses what the matmul refuses: row order, and a missing handle is an invalid value
+    # a missing handle is an invalid value for the heuristic and NOT_INITIALIZED for the matmul
     heur, found = C.create_string_buffer(96), C.c_int(7)
     assert lib.cublasLtMatmulAlgoGetHeuristic(None, desc, layout, layout, layout, layout, pref, 1, C.addressof(heur), C.byref(found)) == capi.STATUS_INVALID_VALUE
     assert lib.cublasLtMatmul(None, desc, None, None, layout, None, layout, None, None, layout, None, layout, None, None, 0, None) == capi.STATUS_NOT_INITIALIZED

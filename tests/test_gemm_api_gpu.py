@@ -197,8 +197,10 @@ def test_lt_refuses_what_it_does_not_serve(cuda, lt):
     A, _ = orc.fill_lcg("f32", 64 * 64, 1)
     d = DeviceBuffer(cuda, A)
     args = (N, N, 8, 8, 8, 1.0, d.ptr, capi.CUDA_R_32F, 8, d.ptr, capi.CUDA_R_32F, 8, 0.0, d.ptr, capi.CUDA_R_32F, 8, d.ptr, capi.CUDA_R_32F, 8)
-    assert lt.matmul(*args, epilogue=128 | 2, check=False) == capi.STATUS_NOT_SUPPORTED   # RELU_AUX
-    assert lt.matmul(*args, order=1, check=False) == capi.STATUS_NOT_SUPPORTED            # row-major layouts
+    assert lt.matmul(*args, epilogue=128 | 2, check=False) == capi.STATUS_INVALID_VALUE   # RELU_AUX without an auxiliary pointer
+    assert lt.matmul(*args, epilogue=128 | 2 | 1, check=False) == capi.STATUS_NOT_SUPPORTED  # not one of NVIDIA's epilogue numbers
+    assert lt.matmul(*args, order=(0, 0, 1, 0), check=False) == capi.STATUS_NOT_SUPPORTED  # C and D in different orders
+    assert lt.matmul(*args, order=1, epilogue=capi.LT_EPILOGUE_GELU_AUX, aux=d.ptr, aux_ld=8, check=False) == capi.STATUS_NOT_SUPPORTED  # aux with row-order D
     assert lt.matmul(*args, epilogue=capi.LT_EPILOGUE_BIAS, bias=0, check=False) == capi.STATUS_INVALID_VALUE  # bias epilogue without a pointer
     assert lt.matmul(*args, check=False) == capi.STATUS_SUCCESS
 
@@ -368,3 +370,64 @@ def test_matrix_vector_chain_between_copies_in_a_graph(cuda):
     assert torch.allclose(ys[3].double(), want, rtol=2e-2, atol=2e-2)
     assert b.device_status() == 0
     b.destroy()
+
+
+@pytest.mark.gpu
+def test_gemm_grouped_batched_ex(cuda, blas):
+    """cublasGemmGroupedBatchedEx as the reference's acceptance test calls it (tests/cublas.cpp:491-548): three groups of f16
+    TN problems with fp32 C, each group with its own shape, scalars, leading dimensions and entry count; the pointer arrays
+    list every problem group after group; scalars are arrays of float on the host (COMPUTE_32F_FAST_16F)."""
+    groups = [(40, 7, 33, 2, 1.0, 0.0), (17, 5, 64, 1, -0.5, 1.0), (64, 1, 48, 3, 2.0, 0.0)]   # m, n, k, count, alpha, beta
+    mats, seed = [], 11
+    for (m, n, k, count, alpha, beta) in groups:
+        for _ in range(count):
+            A, av = orc.fill_lcg("f16", k * m, seed)
+            B, bv = orc.fill_lcg("f16", k * n, seed + 1)
+            Cm, cv = orc.fill_lcg("f32", m * n, seed + 2)
+            seed += 3
+            mats.append((DeviceBuffer(cuda, A), DeviceBuffer(cuda, B), DeviceBuffer(cuda, Cm), av, bv, cv))
+    total = len(mats)
+    ptrs = np.array([x[0].ptr for x in mats] + [x[1].ptr for x in mats] + [x[2].ptr for x in mats], dtype=np.uint64)
+    dP = DeviceBuffer(cuda, ptrs)
+    ints = lambda values: (C.c_int * len(values))(*values)
+    floats = lambda values: (C.c_float * len(values))(*values)
+    status = blas.lib.cublasGemmGroupedBatchedEx(
+        blas.handle, ints([T] * 3), ints([N] * 3), ints([g[0] for g in groups]), ints([g[1] for g in groups]), ints([g[2] for g in groups]),
+        floats([g[4] for g in groups]), dP.ptr, capi.CUDA_R_16F, ints([g[2] for g in groups]), dP.ptr + 8 * total, capi.CUDA_R_16F,
+        ints([g[2] for g in groups]), floats([g[5] for g in groups]), dP.ptr + 16 * total, capi.CUDA_R_32F, ints([g[0] for g in groups]), 3,
+        ints([g[3] for g in groups]), capi.COMPUTE_32F_FAST_16F)
+    assert status == capi.STATUS_SUCCESS
+    p = 0
+    for (m, n, k, count, alpha, beta) in groups:
+        for _ in range(count):
+            dA, dB, dC, av, bv, cv = mats[p]
+            a = av.reshape(m, k).astype(np.float64)            # A stored k x m: op(A) = A^T is m x k
+            b = bv.reshape(n, k).astype(np.float64)
+            want = alpha * (a @ b.T) + beta * cv.reshape(n, m).T.astype(np.float64)
+            got = dC.download().reshape(n, m).T
+            assert (np.abs(got - want) <= 2e-3 * np.maximum(1.0, np.abs(want)) * 8.0).all(), f"problem {p}"   # tests/cublas.cpp:537
+            p += 1
+    # argument checks of the entry point itself
+    assert blas.lib.cublasGemmGroupedBatchedEx(blas.handle, None, None, None, None, None, None, 0, capi.CUDA_R_16F, None, 0, capi.CUDA_R_16F,
+                                               None, None, 0, capi.CUDA_R_32F, None, 0, None, capi.COMPUTE_32F) == capi.STATUS_SUCCESS
+    assert blas.lib.cublasGemmGroupedBatchedEx(blas.handle, None, None, None, None, None, None, 0, capi.CUDA_R_16F, None, 0, capi.CUDA_R_16F,
+                                               None, None, 0, capi.CUDA_R_32F, None, 2, None, capi.COMPUTE_32F) == capi.STATUS_INVALID_VALUE
+
+
+@pytest.mark.gpu
+def test_more_columns_than_one_grid_dimension_holds(cuda, blas):
+    """k = 0 scales C by beta for a result with 300000 columns (a grid dimension holds 65535 blocks), and a thin fp32 product
+    of the same width goes through the tile kernels' column chunks."""
+    m, n = 4, 300000
+    C0, cv = orc.fill_lcg("f32", m * n, 5)
+    dC = DeviceBuffer(cuda, C0)
+    blas.sgemm(N, N, m, n, 0, 1.0, dC.ptr, m, dC.ptr, 1, 0.5, dC.ptr, m)
+    assert blas.last_path() == capi.PATH_SCALE
+    assert np.array_equal(dC.download(), (0.5 * cv).astype(np.float32))
+    k = 3
+    A, av = orc.fill_lcg("f32", m * k, 6)
+    B, bv = orc.fill_lcg("f32", k * n, 7)
+    dA, dB, dD = DeviceBuffer(cuda, A), DeviceBuffer(cuda, B), DeviceBuffer(cuda, np.zeros(m * n, dtype=np.float32))
+    blas.sgemm(N, N, m, n, k, 1.0, dA.ptr, m, dB.ptr, k, 0.0, dD.ptr, m)
+    want = (av.reshape(k, m).T.astype(np.float64) @ bv.reshape(n, k).T.astype(np.float64)).T.ravel()
+    assert np.allclose(dD.download(), want, atol=1e-5)

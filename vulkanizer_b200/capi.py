@@ -33,6 +33,11 @@ PATH_NONE, PATH_SCALE, PATH_GENERIC, PATH_GEMV, PATH_SGEMM, PATH_UMMA, PATH_DGEM
 # cuBLASLt (include/vkzb_cublaslt.h)
 LT_EPILOGUE_DEFAULT, LT_EPILOGUE_RELU, LT_EPILOGUE_BIAS, LT_EPILOGUE_RELU_BIAS = 1, 2, 4, 6
 LT_EPILOGUE_GELU, LT_EPILOGUE_GELU_BIAS = 32, 36
+LT_EPILOGUE_RELU_AUX, LT_EPILOGUE_RELU_AUX_BIAS, LT_EPILOGUE_GELU_AUX, LT_EPILOGUE_GELU_AUX_BIAS = 130, 134, 160, 164
+LT_EPILOGUE_DRELU, LT_EPILOGUE_DRELU_BGRAD, LT_EPILOGUE_DGELU, LT_EPILOGUE_DGELU_BGRAD = 136, 152, 192, 208
+LT_EPILOGUE_BGRADA, LT_EPILOGUE_BGRADB = 256, 512
+LT_DESC_AUX_POINTER, LT_DESC_AUX_LD, LT_DESC_AUX_BATCH_STRIDE, LT_DESC_AUX_DATA_TYPE = 11, 12, 13, 22
+LT_ORDER_COL, LT_ORDER_ROW = 0, 1
 LT_DESC_COMPUTE_TYPE, LT_DESC_SCALE_TYPE, LT_DESC_POINTER_MODE, LT_DESC_TRANSA, LT_DESC_TRANSB, LT_DESC_TRANSC = range(6)
 LT_DESC_EPILOGUE, LT_DESC_BIAS_POINTER, LT_DESC_BIAS_BATCH_STRIDE, LT_DESC_BIAS_DATA_TYPE = 7, 8, 10, 26
 LT_LAYOUT_TYPE, LT_LAYOUT_ORDER, LT_LAYOUT_ROWS, LT_LAYOUT_COLS, LT_LAYOUT_LD, LT_LAYOUT_BATCH_COUNT, LT_LAYOUT_BATCH_STRIDE = range(7)
@@ -397,7 +402,9 @@ class CublasLt:
 
     def matmul(self, ta, tb, m, n, k, alpha, A, type_a, lda, B, type_b, ldb, beta, Cp, type_c, ldc, D, type_d, ldd, *,
                compute=COMPUTE_32F, scale_type=CUDA_R_32F, epilogue=LT_EPILOGUE_DEFAULT, bias=0, bias_type=None, batch=1,
-               stride_a=0, stride_b=0, stride_c=0, stride_d=0, stream=0, check=True, order=None):
+               stride_a=0, stride_b=0, stride_c=0, stride_d=0, stream=0, check=True, order=None, aux=0, aux_ld=0, aux_stride=0,
+               aux_type=None):
+        """One cublasLtMatmul. `order` is None (column order), one LT_ORDER_* for all four matrices, or a tuple (A, B, C, D)."""
         lib = self.lib
         desc = _vp()
         status = lib.cublasLtMatmulDescCreate(C.byref(desc), compute, scale_type)
@@ -412,10 +419,17 @@ class CublasLt:
                 self._set(lib.cublasLtMatmulDescSetAttribute, desc, LT_DESC_BIAS_POINTER, C.c_void_p, bias)
             if bias_type is not None:
                 self._set(lib.cublasLtMatmulDescSetAttribute, desc, LT_DESC_BIAS_DATA_TYPE, C.c_int32, bias_type)
+            if aux:
+                self._set(lib.cublasLtMatmulDescSetAttribute, desc, LT_DESC_AUX_POINTER, C.c_void_p, aux)
+                self._set(lib.cublasLtMatmulDescSetAttribute, desc, LT_DESC_AUX_LD, C.c_int64, aux_ld)
+                self._set(lib.cublasLtMatmulDescSetAttribute, desc, LT_DESC_AUX_BATCH_STRIDE, C.c_int64, aux_stride)
+            if aux_type is not None:
+                self._set(lib.cublasLtMatmulDescSetAttribute, desc, LT_DESC_AUX_DATA_TYPE, C.c_int32, aux_type)
+            orders = (order,) * 4 if order is None or isinstance(order, int) else tuple(order)
             rows_a, cols_a = (m, k) if ta == OP_N else (k, m)
             rows_b, cols_b = (k, n) if tb == OP_N else (n, k)
-            for (typ, rows, cols, ld, stride) in ((type_a, rows_a, cols_a, lda, stride_a), (type_b, rows_b, cols_b, ldb, stride_b),
-                                                  (type_c, m, n, ldc, stride_c), (type_d, m, n, ldd, stride_d)):
+            for which, (typ, rows, cols, ld, stride) in enumerate(((type_a, rows_a, cols_a, lda, stride_a), (type_b, rows_b, cols_b, ldb, stride_b),
+                                                                   (type_c, m, n, ldc, stride_c), (type_d, m, n, ldd, stride_d))):
                 layout = _vp()
                 status = lib.cublasLtMatrixLayoutCreate(C.byref(layout), typ, rows, cols, ld)
                 if status:
@@ -423,8 +437,8 @@ class CublasLt:
                 layouts.append(layout)
                 self._set(lib.cublasLtMatrixLayoutSetAttribute, layout, LT_LAYOUT_BATCH_COUNT, C.c_int32, batch)
                 self._set(lib.cublasLtMatrixLayoutSetAttribute, layout, LT_LAYOUT_BATCH_STRIDE, C.c_int64, stride)
-                if order is not None:
-                    self._set(lib.cublasLtMatrixLayoutSetAttribute, layout, LT_LAYOUT_ORDER, C.c_int32, order)
+                if orders[which] is not None:
+                    self._set(lib.cublasLtMatrixLayoutSetAttribute, layout, LT_LAYOUT_ORDER, C.c_int32, orders[which])
             a = C.create_string_buffer(pack_scalar(alpha, compute), 8)
             b = C.create_string_buffer(pack_scalar(beta, compute), 8)
             heuristic = C.create_string_buffer(96)

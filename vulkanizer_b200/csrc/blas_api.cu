@@ -10,6 +10,7 @@
 //   * there is one tensor-core kernel and no run-time race between kernels (cublas.cpp:644-696).
 #include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -129,10 +130,119 @@ static int accumulatorFor(int ta, int tb, int tc, cublasComputeType_t compute) {
     return kBadType;
 }
 
+// ---- host time per entry point (VKZB_PROFILE=1) ----
+namespace {
+constexpr int kApiSlots = 96;
+struct ApiRow {
+    std::atomic<const char*> name{nullptr};
+    std::atomic<unsigned long long> calls{0}, ns{0};
+};
+ApiRow g_apiRows[kApiSlots];
+
+void printApiTable() {
+    int order[kApiSlots], used = 0;
+    for (int i = 0; i < kApiSlots; ++i)
+        if (g_apiRows[i].name.load() && g_apiRows[i].calls.load()) order[used++] = i;
+    if (!used) return;
+    std::sort(order, order + used, [](int a, int b) { return g_apiRows[a].ns.load() > g_apiRows[b].ns.load(); });
+    std::fprintf(stderr, "vkzb: host time per entry point (VKZB_PROFILE)\n%12s %10s %10s  %s\n", "total ms", "calls", "mean us", "entry point");
+    for (int i = 0; i < used; ++i) {
+        const ApiRow& r = g_apiRows[order[i]];
+        const double ns = double(r.ns.load()), calls = double(r.calls.load());
+        std::fprintf(stderr, "%12.3f %10.0f %10.2f  %s\n", ns * 1e-6, calls, ns * 1e-3 / calls, r.name.load());
+    }
+}
+
+bool profiling() {
+    static const bool on = [] {
+        const char* v = std::getenv("VKZB_PROFILE");
+        const bool enabled = v && *v && std::strcmp(v, "0") != 0;
+        if (enabled) std::atexit(printApiTable);
+        return enabled;
+    }();
+    return on;
+}
+
+long long nowNs() { return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
+}  // namespace
+
+// `name` is a string literal (__func__): rows are found by pointer first, by text when another call site shares the name.
+ApiScope::ApiScope(const char* name) : slot_(-1), start_(0) {
+    if (!profiling()) return;
+    for (int i = 0; i < kApiSlots; ++i) {
+        const char* have = g_apiRows[i].name.load(std::memory_order_acquire);
+        if (!have) {
+            const char* expected = nullptr;
+            if (g_apiRows[i].name.compare_exchange_strong(expected, name)) have = name;
+            else have = expected;
+        }
+        if (have == name || !std::strcmp(have, name)) {
+            slot_ = i;
+            break;
+        }
+    }
+    start_ = nowNs();
+}
+
+ApiScope::~ApiScope() {
+    if (slot_ < 0) return;
+    g_apiRows[slot_].calls.fetch_add(1, std::memory_order_relaxed);
+    g_apiRows[slot_].ns.fetch_add((unsigned long long)(nowNs() - start_), std::memory_order_relaxed);
+}
+
+// ---- the handle's scratch memory ----
+constexpr size_t kScratchBytes = kSplitKCounters * sizeof(unsigned) + (size_t(64) << 20);  // counters, then 64 MiB of partial tiles
+
+// Makes the handle's scratch memory usable by a call on `stream`, allocating it at the first call that wants it. Returns
+// false when the call has to do without: allocation failed, or a stream capture is under way and the memory is not there
+// yet or would need ordering against another stream (neither an allocation nor a cross-stream wait belongs in a capture).
+static bool acquireScratch(cublasHandle_t h, cudaStream_t stream) {
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    const bool capturing = capture != cudaStreamCaptureStatusNone;
+    if (!h->scratch) {
+        if (h->scratchTried || capturing) return false;
+        h->scratchTried = true;
+        if (cudaMalloc(&h->scratch, kScratchBytes) != cudaSuccess || cudaMemset(h->scratch, 0, kSplitKCounters * sizeof(unsigned)) != cudaSuccess ||
+            cudaEventCreateWithFlags(&h->scratchEvent, cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            if (h->scratch) cudaFree(h->scratch);
+            h->scratch = nullptr;
+            return false;
+        }
+        h->scratchBytes = kScratchBytes;
+    }
+    if (h->scratchUsed && h->scratchStream != stream) {
+        // the last user ran on another stream: this call waits for it on the device, the host does not block
+        if (capturing) return false;
+        if (cudaEventRecord(h->scratchEvent, h->scratchStream) != cudaSuccess || cudaStreamWaitEvent(stream, h->scratchEvent, 0) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+    }
+    h->scratchStream = stream, h->scratchUsed = true;
+    return true;
+}
+
+void releaseScratch(cublasContext* h) {
+    if (h->scratch) cudaFree(h->scratch);
+    if (h->scratchEvent) cudaEventDestroy(h->scratchEvent);
+    h->scratch = nullptr, h->scratchEvent = nullptr, h->scratchBytes = 0;
+}
+
+// Would this call split along k if it had the scratch memory? (Only then is the memory allocated or ordered.)
+static bool wantsScratch(const Problem& p, bool umma) {
+    if (umma) return ummaWantsScratch(p, kScratchBytes);
+    return sgemmSplitKPlan(p, kScratchBytes) > 1;
+}
+
 // Picks the kernel family and launches. `p` is complete except for the stream.
-cublasStatus_t dispatch(cublasHandle_t h, Problem& p) {
-    p.stream = h->stream;
-    p.scratch = h->scratch, p.scratchBytes = h->scratchBytes;
+cublasStatus_t dispatch(cublasHandle_t h, Problem& p, cudaStream_t stream) {
+    p.stream = stream;
+    p.scratch = nullptr, p.scratchBytes = 0;
     p.mirrorCount = 0;
     if (h->mirrorCount > 0 && !p.epi.pointerArrays) {
         const char* d = static_cast<const char*>(p.epi.D);
@@ -156,9 +266,11 @@ cublasStatus_t dispatch(cublasHandle_t h, Problem& p) {
         err = launchGeneric(p);
     } else if (forcedPath() != -int(VKZB_PATH_UMMA) && ummaEligible(p)) {
         path = VKZB_PATH_UMMA;
+        if (wantsScratch(p, true) && acquireScratch(h, stream)) p.scratch = h->scratch, p.scratchBytes = h->scratchBytes;
         err = launchUmma(p);
     } else if (sgemmEligible(p)) {
         path = VKZB_PATH_SGEMM;
+        if (wantsScratch(p, false) && acquireScratch(h, stream)) p.scratch = h->scratch, p.scratchBytes = h->scratchBytes;
         err = launchSgemm(p);
     } else {
         path = p.accType == kF64 ? VKZB_PATH_DGEMM : VKZB_PATH_GENERIC;
@@ -227,7 +339,7 @@ cublasStatus_t run(cublasHandle_t h, const Call& c) {
     p.epi.pointerArrays = c.pointerArrays;
     if (!fillScalars(p.epi.scalars, c.alpha, c.beta, scalarTypeOf(c.compute), h->pointerMode == CUBLAS_POINTER_MODE_DEVICE))
         return CUBLAS_STATUS_INVALID_VALUE;
-    return dispatch(h, p);
+    return dispatch(h, p, h->stream);
 }
 
 bool fitsInt(std::initializer_list<int64_t> values) {
@@ -245,6 +357,7 @@ using namespace vkzb;
 extern "C" {
 
 cublasStatus_t cublasCreate_v2(cublasHandle_t* handle) {
+    VKZB_API_SCOPE();
     if (!handle) return CUBLAS_STATUS_INVALID_VALUE;
     // Binds to the context that is current (a driver-API one made by the caller, or the device's primary
     // one, which this call brings up if needed) as cublas.cpp:931-945 does.
@@ -254,20 +367,14 @@ cublasStatus_t cublasCreate_v2(cublasHandle_t* handle) {
     cudaGetDevice(&h->device);
     envLevel();
     forcedPath();
-    // scratch for split-k partial sums: 64 MiB of partial tiles behind the arrival counters, which start at zero
-    h->scratchBytes = kSplitKCounters * sizeof(unsigned) + (size_t(64) << 20);
-    if (cudaMalloc(&h->scratch, h->scratchBytes) != cudaSuccess || cudaMemset(h->scratch, 0, kSplitKCounters * sizeof(unsigned)) != cudaSuccess) {
-        cudaGetLastError();
-        if (h->scratch) cudaFree(h->scratch);
-        h->scratch = nullptr, h->scratchBytes = 0;  // products simply are not split
-    }
-    *handle = h;
+    *handle = h;  // no device memory yet: split-k scratch comes with the first call that wants it (acquireScratch)
     return CUBLAS_STATUS_SUCCESS;
 }
 
 cublasStatus_t cublasDestroy_v2(cublasHandle_t handle) {
+    VKZB_API_SCOPE();
     if (!handle) return CUBLAS_STATUS_NOT_INITIALIZED;
-    if (handle->scratch) cudaFree(handle->scratch);
+    releaseScratch(handle);
     delete handle;
     return CUBLAS_STATUS_SUCCESS;
 }
@@ -388,6 +495,7 @@ cublasStatus_t cublasLoggerConfigure(int, int, int, const char*) { return CUBLAS
 cublasStatus_t cublasSgemm_v2(cublasHandle_t h, cublasOperation_t transa, cublasOperation_t transb, int m, int n, int k,
                               const float* alpha, const float* A, int lda, const float* B, int ldb, const float* beta,
                               float* C, int ldc) {
+    VKZB_API_SCOPE();
     return run(h, {transa, transb, m, n, k, alpha, A, CUDA_R_32F, lda, 0, B, CUDA_R_32F, ldb, 0, beta, C, CUDA_R_32F, ldc, 0,
                    1, false, CUBLAS_COMPUTE_32F});
 }
@@ -395,6 +503,7 @@ cublasStatus_t cublasSgemm_v2(cublasHandle_t h, cublasOperation_t transa, cublas
 cublasStatus_t cublasSgemmBatched(cublasHandle_t h, cublasOperation_t transa, cublasOperation_t transb, int m, int n, int k,
                                   const float* alpha, const float* const A[], int lda, const float* const B[], int ldb,
                                   const float* beta, float* const C[], int ldc, int batchCount) {
+    VKZB_API_SCOPE();
     return run(h, {transa, transb, m, n, k, alpha, A, CUDA_R_32F, lda, 0, B, CUDA_R_32F, ldb, 0, beta,
                    const_cast<void*>(static_cast<const void*>(C)), CUDA_R_32F, ldc, 0, batchCount, true, CUBLAS_COMPUTE_32F});
 }
@@ -403,6 +512,7 @@ cublasStatus_t cublasSgemmStridedBatched(cublasHandle_t h, cublasOperation_t tra
                                          int k, const float* alpha, const float* A, int lda, long long strideA,
                                          const float* B, int ldb, long long strideB, const float* beta, float* C, int ldc,
                                          long long strideC, int batchCount) {
+    VKZB_API_SCOPE();
     return run(h, {transa, transb, m, n, k, alpha, A, CUDA_R_32F, lda, strideA, B, CUDA_R_32F, ldb, strideB, beta, C,
                    CUDA_R_32F, ldc, strideC, batchCount, false, CUBLAS_COMPUTE_32F});
 }
@@ -410,6 +520,7 @@ cublasStatus_t cublasSgemmStridedBatched(cublasHandle_t h, cublasOperation_t tra
 cublasStatus_t cublasDgemm_v2(cublasHandle_t h, cublasOperation_t transa, cublasOperation_t transb, int m, int n, int k,
                               const double* alpha, const double* A, int lda, const double* B, int ldb, const double* beta,
                               double* C, int ldc) {
+    VKZB_API_SCOPE();
     return run(h, {transa, transb, m, n, k, alpha, A, CUDA_R_64F, lda, 0, B, CUDA_R_64F, ldb, 0, beta, C, CUDA_R_64F, ldc, 0,
                    1, false, CUBLAS_COMPUTE_64F});
 }
@@ -417,6 +528,7 @@ cublasStatus_t cublasDgemm_v2(cublasHandle_t h, cublasOperation_t transa, cublas
 cublasStatus_t cublasDgemmBatched(cublasHandle_t h, cublasOperation_t transa, cublasOperation_t transb, int m, int n, int k,
                                   const double* alpha, const double* const A[], int lda, const double* const B[], int ldb,
                                   const double* beta, double* const C[], int ldc, int batchCount) {
+    VKZB_API_SCOPE();
     return run(h, {transa, transb, m, n, k, alpha, A, CUDA_R_64F, lda, 0, B, CUDA_R_64F, ldb, 0, beta,
                    const_cast<void*>(static_cast<const void*>(C)), CUDA_R_64F, ldc, 0, batchCount, true, CUBLAS_COMPUTE_64F});
 }
@@ -425,6 +537,7 @@ cublasStatus_t cublasDgemmStridedBatched(cublasHandle_t h, cublasOperation_t tra
                                          int k, const double* alpha, const double* A, int lda, long long strideA,
                                          const double* B, int ldb, long long strideB, const double* beta, double* C, int ldc,
                                          long long strideC, int batchCount) {
+    VKZB_API_SCOPE();
     return run(h, {transa, transb, m, n, k, alpha, A, CUDA_R_64F, lda, strideA, B, CUDA_R_64F, ldb, strideB, beta, C,
                    CUDA_R_64F, ldc, strideC, batchCount, false, CUBLAS_COMPUTE_64F});
 }
@@ -433,6 +546,7 @@ cublasStatus_t cublasGemmEx(cublasHandle_t h, cublasOperation_t transa, cublasOp
                             const void* alpha, const void* A, cudaDataType Atype, int lda, const void* B, cudaDataType Btype,
                             int ldb, const void* beta, void* C, cudaDataType Ctype, int ldc, cublasComputeType_t computeType,
                             cublasGemmAlgo_t) {
+    VKZB_API_SCOPE();
     return run(h, {transa, transb, m, n, k, alpha, A, Atype, lda, 0, B, Btype, ldb, 0, beta, C, Ctype, ldc, 0, 1, false,
                    computeType});
 }
@@ -441,6 +555,7 @@ cublasStatus_t cublasGemmEx(cublasHandle_t h, cublasOperation_t transa, cublasOp
 cublasStatus_t cublasHgemm(cublasHandle_t h, cublasOperation_t transa, cublasOperation_t transb, int m, int n, int k,
                            const void* alpha, const void* A, int lda, const void* B, int ldb, const void* beta, void* C,
                            int ldc) {
+    VKZB_API_SCOPE();
     return run(h, {transa, transb, m, n, k, alpha, A, CUDA_R_16F, lda, 0, B, CUDA_R_16F, ldb, 0, beta, C, CUDA_R_16F, ldc, 0,
                    1, false, CUBLAS_COMPUTE_16F});
 }
@@ -450,6 +565,7 @@ cublasStatus_t cublasGemmBatchedEx(cublasHandle_t h, cublasOperation_t transa, c
                                    const void* const Barray[], cudaDataType Btype, int ldb, const void* beta,
                                    void* const Carray[], cudaDataType Ctype, int ldc, int batchCount,
                                    cublasComputeType_t computeType, cublasGemmAlgo_t) {
+    VKZB_API_SCOPE();
     return run(h, {transa, transb, m, n, k, alpha, Aarray, Atype, lda, 0, Barray, Btype, ldb, 0, beta,
                    const_cast<void*>(static_cast<const void*>(Carray)), Ctype, ldc, 0, batchCount, true, computeType});
 }
@@ -459,6 +575,7 @@ cublasStatus_t cublasGemmStridedBatchedEx(cublasHandle_t h, cublasOperation_t tr
                                           long long strideA, const void* B, cudaDataType Btype, int ldb, long long strideB,
                                           const void* beta, void* C, cudaDataType Ctype, int ldc, long long strideC,
                                           int batchCount, cublasComputeType_t computeType, cublasGemmAlgo_t) {
+    VKZB_API_SCOPE();
     return run(h, {transa, transb, m, n, k, alpha, A, Atype, lda, strideA, B, Btype, ldb, strideB, beta, C, Ctype, ldc,
                    strideC, batchCount, false, computeType});
 }
@@ -466,6 +583,7 @@ cublasStatus_t cublasGemmStridedBatchedEx(cublasHandle_t h, cublasOperation_t tr
 cublasStatus_t cublasSgemmEx(cublasHandle_t h, cublasOperation_t transa, cublasOperation_t transb, int m, int n, int k,
                              const float* alpha, const void* A, cudaDataType Atype, int lda, const void* B,
                              cudaDataType Btype, int ldb, const float* beta, void* C, cudaDataType Ctype, int ldc) {
+    VKZB_API_SCOPE();
     return run(h, {transa, transb, m, n, k, alpha, A, Atype, lda, 0, B, Btype, ldb, 0, beta, C, Ctype, ldc, 0, 1, false,
                    CUBLAS_COMPUTE_32F});
 }
@@ -479,6 +597,7 @@ cublasStatus_t cublasGemmGroupedBatchedEx(cublasHandle_t h, const cublasOperatio
                                           cudaDataType Btype, const int ldb_array[], const void* beta_array,
                                           void* const Carray[], cudaDataType Ctype, const int ldc_array[], int group_count,
                                           const int group_size[], cublasComputeType_t computeType) {
+    VKZB_API_SCOPE();
     if (!h) return CUBLAS_STATUS_NOT_INITIALIZED;
     if (group_count < 0) return CUBLAS_STATUS_INVALID_VALUE;
     if (group_count && (!transa_array || !transb_array || !m_array || !n_array || !k_array || !alpha_array || !lda_array ||
@@ -506,6 +625,7 @@ cublasStatus_t cublasGemmGroupedBatchedEx(cublasHandle_t h, const cublasOperatio
 // dimensions and the matrix-vector kernel does the work (cublas.cpp:1143-1159).
 cublasStatus_t cublasSgemv_v2(cublasHandle_t h, cublasOperation_t trans, int m, int n, const float* alpha, const float* A,
                               int lda, const float* x, int incx, const float* beta, float* y, int incy) {
+    VKZB_API_SCOPE();
     if (!h) return CUBLAS_STATUS_NOT_INITIALIZED;
     if (m < 0 || n < 0 || lda < std::max(1, m) || incx == 0 || incy == 0) return CUBLAS_STATUS_INVALID_VALUE;
     if (incx < 0 || incy < 0) return CUBLAS_STATUS_NOT_SUPPORTED;

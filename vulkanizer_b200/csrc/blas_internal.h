@@ -15,10 +15,15 @@ struct cublasContext {
     int device = 0;
     void* workspace = nullptr;
     size_t workspaceBytes = 0;
-    // Scratch memory owned by the handle (allocated at creation, like cuBLAS's own workspace): partial sums of split-k
-    // products. One handle, one stream at a time: two calls that overlap on the GPU through the same handle would share it.
+    // Scratch memory owned by the handle: arrival counters and partial sums of split-k products. Nothing is allocated until
+    // the first call that wants to split (and never during a stream capture); a handle whose allocation failed simply does not
+    // split. Calls that use it from a different stream than the last one that did are ordered behind that one with an event.
     void* scratch = nullptr;
     size_t scratchBytes = 0;
+    bool scratchTried = false;
+    cudaStream_t scratchStream = nullptr;  // stream of the last call that used the scratch memory
+    bool scratchUsed = false;
+    cudaEvent_t scratchEvent = nullptr;
     // output mirrors (vkzbSetOutputMirrors): results inside [mirrorLocal, mirrorLocal + mirrorBytes) are also written there
     const char* mirrorLocal = nullptr;
     size_t mirrorBytes = 0;
@@ -31,6 +36,20 @@ namespace vkzb {
 int dtypeOf(cudaDataType t);
 int scalarTypeOf(cublasComputeType_t compute);
 bool fillScalars(ScalarArgs& s, const void* alpha, const void* beta, int type, bool devicePointers);
-cublasStatus_t dispatch(cublasContext* h, Problem& p);
+// Picks the kernel family for `p` and launches it on `stream` (the handle's own for cuBLAS calls, the call's for cuBLASLt).
+cublasStatus_t dispatch(cublasContext* h, Problem& p, cudaStream_t stream);
+void releaseScratch(cublasContext* h);  // at handle destruction
+
+// Host time per exported entry point, printed at exit when VKZB_PROFILE=1 (the counterpart of the reference's
+// VULKANIZER_PROFILE=1 table, src/common/log.cpp:44-74). A scope object at the top of an entry point does the timing.
+class ApiScope {
+public:
+    explicit ApiScope(const char* name);
+    ~ApiScope();
+private:
+    int slot_;
+    long long start_;
+};
+#define VKZB_API_SCOPE() ::vkzb::ApiScope vkzbApiScope_(__func__)
 
 }  // namespace vkzb

@@ -61,6 +61,13 @@ __device__ __forceinline__ float geluTanh(float x) {
     return 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
 }
 
+// Derivative of geluTanh.
+__device__ __forceinline__ float geluTanhGrad(float x) {
+    const float u = 0.7978845608f * (x + 0.044715f * x * x * x);
+    const float t = tanhf(u);
+    return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * 0.7978845608f * (1.0f + 3.0f * 0.044715f * x * x);
+}
+
 __device__ __forceinline__ double readScalar(const void* dev, double host, int type) {
     if (!dev) return host;
     switch (type) {
@@ -85,9 +92,10 @@ struct Epilogue {
     char* D;
     const char* C;
     const char* bias;
-    long long ldd, ldc;
+    char* aux;
+    long long ldd, ldc, auxLd;
     Acc alpha, beta;
-    int typeD, typeC, typeBias, activation, roundBeforeBias;
+    int typeD, typeC, typeBias, activation, roundBeforeBias, biasAlongN, typeAux, auxMode;
     int mode;       // StoreMode
     int typedMode;  // the StoreMode D and C alone ask for: what `mode` would be without bias, activation and the extra rounding
     bool readC;
@@ -101,6 +109,7 @@ struct Epilogue {
         readC = b != 0.0;  // beta = 0: C is not read, so NaNs in it do not propagate (gemm.comp:143)
         typeD = e.typeD, typeC = e.typeC, typeBias = e.typeBias;
         activation = e.activation, roundBeforeBias = e.roundBeforeBias;
+        biasAlongN = e.biasAlongN, typeAux = e.typeAux, auxMode = e.auxMode, auxLd = e.auxLd;
         ldd = e.ldd, ldc = e.ldc;
         if (e.pointerArrays) {
             D = static_cast<char*>(static_cast<void* const*>(e.D)[batchEntry]);
@@ -110,7 +119,12 @@ struct Epilogue {
             C = static_cast<const char*>(e.C) + batchEntry * e.strideC * dtypeSize(e.typeC);
         }
         bias = e.bias ? static_cast<const char*>(e.bias) + batchEntry * e.biasStride * dtypeSize(e.typeBias) : nullptr;
-        post = bias || activation != kActNone || roundBeforeBias;
+        aux = nullptr;
+        if (e.aux && e.auxMode != kAuxNone) {
+            const bool mask = e.auxMode == kAuxWriteMask || e.auxMode == kAuxReadMask;  // strides of a mask count bits
+            aux = static_cast<char*>(e.aux) + (mask ? batchEntry * e.auxStride / 8 : batchEntry * e.auxStride * dtypeSize(e.typeAux));
+        }
+        post = bias || activation != kActNone || roundBeforeBias || aux;
         const bool mixed = readC && typeC != typeD;
         if constexpr (std::is_same_v<Acc, double>) typedMode = kStoreF64;
         else if constexpr (std::is_same_v<Acc, int>) typedMode = typeD == kS32 && !mixed ? kStoreS32 : kStoreSlow;
@@ -118,12 +132,35 @@ struct Epilogue {
         mode = post && !std::is_same_v<Acc, double> ? kStoreSlow : typedMode;
     }
 
-    // What follows alpha * acc + beta * C when `post` is set, for one result of row `row` (float accumulators).
+    // What follows alpha * acc + beta * C when `post` is set and no auxiliary matrix is involved (float accumulators).
     __device__ __forceinline__ float finish(float v, float biasValue) const {
         if (roundBeforeBias) v = roundTo(v, typeD);
         v += biasValue;
         if (activation == kActRelu) v = fmaxf(v, 0.0f);
         else if (activation == kActGelu) v = geluTanh(v);
+        return v;
+    }
+
+    __device__ __forceinline__ float biasAt(int row, int col) const { return bias ? loadAs<float>(bias, biasAlongN ? col : row, typeBias) : 0.0f; }
+
+    // The same for one result at (row, col) with the auxiliary matrix handled by this thread alone: the mask bit is set or
+    // cleared with an atomic on its 32-bit word, so any assignment of results to threads is safe (the tensor-core kernel has a
+    // faster form that writes whole words, one per warp and column).
+    __device__ __noinline__ float finishAt(float v, int row, int col) const {
+        if (roundBeforeBias) v = roundTo(v, typeD);
+        v += biasAt(row, col);
+        const long long at = row + col * auxLd;
+        if (auxMode == kAuxWriteInput) storeFloat(aux, at, typeAux, v);
+        if (auxMode == kAuxWriteMask) {
+            unsigned* word = reinterpret_cast<unsigned*>(aux) + (at >> 5);
+            const unsigned bit = 1u << (at & 31);
+            if (v > 0.0f) atomicOr(word, bit);
+            else atomicAnd(word, ~bit);
+        }
+        if (activation == kActRelu) v = fmaxf(v, 0.0f);
+        else if (activation == kActGelu) v = geluTanh(v);
+        else if (activation == kActDRelu) v = (reinterpret_cast<const unsigned*>(aux)[at >> 5] >> (at & 31)) & 1u ? v : 0.0f;
+        else if (activation == kActDGelu) v *= geluTanhGrad(loadAs<float>(aux, at, typeAux));
         return v;
     }
 
@@ -138,10 +175,14 @@ struct Epilogue {
         } else if constexpr (std::is_same_v<Acc, float>) {
             float v = alpha * acc;
             if (readC) v += beta * loadAs<float>(C, row + col * ldc, typeC);
-            if (roundBeforeBias) v = roundTo(v, typeD);
-            if (bias) v += loadAs<float>(bias, row, typeBias);
-            if (activation == kActRelu) v = fmaxf(v, 0.0f);
-            else if (activation == kActGelu) v = geluTanh(v);
+            if (aux) {
+                v = finishAt(v, row, col);
+            } else {
+                if (roundBeforeBias) v = roundTo(v, typeD);
+                v += biasAt(row, col);
+                if (activation == kActRelu) v = fmaxf(v, 0.0f);
+                else if (activation == kActGelu) v = geluTanh(v);
+            }
             storeFloat(D, di, typeD, v);
         }
     }

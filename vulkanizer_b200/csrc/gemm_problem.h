@@ -16,7 +16,17 @@ enum DType : int { kF32 = 0, kF16 = 1, kBF16 = 2, kS8 = 3, kS32 = 4, kF64 = 5, k
 // Type of alpha and beta: fixed by the compute type (cublas.cpp:235-258 reads 2, 4 or 8 bytes).
 enum ScalarType : int { kScalarF32 = 0, kScalarF16 = 1, kScalarS32 = 2, kScalarF64 = 3 };
 
-enum Activation : int { kActNone = 0, kActRelu = 1, kActGelu = 2 };
+// kActDRelu / kActDGelu are the backward forms: the value is multiplied by the activation's derivative at the forward
+// pass's input, which the caller hands in as the auxiliary matrix (a bit mask for ReLU, the input itself for GELU).
+enum Activation : int { kActNone = 0, kActRelu = 1, kActGelu = 2, kActDRelu = 3, kActDGelu = 4 };
+
+// What the auxiliary matrix of a cuBLASLt epilogue is (NVIDIA's CUBLASLT_EPILOGUE_*_AUX and D* forms; the reference refuses
+// them, src/cublas/cublasLt.cpp:68-78).
+//   kAuxWriteMask   ReLU forward: bit (row + col * auxLd) of the matrix is 1 where the value before ReLU was > 0
+//   kAuxWriteInput  GELU forward: the value before GELU, in the auxiliary type
+//   kAuxReadMask    ReLU backward: the bit mask a forward pass wrote
+//   kAuxReadInput   GELU backward: the forward pass's input
+enum AuxMode : int { kAuxNone = 0, kAuxWriteMask = 1, kAuxWriteInput = 2, kAuxReadMask = 3, kAuxReadInput = 4 };
 
 constexpr int kMaxMirrors = 7;  // other buffers a result can be written to as well (the other GPUs of an 8-GPU box)
 
@@ -44,7 +54,13 @@ struct EpilogueArgs {
     const void* bias;     // per-row vector of length m, or null
     long long biasStride; // elements, per batch entry
     int typeBias;
+    int biasAlongN;       // 1: the bias vector has length n and is indexed by the column (row-order problems, run transposed)
     int activation;       // Activation
+    void* aux;            // auxiliary matrix of the epilogue (see AuxMode), or null
+    long long auxLd;      // leading dimension of the auxiliary matrix: in elements, or in bits for the ReLU mask (a multiple of 32)
+    long long auxStride;  // per batch entry, same unit
+    int typeAux;          // DType of a GELU input matrix
+    int auxMode;          // AuxMode
     int roundBeforeBias;  // 1: round alpha*acc+beta*C to D's type before bias/activation, as a second pass over D would
     int pointerArrays;    // D (and C) are arrays of pointers indexed by the batch entry
     ScalarArgs scalars;
@@ -72,6 +88,9 @@ struct Problem {
 // Kernel families (launchers return cudaError_t; the dispatch layer maps it to a cuBLAS status).
 cudaError_t launchScale(const Problem& p);    // k = 0: D = act(beta * C + bias)
 cudaError_t launchGeneric(const Problem& p);  // any types / leading dimensions / pointer arrays
+// out[i] = sum_j M[i * strideI + j * strideJ] for i < count, j < length, per batch entry (bias gradients of cuBLASLt epilogues)
+cudaError_t launchVectorSums(const void* M, int type, long long strideI, long long strideJ, long long batchStrideM, int count, int length,
+                             void* out, int typeOut, long long batchStrideOut, int batch, cudaStream_t stream);
 bool gemvTakesFewColumns(const Problem& p);   // n = 2: two right-hand sides for which the matrix-vector kernel streams A once
 cudaError_t launchGemv(const Problem& p);     // m = 1 or n = 1 (or gemvTakesFewColumns)
 bool sgemmEligible(const Problem& p);
@@ -80,8 +99,10 @@ constexpr int kSplitKCounters = 4096;          // arrival counters at the start 
 size_t sgemmSplitKScratchBytes(int m, int n, int splits);
 int sgemmSplitKPlan(const Problem& p, size_t scratchBytes);
 cudaError_t launchSgemmSplitK(const Problem& p, int splits, void* scratch);
+int sgemmSmCount();                           // SMs of the device that was current at the first call
 bool ummaEligible(const Problem& p);
 bool ummaCanMirror(const Problem& p);          // D and the mirrors can be written with bulk stores
+bool ummaWantsScratch(const Problem& p, size_t scratchBytesOnOffer);  // the launch would split along k given that much scratch memory
 cudaError_t launchUmma(const Problem& p);     // tcgen05 tensor cores
 int ummaDeviceStatus();
 int gemvDeviceStatus();                      // 0, or 16 after a bulk copy of the matrix-vector kernel never arrived

@@ -19,6 +19,7 @@
 #include <cstdlib>
 
 #include "epilogue.cuh"
+#include "measure.h"
 
 namespace vkzb {
 namespace {
@@ -430,9 +431,15 @@ cudaError_t launchTyped(const Problem& p, GemvArgs& g, bool rowMajor) {
 // pass over A. (Below about 16 columns a GEMM is bound by reading A, and the tensor-core kernel takes half as long again for
 // that pass: 4096 x n x 4096 f16 took 15.5 us for n = 2 .. 64 against 9.5 us for n = 1. More than two right-hand sides make
 // this kernel's conversions and FMAs the bound.)
+// 0: plain launches; 2 (the default): programmatic serialisation, the blocks start before the prior kernel has ended
+static int overlapMode() {
+    static const int mode = measureKnob("VKZB_GEMV_OVERLAP", 2);
+    return mode;
+}
+
 bool gemvTakesFewColumns(const Problem& p) {
     const auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
-    static const bool disabled = std::getenv("VKZB_GEMV_NO_FEW_COLUMNS") != nullptr;
+    static const bool disabled = measureKnob("VKZB_GEMV_NO_FEW_COLUMNS", 0) != 0;  // measurement builds only
     if (disabled || p.n < 2 || p.n > kMaxVectors || p.m < 64 || p.batch != 1 || p.pointerArrays || p.accType != kF32) return false;
     if (!p.transA || p.transB || p.typeA != p.typeB || (p.typeA != kF16 && p.typeA != kBF16)) return false;
     if (p.k < 8 || p.k % 8 != 0 || p.lda % 8 != 0 || p.ldb % 8 != 0 || !aligned16(p.A) || !aligned16(p.B)) return false;
@@ -449,8 +456,7 @@ cudaError_t launchGemv(const Problem& p) {
         g.M = p.A, g.v = p.B, g.typeM = p.typeA, g.typeV = p.typeB;
         g.rows = p.m, g.rowStride = p.lda, g.colStride = 1, g.incv = 1, g.yIsRow = 0;
         g.vectors = p.n, g.vectorStride = p.ldb;
-        static const char* overlapEnv = std::getenv("VKZB_GEMV_OVERLAP");
-        g.overlap = overlapEnv ? std::atoi(overlapEnv) : 2;
+        g.overlap = overlapMode();
         const BulkShape shape = bulkShape(g.len, g.vectors);
         if (!shape.warps) return cudaErrorInvalidValue;
         return g.typeM == kBF16 ? launchBulk<true>(p, g, shape) : launchBulk<false>(p, g, shape);
@@ -476,10 +482,9 @@ cudaError_t launchGemv(const Problem& p) {
     const bool vec16 = rowMajor && p.accType == kF32 && !p.pointerArrays && g.typeM == g.typeV &&
                        (g.typeM == kF16 || g.typeM == kBF16) && g.incv == 1 && g.len >= 8 && aligned16(g.M) &&
                        aligned16(g.v) && g.rowStride % 8 == 0 && g.strideM % 8 == 0 && g.strideV % 8 == 0;
-    static const char* overlapEnv = std::getenv("VKZB_GEMV_OVERLAP");  // 0: plain launches, no start before the prior kernel ends
-    g.overlap = overlapEnv ? std::atoi(overlapEnv) : 2;
-    static const char* kernelEnv = std::getenv("VKZB_GEMV_KERNEL");  // "rows": never the bulk-copy kernel (for experiments)
-    const BulkShape shape = vec16 && p.batch == 1 && !(kernelEnv && kernelEnv[0] == 'r') ? bulkShape(g.len, 1) : BulkShape{};
+    g.overlap = overlapMode();
+    static const bool rowsOnly = measureKnob("VKZB_GEMV_ROWS_ONLY", 0) != 0;  // measurement builds: never the bulk-copy kernel
+    const BulkShape shape = vec16 && p.batch == 1 && !rowsOnly ? bulkShape(g.len, 1) : BulkShape{};
     if (shape.warps) return g.typeM == kBF16 ? launchBulk<true>(p, g, shape) : launchBulk<false>(p, g, shape);
     if (vec16) {
         for (int first = 0; first < p.batch; first += kMaxGridY) {

@@ -20,6 +20,7 @@ struct GenericArgs {
     int m, n, k;
     int transA, transB, pointerArrays;
     int batchOffset;
+    int colTileBase;  // first tile column of this launch (gridDim.y holds at most 65535 of them)
     EpilogueArgs epi;
 };
 
@@ -37,7 +38,7 @@ __global__ void __launch_bounds__(kThreads) genericGemmKernel(const GenericArgs 
         A = static_cast<const char*>(g.A) + entry * g.strideA * dtypeSize(g.typeA);
         B = static_cast<const char*>(g.B) + entry * g.strideB * dtypeSize(g.typeB);
     }
-    const int row0 = blockIdx.x * kTile, col0 = blockIdx.y * kTile;
+    const int row0 = blockIdx.x * kTile, col0 = (blockIdx.y + g.colTileBase) * kTile;
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     Acc acc[4][4] = {};
     for (int k0 = 0; k0 < g.k; k0 += kStep) {
@@ -85,44 +86,89 @@ __global__ void __launch_bounds__(kThreads) genericGemmKernel(const GenericArgs 
 // k = 0 (or alpha's product absent): D = act(beta C + bias), the "k = 0 scales C" case of the
 // reference's acceptance test (tests/cublas.cpp:662).
 template <typename Acc>
-__global__ void scaleKernel(int m, int n, int batchOffset, const EpilogueArgs e) {
+__global__ void scaleKernel(int m, int n, int batchOffset, int colBase, const EpilogueArgs e) {
     const long long entry = (long long)blockIdx.z + batchOffset;
     Epilogue<Acc> epi;
     epi.init(e, entry);
-    const int row = blockIdx.x * blockDim.x + threadIdx.x, col = blockIdx.y * blockDim.y + threadIdx.y;
+    const int row = blockIdx.x * blockDim.x + threadIdx.x, col = colBase + blockIdx.y * blockDim.y + threadIdx.y;
     if (row < m && col < n) epi.store(row, col, Acc(0));
 }
 
-constexpr int kMaxGridZ = 65535;
+constexpr int kMaxGridZ = 65535, kMaxGridY = 65535;
+
+// out[i] = sum over j of M(i, j), i < count, j < length, where M(i, j) lives at M[i * strideI + j * strideJ]: the bias
+// gradients of the cuBLASLt epilogues (a sum of op(A) or op(B) over k, or of the result over its columns). fp32 sums in a
+// fixed order, so the result is the same from run to run. ALONG_I: consecutive i are adjacent in memory, one thread per sum
+// (its loads coalesce with its neighbours'); otherwise one warp per sum, lanes striding j, then a shuffle tree.
+template <bool ALONG_I>
+__global__ void vectorSumKernel(const void* M, int type, long long strideI, long long strideJ, long long batchStrideM, int count, int length,
+                                void* out, int typeOut, long long batchStrideOut) {
+    const char* src = static_cast<const char*>(M) + (long long)blockIdx.y * batchStrideM * dtypeSize(type);
+    char* dst = static_cast<char*>(out) + (long long)blockIdx.y * batchStrideOut * dtypeSize(typeOut);
+    if constexpr (ALONG_I) {
+        const int i = blockIdx.x * blockDim.x + threadIdx.x;
+        if (i >= count) return;
+        float sum = 0.0f;
+        for (int j = 0; j < length; ++j) sum += loadAs<float>(src, i * strideI + j * strideJ, type);
+        storeFloat(dst, i, typeOut, sum);
+    } else {
+        const int i = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32, lane = threadIdx.x % 32;
+        if (i >= count) return;
+        float sum = 0.0f;
+        for (int j = lane; j < length; j += 32) sum += loadAs<float>(src, i * strideI + j * strideJ, type);
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+        if (lane == 0) storeFloat(dst, i, typeOut, sum);
+    }
+}
 
 }  // namespace
 
-cudaError_t launchGeneric(const Problem& p) {
-    GenericArgs g{p.A, p.B, p.lda, p.ldb, p.strideA, p.strideB, p.typeA, p.typeB, p.m, p.n, p.k,
-                  p.transA, p.transB, p.pointerArrays, 0, p.epi};
-    const dim3 block(kThreads);
-    for (int first = 0; first < p.batch; first += kMaxGridZ) {
-        g.batchOffset = first;
-        const dim3 grid((p.m + kTile - 1) / kTile, (p.n + kTile - 1) / kTile, std::min(p.batch - first, kMaxGridZ));
-        if (p.accType == kF64) genericGemmKernel<double><<<grid, block, 0, p.stream>>>(g);
-        else if (p.accType == kS32) genericGemmKernel<int><<<grid, block, 0, p.stream>>>(g);
-        else genericGemmKernel<float><<<grid, block, 0, p.stream>>>(g);
+cudaError_t launchVectorSums(const void* M, int type, long long strideI, long long strideJ, long long batchStrideM, int count, int length,
+                             void* out, int typeOut, long long batchStrideOut, int batch, cudaStream_t stream) {
+    if (count <= 0 || batch <= 0) return cudaSuccess;
+    for (int first = 0; first < batch; first += kMaxGridY) {
+        const unsigned entries = unsigned(std::min(batch - first, kMaxGridY));
+        const char* src = static_cast<const char*>(M) + (long long)first * batchStrideM * dtypeSize(type);
+        char* dst = static_cast<char*>(out) + (long long)first * batchStrideOut * dtypeSize(typeOut);
+        if (strideI == 1) vectorSumKernel<true><<<dim3((count + 127) / 128, entries), 128, 0, stream>>>(src, type, strideI, strideJ, batchStrideM, count, length, dst, typeOut, batchStrideOut);
+        else vectorSumKernel<false><<<dim3((count + 7) / 8, entries), 256, 0, stream>>>(src, type, strideI, strideJ, batchStrideM, count, length, dst, typeOut, batchStrideOut);
         countLaunch();
         if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
     }
     return cudaSuccess;
 }
 
+cudaError_t launchGeneric(const Problem& p) {
+    GenericArgs g{p.A, p.B, p.lda, p.ldb, p.strideA, p.strideB, p.typeA, p.typeB, p.m, p.n, p.k,
+                  p.transA, p.transB, p.pointerArrays, 0, 0, p.epi};
+    const dim3 block(kThreads);
+    const int tilesN = (p.n + kTile - 1) / kTile;
+    for (int first = 0; first < p.batch; first += kMaxGridZ)
+        for (int tile = 0; tile < tilesN; tile += kMaxGridY) {
+            g.batchOffset = first, g.colTileBase = tile;
+            const dim3 grid((p.m + kTile - 1) / kTile, std::min(tilesN - tile, kMaxGridY), std::min(p.batch - first, kMaxGridZ));
+            if (p.accType == kF64) genericGemmKernel<double><<<grid, block, 0, p.stream>>>(g);
+            else if (p.accType == kS32) genericGemmKernel<int><<<grid, block, 0, p.stream>>>(g);
+            else genericGemmKernel<float><<<grid, block, 0, p.stream>>>(g);
+            countLaunch();
+            if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
+        }
+    return cudaSuccess;
+}
+
 cudaError_t launchScale(const Problem& p) {
     const dim3 block(64, 4);
-    for (int first = 0; first < p.batch; first += kMaxGridZ) {
-        const dim3 grid((p.m + 63) / 64, (p.n + 3) / 4, std::min(p.batch - first, kMaxGridZ));
-        if (p.accType == kF64) scaleKernel<double><<<grid, block, 0, p.stream>>>(p.m, p.n, first, p.epi);
-        else if (p.accType == kS32) scaleKernel<int><<<grid, block, 0, p.stream>>>(p.m, p.n, first, p.epi);
-        else scaleKernel<float><<<grid, block, 0, p.stream>>>(p.m, p.n, first, p.epi);
-        countLaunch();
-        if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
-    }
+    const int groupsN = (p.n + 3) / 4;  // column groups of 4; a launch takes at most 65535 of them
+    for (int first = 0; first < p.batch; first += kMaxGridZ)
+        for (int group = 0; group < groupsN; group += kMaxGridY) {
+            const dim3 grid((p.m + 63) / 64, std::min(groupsN - group, kMaxGridY), std::min(p.batch - first, kMaxGridZ));
+            if (p.accType == kF64) scaleKernel<double><<<grid, block, 0, p.stream>>>(p.m, p.n, first, group * 4, p.epi);
+            else if (p.accType == kS32) scaleKernel<int><<<grid, block, 0, p.stream>>>(p.m, p.n, first, group * 4, p.epi);
+            else scaleKernel<float><<<grid, block, 0, p.stream>>>(p.m, p.n, first, group * 4, p.epi);
+            countLaunch();
+            if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
+        }
     return cudaSuccess;
 }
 

@@ -10,6 +10,7 @@
 #include <cstdlib>
 
 #include "epilogue.cuh"
+#include "measure.h"
 
 namespace vkzb {
 namespace {
@@ -22,6 +23,7 @@ struct SgemmArgs {
     long long lda, ldb, strideA, strideB;
     int m, n, k;
     int batchOffset;
+    int colTileBase;  // first tile column of this launch (gridDim.y holds at most 65535)
     EpilogueArgs epi;
     // split-k (one batch entry only): blockIdx.z is the slice of k, kPer its length; partial tiles and per-tile arrival
     // counters live in scratch memory
@@ -110,7 +112,7 @@ __global__ void __launch_bounds__(kThreads, 2) sgemmKernel(const SgemmArgs g) {
     const long long entry = SPLITK ? 0 : (long long)blockIdx.z + g.batchOffset;
     const float* A = g.A + entry * g.strideA;
     const float* B = g.B + entry * g.strideB;
-    const int row0 = blockIdx.x * BM, col0 = blockIdx.y * BN;
+    const int row0 = blockIdx.x * BM, col0 = (blockIdx.y + g.colTileBase) * BN;
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     const int kBegin = SPLITK ? int(blockIdx.z) * g.kPer : 0;
     const int kEnd = SPLITK ? min(g.k, kBegin + g.kPer) : g.k;
@@ -238,7 +240,7 @@ cudaError_t launchTile(const Problem& p, SgemmArgs& g, dim3 grid) {
 
 constexpr int kMaxGridZ = 65535;
 
-int smCount() {
+int smCountOnce() {
     static const int count = [] {
         int dev = 0, n = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
@@ -249,6 +251,8 @@ int smCount() {
 }
 
 }  // namespace
+
+int sgemmSmCount() { return smCountOnce(); }
 
 bool sgemmEligible(const Problem& p) {
     return p.accType == kF32 && p.typeA == kF32 && p.typeB == kF32 && !p.pointerArrays && p.k > 0 &&
@@ -265,17 +269,17 @@ size_t sgemmSplitKScratchBytes(int m, int n, int splits) {
 // most SMs idle and k is long enough to share out; the partial tiles must fit the scratch memory.
 int sgemmSplitKPlan(const Problem& p, size_t scratchBytes) {
     if (p.batch != 1 || scratchBytes == 0) return 1;
-    static const int forced = [] { const char* v = std::getenv("VKZB_SGEMM_SPLITS"); return v ? std::atoi(v) : 0; }();  // experiment knob
+    static const int forced = measureKnob("VKZB_SGEMM_SPLITS", 0);  // measurement builds only
     if (forced > 0) return sgemmSplitKScratchBytes(p.m, p.n, forced) <= scratchBytes && (long long)((p.m + 63) / 64) * ((p.n + 63) / 64) <= kSplitKCounters ? forced : 1;
     const long long tiles = (long long)((p.m + 63) / 64) * ((p.n + 63) / 64);
-    if (tiles > kSplitKCounters || tiles * 2 > smCount() || p.k < 256) return 1;  // measured: below k = 256 the hand-over costs more than it saves
-    int splits = int(std::min<long long>(std::min<long long>(8, 2LL * smCount() / tiles), p.k / 64));
+    if (tiles > kSplitKCounters || tiles * 2 > smCountOnce() || p.k < 256) return 1;  // measured: below k = 256 the hand-over costs more than it saves
+    int splits = int(std::min<long long>(std::min<long long>(8, 2LL * smCountOnce() / tiles), p.k / 64));
     while (splits > 1 && sgemmSplitKScratchBytes(p.m, p.n, splits) > scratchBytes) --splits;
     return splits;
 }
 
 cudaError_t launchSgemmSplitK(const Problem& p, int splits, void* scratch) {
-    SgemmArgs g{static_cast<const float*>(p.A), static_cast<const float*>(p.B), p.lda, p.ldb, 0, 0, p.m, p.n, p.k, 0, p.epi};
+    SgemmArgs g{static_cast<const float*>(p.A), static_cast<const float*>(p.B), p.lda, p.ldb, 0, 0, p.m, p.n, p.k, 0, 0, p.epi};
     g.splits = splits;
     g.kPer = ((p.k + splits - 1) / splits + 15) / 16 * 16;  // whole shared-memory fills
     g.splits = (p.k + g.kPer - 1) / g.kPer;
@@ -297,86 +301,22 @@ cudaError_t launchSgemm(const Problem& p) {
         if (splits > 1) return launchSgemmSplitK(p, splits, p.scratch);
     }
     SgemmArgs g{static_cast<const float*>(p.A), static_cast<const float*>(p.B), p.lda, p.ldb, p.strideA, p.strideB,
-                p.m, p.n, p.k, 0, p.epi};
+                p.m, p.n, p.k, 0, 0, p.epi};
     // 128 x 128 tiles once they fill the machine; 64 x 64 below that so small products still spread over the SMs
     const long long bigTiles = (long long)((p.m + 127) / 128) * ((p.n + 127) / 128) * p.batch;
-    const bool big = bigTiles >= smCount();
-    for (int first = 0; first < p.batch; first += kMaxGridZ) {
-        g.batchOffset = first;
-        const unsigned gz = unsigned(std::min(p.batch - first, kMaxGridZ));
-        cudaError_t e;
-        if (big) e = launchTile<128, 128>(p, g, dim3((p.m + 127) / 128, (p.n + 127) / 128, gz));
-        else e = launchTile<64, 64>(p, g, dim3((p.m + 63) / 64, (p.n + 63) / 64, gz));
-        countLaunch();
-        if (e != cudaSuccess) return e;
-    }
+    const bool big = bigTiles >= smCountOnce();
+    const int tile = big ? 128 : 64, tilesN = (p.n + tile - 1) / tile;
+    for (int first = 0; first < p.batch; first += kMaxGridZ)
+        for (int col = 0; col < tilesN; col += kMaxGridZ) {  // gridDim.y has the same limit as gridDim.z
+            g.batchOffset = first, g.colTileBase = col;
+            const unsigned gz = unsigned(std::min(p.batch - first, kMaxGridZ)), gy = unsigned(std::min(tilesN - col, kMaxGridZ));
+            cudaError_t e;
+            if (big) e = launchTile<128, 128>(p, g, dim3((p.m + 127) / 128, gy, gz));
+            else e = launchTile<64, 64>(p, g, dim3((p.m + 63) / 64, gy, gz));
+            countLaunch();
+            if (e != cudaSuccess) return e;
+        }
     return cudaSuccess;
 }
 
 }  // namespace vkzb
-
-// ---- the split-k product for callers that may not allocate ---------------------------------------------------------------
-//
-// Some users of this library hand every byte of device memory to their own pool when they start (an inference server
-// sized to the model it serves) or run in a phase where cudaMalloc is off limits because it synchronises the whole device
-// (a latency-bound serving loop). They cannot create a cuBLAS handle, whose creation allocates the split-k scratch, and
-// they cannot let a call allocate on their behalf. For them the same kernel runs on scratch memory that is part of the
-// library image: a file-scope device array, present on every GPU that loads the library for as long as the process lives.
-
-namespace {
-// Room for the arrival counters and 4 MiB of partial tiles: products of up to 256 tiles of 64 x 64 (m * n up to about one
-// million results, for instance 1024 x 1024), cut into as many k slices as still fit.
-constexpr size_t kStaticPartialBytes = size_t(4) << 20;
-constexpr size_t kStaticScratchBytes = vkzb::kSplitKCounters * sizeof(unsigned) + kStaticPartialBytes;
-static __device__ __align__(256) unsigned char g_staticSplitKScratch[kStaticScratchBytes];  // zero at load: the counters start at zero
-
-constexpr int kMaxDevices = 64;
-void* g_staticScratchAddress[kMaxDevices] = {};  // the array's address on each device, looked up once
-}  // namespace
-
-extern "C" __attribute__((visibility("default"))) int vkzbSgemmStaticScratch(cudaStream_t stream, int transa, int transb, int m, int n, int k,
-                                                                             const float* alpha, const float* A, int lda, const float* B,
-                                                                             int ldb, const float* beta, float* C, int ldc) {
-    using namespace vkzb;
-    enum { kSuccess = 0, kNotInitialized = 1, kInvalidValue = 7, kExecutionFailed = 13, kNotSupported = 15 };  // cublasStatus_t values
-    if (m < 0 || n < 0 || k < 0 || !alpha || !beta || unsigned(transa) > 2u || unsigned(transb) > 2u) return kInvalidValue;
-    const int rowsA = transa == 0 ? m : k, rowsB = transb == 0 ? k : n;
-    if (lda < std::max(1, rowsA) || ldb < std::max(1, rowsB) || ldc < std::max(1, m)) return kInvalidValue;
-    if (m == 0 || n == 0) return kSuccess;
-    if (k == 0 || m == 1 || n == 1) return kNotSupported;  // this entry point is the tiled split-k product only
-    const long long tiles = (long long)((m + 63) / 64) * ((n + 63) / 64);
-    if (tiles > kSplitKCounters || sgemmSplitKScratchBytes(m, n, 1) > kStaticScratchBytes) {
-        std::fprintf(stderr, "vkzbSgemmStaticScratch: a %d x %d result needs %zu bytes of scratch memory, the built-in array holds %zu "
-                             "(products of up to 256 tiles of 64 x 64)\n", m, n, sgemmSplitKScratchBytes(m, n, 1), kStaticScratchBytes);
-        return kInvalidValue;
-    }
-    // Set-up, once per device, with that device current: in host code the array's name is only a stand-in, so its device
-    // address has to be asked for. The first call on a device does this.
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return kNotInitialized;
-    if (!g_staticScratchAddress[device]) {
-        void* address = nullptr;
-        if (cudaGetSymbolAddress(&address, g_staticSplitKScratch) != cudaSuccess || !address) {
-            cudaGetLastError();
-            return kNotInitialized;
-        }
-        g_staticScratchAddress[device] = address;
-    }
-    Problem p;
-    p.transA = transa != 0, p.transB = transb != 0;
-    p.m = m, p.n = n, p.k = k, p.batch = 1;
-    p.A = A, p.B = B, p.typeA = p.typeB = kF32;
-    p.lda = lda, p.ldb = ldb;
-    p.accType = kF32;
-    p.epi.D = C, p.epi.C = C;
-    p.epi.ldd = p.epi.ldc = ldc;
-    p.epi.typeD = p.epi.typeC = kF32;
-    p.epi.scalars.type = kScalarF32;
-    p.epi.scalars.alphaHost = double(*alpha), p.epi.scalars.betaHost = double(*beta);
-    p.stream = stream;
-    if (!sgemmEligible(p)) return kInvalidValue;  // A and B must be 4-byte aligned
-    int splits = int(std::min<long long>(std::min<long long>(8, std::max<long long>(1, 2LL * smCount() / tiles)), std::max(1, k / 64)));
-    while (splits > 1 && sgemmSplitKScratchBytes(m, n, splits) > kStaticScratchBytes) --splits;
-    return launchSgemmSplitK(p, splits, g_staticScratchAddress[device]) == cudaSuccess ? kSuccess : kExecutionFailed;
-}
-

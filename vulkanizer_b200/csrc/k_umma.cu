@@ -32,6 +32,7 @@
 #include <mutex>
 
 #include "epilogue.cuh"
+#include "measure.h"
 
 namespace vkzb {
 namespace {
@@ -77,10 +78,6 @@ struct UmmaArgs {
     int boxBytesA, boxBytesB;
     int boxElemsA, boxElemsB;       // elements of m / n per box when MN-major
     int batchMulA, batchMulB;       // 0: the operand is shared by every batch entry
-    int debugSkipStore;             // measurement aid: run everything but the global stores
-    int debugSkipLoad, debugSkipMma;  // measurement aids: main loop without its TMA loads / without its MMAs
-    int debugSplit;                  // measurement aids for the split hand-over: 1 no stores of the accumulator, 2 no fence, 4 no loads of the others
-    int debugEpi;                    // measurement aids for the staged epilogue: 1 no bulk store, 2 no shared-memory writes, 4 no fence
     int tmaStore;                   // D is 16-byte aligned in every dimension: results leave through shared memory and TMA
     int mirrorCount;                // every bulk store of D is repeated into this many other buffers (peer GPUs)
     // Split along k: a unit of work is (tile, split); the splits of a tile run on different CTAs at the same time, each
@@ -388,7 +385,7 @@ __device__ __forceinline__ void drainAccumulator(const Epilogue<Acc>& epi, unsig
 template <int MODE, int NB, int COLS, typename Acc>
 __device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const unsigned (&v)[COLS], int rowInTile, int row, bool rowOk,
                                               int row0, int col, int count, int batchEntry, const CUtensorMap* mapD, const MirrorMaps* mirrors,
-                                              int mirrorCount, unsigned char* staging, unsigned& step, bool issuer, int group, int dbg) {
+                                              int mirrorCount, unsigned char* staging, unsigned& step, bool issuer, int group) {
     using Elem = std::conditional_t<MODE == kStoreF32, float, std::conditional_t<MODE == kStoreS32, int,
                  std::conditional_t<MODE == kStoreF16, __half, __nv_bfloat16>>>;
     const Acc alpha = epi.alpha, beta = epi.beta;
@@ -397,7 +394,7 @@ __device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const un
         if (issuer) tmaStoreWaitRead<1>();
         epilogueBarrier(group);
     }
-    if (!(dbg & 2)) {
+    {
         if (epi.readC && rowOk) {
             const Elem* cin = reinterpret_cast<const Elem*>(epi.C) + (row + col * epi.ldc);
 #pragma unroll
@@ -422,9 +419,9 @@ __device__ __forceinline__ void stageAndStore(const Epilogue<Acc>& epi, const un
             }
         }
     }
-    if (!(dbg & 4)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     epilogueBarrier(group);
-    if (issuer && !(dbg & 1)) {
+    if (issuer) {
         const unsigned src = smemAddr(buf - rowInTile);
         tmaStore3dIssue(mapD, src, row0, col, batchEntry);
         for (int q = 0; q < mirrorCount; ++q) tmaStore3dIssue(&mirrors->map[q], src, row0, col, batchEntry);  // the same block to every peer
@@ -477,8 +474,7 @@ constexpr int kStepCols = 32, kWideBuffers = 4;
 template <int BN, int MODE, int NB, typename Acc>
 __device__ __forceinline__ void drainAccumulatorStaged(const Epilogue<Acc>& epi, unsigned taddr, int rowInTile, int row, bool rowOk, int row0,
                                                            int col0, int n, int batchEntry, const CUtensorMap* mapD, const MirrorMaps* mirrors,
-                                                           int mirrorCount, unsigned char* staging, unsigned& step, bool issuer, int group,
-                                                           int dbg) {
+                                                           int mirrorCount, unsigned char* staging, unsigned& step, bool issuer, int group) {
 #pragma unroll 1
     for (int c = group * kStepCols; c < BN; c += kStepCols * kEpilogueGroups) {
         const int count = n - (col0 + c);
@@ -487,7 +483,7 @@ __device__ __forceinline__ void drainAccumulatorStaged(const Epilogue<Acc>& epi,
         tmemLoad32Issue(taddr + c, v);
         tmemWaitLoads();
         stageAndStore<MODE, NB, kStepCols>(epi, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, mirrors, mirrorCount, staging,
-                                                         step, issuer, group, dbg);
+                                                         step, issuer, group);
     }
 }
 
@@ -511,7 +507,7 @@ __device__ __noinline__ void drainAccumulatorStagedSplit(const Epilogue<Acc>& ep
         for (int q = 0; q < kStepCols / 4; ++q) first[q] = __ldcg(splitBase + size_t(firstOther) * tileV4 + size_t(c / 4 + q) * kBM);
         tmemWaitLoads();
         splitSum<Acc, kStepCols>(v, first, firstOther, splitBase, tileV4, c, splits, split);
-        stageAndStore<MODE, NB, kStepCols>(epi, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, nullptr, 0, staging, step, issuer, group, 0);
+        stageAndStore<MODE, NB, kStepCols>(epi, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, nullptr, 0, staging, step, issuer, group);
     }
 }
 
@@ -524,7 +520,9 @@ __device__ __noinline__ void drainAccumulatorStagedPost(const Epilogue<float>& e
     using Elem = std::conditional_t<MODE == kStoreF32, float, std::conditional_t<MODE == kStoreF16, __half, __nv_bfloat16>>;
     Epilogue<float> plain = epi;
     plain.alpha = 1.0f, plain.readC = false;
-    const float biasValue = epi.bias && rowOk ? loadAs<float>(epi.bias, row, epi.typeBias) : 0.0f;
+    const float rowBias = epi.bias && rowOk && !epi.biasAlongN ? loadAs<float>(epi.bias, row, epi.typeBias) : 0.0f;
+    const bool colBias = epi.bias && epi.biasAlongN;
+    const int lane = threadIdx.x % 32;
 #pragma unroll 1
     for (int c = group * kStepCols; c < BN; c += kStepCols * kEpilogueGroups) {
         const int count = n - (col0 + c);
@@ -541,10 +539,31 @@ __device__ __noinline__ void drainAccumulatorStagedPost(const Epilogue<float>& e
                 else if constexpr (MODE == kStoreF16) r += epi.beta * __half2float(cin[j * epi.ldc]);
                 else r += epi.beta * __bfloat162float(cin[j * epi.ldc]);
             }
-            v[j] = __float_as_uint(epi.finish(r, biasValue));
+            const float biasValue = colBias && j < count ? loadAs<float>(epi.bias, col0 + c + j, epi.typeBias) : rowBias;
+            if (!epi.aux) {
+                v[j] = __float_as_uint(epi.finish(r, biasValue));
+                continue;
+            }
+            // with an auxiliary matrix: a warp holds 32 consecutive rows of one column, so a ReLU mask leaves (and arrives)
+            // as one 32-bit word per warp and column, a GELU input as one 128-byte (or 64-byte) line
+            if (epi.roundBeforeBias) r = roundTo(r, epi.typeD);
+            r += biasValue;
+            const long long at = row + (long long)(col0 + c + j) * epi.auxLd;  // row - lane is a multiple of 32, and so is auxLd for masks
+            const bool live = j < count;
+            if (epi.auxMode == kAuxWriteMask) {
+                const unsigned word = __ballot_sync(0xFFFFFFFFu, rowOk && r > 0.0f);
+                if (lane == 0 && live) reinterpret_cast<unsigned*>(epi.aux)[at >> 5] = word;
+            } else if (epi.auxMode == kAuxWriteInput) {
+                if (rowOk && live) storeFloat(epi.aux, at, epi.typeAux, r);
+            }
+            if (epi.activation == kActRelu) r = fmaxf(r, 0.0f);
+            else if (epi.activation == kActGelu) r = geluTanh(r);
+            else if (epi.activation == kActDRelu) r = live && ((reinterpret_cast<const unsigned*>(epi.aux)[(at - lane) >> 5] >> lane) & 1u) ? r : 0.0f;
+            else if (epi.activation == kActDGelu) r = rowOk && live ? r * geluTanhGrad(loadAs<float>(epi.aux, at, epi.typeAux)) : 0.0f;
+            v[j] = __float_as_uint(r);
         }
         stageAndStore<MODE, NB, kStepCols>(plain, v, rowInTile, row, rowOk, row0, col0 + c, count, batchEntry, mapD, mirrors, mirrorCount, staging, step, issuer,
-                                           group, 0);
+                                           group);
     }
 }
 
@@ -561,7 +580,7 @@ __device__ __forceinline__ void epilogueBarrierAll() { asm volatile("bar.sync 3,
 // from run to run) and writes D. The others are done with the tile. Nobody waits for anybody.
 template <int BN>
 __device__ __noinline__ bool splitDump(unsigned* counters, unsigned* partials, int splits, unsigned taddr, long long slot, int split, int quarter,
-                                       int lane, int group, volatile int* lastFlag, int dbg) {
+                                       int lane, int group, volatile int* lastFlag) {
     constexpr int kStride = kStoreCols * kEpilogueGroups, kSteps = BN / kStride, kBatch = kSteps < 4 ? kSteps : 4;
     uint4* mine = reinterpret_cast<uint4*>(partials + (size_t(slot) * splits + split) * (size_t(BN) * kBM)) + quarter * 32 + lane;
 #pragma unroll 1
@@ -570,14 +589,13 @@ __device__ __noinline__ bool splitDump(unsigned* counters, unsigned* partials, i
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) tmemLoad16Issue(taddr + c + b * kStride, v[b]);
         tmemWaitLoads();
-        if (!(dbg & 1))
 #pragma unroll
         for (int b = 0; b < kBatch; ++b)
 #pragma unroll
             for (int q = 0; q < 4; ++q)
                 __stcg(mine + size_t((c + b * kStride) / 4 + q) * kBM, make_uint4(v[b][4 * q], v[b][4 * q + 1], v[b][4 * q + 2], v[b][4 * q + 3]));
     }
-    if (!(dbg & 2)) __threadfence();
+    __threadfence();
     epilogueBarrierAll();
     if (threadIdx.x == 64) {
         const unsigned before = atomicAdd(counters + slot, 1u);
@@ -722,7 +740,6 @@ __device__ __forceinline__ void mmaIssuerLoop(const UmmaArgs& g, unsigned smemBa
     const unsigned long long hi = static_cast<unsigned long long>(g.descHi) << 32;
     const unsigned lboA = g.lboA << 16, lboB = g.lboB << 16, stepA = g.kStepA, stepB = g.kStepB, idesc = g.idesc;
     const int slices = g.numKSlices;
-    const bool skipLoad = g.debugSkipLoad != 0, skipMma = g.debugSkipMma != 0;
     int stage = 0;
     unsigned phase = 0, tileCount = 0;
     bool ok = true;
@@ -734,17 +751,15 @@ __device__ __forceinline__ void mmaIssuerLoop(const UmmaArgs& g, unsigned smemBa
         const int split = int(unit % g.splits);
         const int ksBegin = int((long long)slices * split / g.splits), ksEnd = int((long long)slices * (split + 1) / g.splits);
         for (int ks = ksBegin; ks < ksEnd; ++ks) {
-            if (!skipLoad && !(ok = mbarWait(fullBar + 8 * stage, phase, abortFlag, kStatusMmaFullWait))) break;
+            if (!(ok = mbarWait(fullBar + 8 * stage, phase, abortFlag, kStatusMmaFullWait))) break;
             tcgen05FenceAfter();
             const unsigned addrA = smemBase + stage * Plan::kStageBytes, addrB = addrA + kStageABytes;
             const unsigned long long descA = hi | (((addrA & 0x3FFFFu) >> 4) | lboA), descB = hi | (((addrB & 0x3FFFFu) >> 4) | lboB);
             if (electOne()) {
-                if (!skipMma) {
-                    ummaIssueFixed<KIND, PAIR>(tmemD, descA, descB, idesc, ks != ksBegin ? 1u : 0u);
+                ummaIssueFixed<KIND, PAIR>(tmemD, descA, descB, idesc, ks != ksBegin ? 1u : 0u);
 #pragma unroll
-                    for (int j = 1; j < kMmasPerStage; ++j)  // the low word cannot carry into the high one: addresses stay below 2^14 units
-                        ummaIssueFixed<KIND, PAIR>(tmemD, descA + j * stepA, descB + j * stepB, idesc, 1u);
-                }
+                for (int j = 1; j < kMmasPerStage; ++j)  // the low word cannot carry into the high one: addresses stay below 2^14 units
+                    ummaIssueFixed<KIND, PAIR>(tmemD, descA + j * stepA, descB + j * stepB, idesc, 1u);
                 // the stage may be refilled (in both CTAs of a pair) once these MMAs have read it
                 if constexpr (PAIR) tcgen05CommitPair(emptyBar + 8 * stage);
                 else tcgen05Commit(emptyBar + 8 * stage);
@@ -819,7 +834,7 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
 
     if (warp == 0) {
         // ---- TMA producer ----
-        if (lane == 0 && !g.debugSkipLoad) {
+        if (lane == 0) {
             if (!g.mnMajorA && !g.mnMajorB)
                 producerLoop<BN, PAIR, WIDE, true>(g, &mapA, &mapB, smemBase, fullBar, emptyBar, ctaRank, firstUnit, unitStride, abortFlag);
             else
@@ -867,8 +882,7 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
             const auto handOver = [&](bool staged, auto accTag) {
                 if (g.splits == 1) return true;
                 const long long slot = PAIR ? tile * 2 + ctaRank : tile;
-                if (!splitDump<BN>(g.splitCounters, g.splitPartials, g.splits, taddr, slot, split, quarter, lane, group, abortFlag + 1, g.debugSplit)) return false;
-                if (staged && (g.debugSplit & 4)) return true;
+                if (!splitDump<BN>(g.splitCounters, g.splitPartials, g.splits, taddr, slot, split, quarter, lane, group, abortFlag + 1)) return false;
                 if (staged) splitBase = reinterpret_cast<const uint4*>(g.splitPartials) + size_t(slot) * g.splits * (size_t(BN) * kBM / 4) + rowInTile;
                 else splitSumToTmem<BN, decltype(accTag)>(g.splitPartials, g.splits, taddr, slot, split, quarter, lane, group);
                 return true;
@@ -876,21 +890,21 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
             if (g.kind == kKindI8) {
                 Epilogue<int> epi;
                 epi.init(g.epi, t.batch);
-                const bool staged = g.tmaStore && epi.mode == kStoreS32 && !g.debugSkipStore;
+                const bool staged = g.tmaStore && epi.mode == kStoreS32;
                 if (!handOver(staged, int(0))) {
                     // another split of this tile writes D
                 } else if (staged) {
                     if (splitBase) drainAccumulatorStagedSplit<BN, kStoreS32, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
-                    else drainAccumulatorStaged<BN, kStoreS32, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
+                    else drainAccumulatorStaged<BN, kStoreS32, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else {
-                    drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
+                    drainAccumulator<BN>(epi, taddr, row, rowOk, col0, g.n, group);
                 }
             } else {
                 Epilogue<float> epi;
                 epi.init(g.epi, t.batch);
-                const bool staged = g.tmaStore && !g.debugSkipStore && epi.mode != kStoreSlow;
+                const bool staged = g.tmaStore && epi.mode != kStoreSlow;
                 // bias, activation, extra rounding: staged as well when C and D alone would be (after a split the sum goes back to TMEM first)
-                const bool stagedPost = g.tmaStore && !g.debugSkipStore && epi.post && epi.typedMode != kStoreSlow;
+                const bool stagedPost = g.tmaStore && epi.post && epi.typedMode != kStoreSlow;
                 constexpr int kBuffers = WIDE ? kWideBuffers : 2;
                 if (!handOver(staged, float(0))) {
                     // another split of this tile writes D
@@ -902,15 +916,15 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                     drainAccumulatorStagedPost<BN, kStoreBF16, kBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else if (staged && epi.mode == kStoreF32) {
                     if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF32, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
-                    else drainAccumulatorStaged<BN, kStoreF32, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
+                    else drainAccumulatorStaged<BN, kStoreF32, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else if (staged && epi.mode == kStoreF16) {
                     if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF16, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
-                    else drainAccumulatorStaged<BN, kStoreF16, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
+                    else drainAccumulatorStaged<BN, kStoreF16, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else if (staged && epi.mode == kStoreBF16) {
                     if (splitBase) drainAccumulatorStagedSplit<BN, kStoreBF16, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
-                    else drainAccumulatorStaged<BN, kStoreBF16, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group, g.debugEpi);
+                    else drainAccumulatorStaged<BN, kStoreBF16, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else {
-                    drainAccumulator<BN>(epi, taddr, row, rowOk && !g.debugSkipStore, col0, g.n, group);
+                    drainAccumulator<BN>(epi, taddr, row, rowOk, col0, g.n, group);
                 }
             }
             tcgen05FenceBefore();
@@ -1038,6 +1052,8 @@ cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtenso
                        int slot, cudaStream_t stream) {
     using Plan = SmemPlan<BN, PAIR, WIDE>;
     DeviceInfo& d = deviceInfo();
+    static std::mutex setupMutex;  // the first launch of a variant on a device sets it up; host threads may race to be first
+    std::unique_lock<std::mutex> setup(setupMutex);
     if (!d.attrSet[slot]) {
         if (cudaError_t e = cudaFuncSetAttribute(ummaGemmKernel<BN, PAIR, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kDynamicBytes);
             e != cudaSuccess)
@@ -1058,6 +1074,7 @@ cudaError_t launchWith(const UmmaArgs& g, const CUtensorMap& mapA, const CUtenso
         }
         d.attrSet[slot] = true;
     }
+    setup.unlock();
     countLaunch();
     if (!PAIR) {
         const unsigned grid = unsigned(std::min<long long>(g.totalUnits, d.sms));
@@ -1105,18 +1122,29 @@ bool ummaCanMirror(const Problem& p) {
     return true;
 }
 
-cudaError_t launchUmma(const Problem& p) {
-    const int kind = ummaKindOf(p);
+namespace {
+
+// What a launch will look like: tile shape, pairing, epilogue variant and split count. Computed from the problem and the
+// scratch memory on offer alone, so the dispatch layer can ask beforehand whether a call wants scratch memory at all.
+struct UmmaPlan {
+    int bn = 0;
+    bool pair = false, wide = false;
+    int splits = 1;
+    int tilesM = 0, tilesN = 0;
+    long long totalTiles = 0, kSlices = 0;
+};
+
+UmmaPlan planUmma(const Problem& p, size_t scratchBytes) {
     const int es = elemSizeOf(p.typeA);
     DeviceInfo& d = deviceInfo();
-
+    UmmaPlan plan;
     // Tile shape: the candidate that needs the least time by a simple model. The main loop is bound by how fast operand
     // slices arrive from L2, so the cost of a candidate is its number of waves over the machine times the rows of 128
     // bytes one CTA fetches per k slice: 128 + BN for a CTA on its own, 128 + BN / 2 in a two-CTA pair (tile 256 x BN).
     const int mnBoxElems = kSliceBytes / es;  // an MN-major operand arrives in boxes of 128 bytes of m or n
-    static const int forcedBn = [] { const char* v = std::getenv("VKZB_UMMA_BN"); return v ? std::atoi(v) : 0; }();
-    static const int forcedPair = [] { const char* v = std::getenv("VKZB_UMMA_PAIR"); return v ? std::atoi(v) : -1; }();
-    static const int forcedSplits = [] { const char* v = std::getenv("VKZB_UMMA_SPLITS"); return v ? std::atoi(v) : 0; }();
+    // forced choices exist only in a measurement build (measure.h)
+    static const int forcedBn = measureKnob("VKZB_UMMA_BN", 0), forcedPair = measureKnob("VKZB_UMMA_PAIR", -1);
+    static const int forcedSplits = measureKnob("VKZB_UMMA_SPLITS", 0);
     const long long kSlices = (p.k + kSliceBytes / es - 1) / (kSliceBytes / es);
     int bn = 0;
     bool pair = false;
@@ -1137,38 +1165,47 @@ cudaError_t launchUmma(const Problem& p) {
         }
     }
     if (!bn) bn = p.transB && mnBoxElems > 64 ? 128 : 64, pair = false;  // forced values that fit nothing: smallest legal tile
-    const int tilesM = (p.m + (pair ? 255 : 127)) / (pair ? 256 : 128);
-    static const int skipStore = [] { const char* v = std::getenv("VKZB_UMMA_SKIP_STORE"); return v ? std::atoi(v) : 0; }();
-    static const int forcedWide = [] { const char* v = std::getenv("VKZB_UMMA_WIDE"); return v ? std::atoi(v) : -1; }();
-    static const int debugBits = [] { const char* v = std::getenv("VKZB_UMMA_DEBUG"); return v ? std::atoi(v) : 0; }();
-
+    static const int forcedWide = measureKnob("VKZB_UMMA_WIDE", -1);
     // few k slices per tile: the launch is bound by writing D, so it takes the variant with more epilogue buffers
     // (measured at 4096 x 4096 x k, f16: k = 512, 8 slices, 29.1 us wide against 30.7; k = 1024, 16 slices, 38.8 against 35.4)
-    const bool wide = forcedWide >= 0 ? forcedWide != 0 : (p.k + kSliceBytes / es - 1) / (kSliceBytes / es) <= 8;
-    UmmaArgs g{};
-    g.m = p.m, g.n = p.n, g.k = p.k, g.batch = p.batch;
-    g.tilesM = tilesM, g.tilesN = (p.n + bn - 1) / bn;
-    g.groupM = pair ? 8 : 16;  // about as many tile rows as tile columns among the tiles in flight
-    g.totalTiles = (long long)g.tilesM * g.tilesN * p.batch;
-    // Splitting along k through the handle's scratch memory. Measured, it pays for a small result with a long k, where the
+    const bool wide = forcedWide >= 0 ? forcedWide != 0 : kSlices <= 8;
+    plan.bn = bn, plan.pair = pair, plan.wide = wide, plan.kSlices = kSlices;
+    plan.tilesM = (p.m + (pair ? 255 : 127)) / (pair ? 256 : 128), plan.tilesN = (p.n + bn - 1) / bn;
+    plan.totalTiles = (long long)plan.tilesM * plan.tilesN * p.batch;
+    // Splitting along k through scratch memory. Measured, it pays for a small result with a long k, where the
     // tiles leave most SMs idle (4096 x 16 x 11008 f16: 50 -> 27 us; 512 x 512 x 16384 int8: 37 -> 19 us), and costs
     // time once the accumulators that travel through scratch memory are megabytes (4096 x 512 x 11008: 31 -> 43 us; that
     // main loop is bound by fetching its operands, which a split does not speed up). So: results of at most 2 MiB of
     // accumulators, all units in one wave, at least 8 k slices per split, as many splits (up to 4) as that allows.
-    int splits = 1;
-    {
-        const long long halfTiles = g.totalTiles * (pair ? 2 : 1), slots = pair ? pairClusters() : d.sms;
-        const size_t room = p.scratch && p.scratchBytes > kSplitKCounters * sizeof(unsigned) ? p.scratchBytes - kSplitKCounters * sizeof(unsigned) : 0;
-        const auto allowed = [&](int s) {
-            return !wide && p.mirrorCount == 0 && kSlices / s >= 8 && halfTiles <= kSplitKCounters && size_t(halfTiles) * s * bn * kBM * 4 <= room;
-        };
-        if (forcedSplits > 1) {
-            if (allowed(forcedSplits)) splits = forcedSplits;
-        } else if (!forcedSplits && (long long)p.m * p.n * p.batch * 4 <= (2 << 20)) {
-            for (int s = 4; s > 1 && splits == 1; --s)
-                if (g.totalTiles * s <= slots && allowed(s)) splits = s;
-        }
+    const long long halfTiles = plan.totalTiles * (pair ? 2 : 1), slots = pair ? pairClusters() : d.sms;
+    const size_t room = scratchBytes > kSplitKCounters * sizeof(unsigned) ? scratchBytes - kSplitKCounters * sizeof(unsigned) : 0;
+    const auto allowed = [&](int s) {
+        return !wide && p.mirrorCount == 0 && !p.pointerArrays && kSlices / s >= 8 && halfTiles <= kSplitKCounters && size_t(halfTiles) * s * bn * kBM * 4 <= room;
+    };
+    if (forcedSplits > 1) {
+        if (allowed(forcedSplits)) plan.splits = forcedSplits;
+    } else if (!forcedSplits && (long long)p.m * p.n * p.batch * 4 <= (2 << 20)) {
+        for (int s = 4; s > 1 && plan.splits == 1; --s)
+            if (plan.totalTiles * s <= slots && allowed(s)) plan.splits = s;
     }
+    return plan;
+}
+
+}  // namespace
+
+bool ummaWantsScratch(const Problem& p, size_t scratchBytesOnOffer) { return planUmma(p, scratchBytesOnOffer).splits > 1; }
+
+cudaError_t launchUmma(const Problem& p) {
+    const int kind = ummaKindOf(p);
+    const int es = elemSizeOf(p.typeA);
+    const UmmaPlan plan = planUmma(p, p.scratch ? p.scratchBytes : 0);
+    const int bn = plan.bn, splits = plan.splits;
+    const bool pair = plan.pair, wide = plan.wide;
+    UmmaArgs g{};
+    g.m = p.m, g.n = p.n, g.k = p.k, g.batch = p.batch;
+    g.tilesM = plan.tilesM, g.tilesN = plan.tilesN;
+    g.groupM = pair ? 8 : 16;  // about as many tile rows as tile columns among the tiles in flight
+    g.totalTiles = plan.totalTiles;
     g.splits = splits;
     g.totalUnits = g.totalTiles * splits;
     g.splitCounters = static_cast<unsigned*>(p.scratch);
@@ -1198,14 +1235,10 @@ cudaError_t launchUmma(const Problem& p) {
     g.batchMulA = p.batch > 1 && p.strideA != 0;
     g.batchMulB = p.batch > 1 && p.strideB != 0;
     g.epi = p.epi;
-    g.debugSkipStore = skipStore || (debugBits & 1);
-    g.debugSkipLoad = (debugBits & 2) != 0, g.debugSkipMma = (debugBits & 4) != 0;
-    g.debugEpi = (debugBits >> 5) & 7;
-    g.debugSplit = (debugBits >> 8) & 7;
 
     CUtensorMap mapA, mapB;
     const long long batchA = g.batchMulA ? p.batch : 1, batchB = g.batchMulB ? p.batch : 1;
-    static const bool noChunks = std::getenv("VKZB_UMMA_NO_CHUNKS") != nullptr;
+    static const bool noChunks = measureKnob("VKZB_UMMA_NO_CHUNKS", 0) != 0;
     g.chunkedA = g.mnMajorA && !noChunks && g.boxesA > 1 && p.m % g.boxElemsA == 0;
     g.chunkedB = g.mnMajorB && !noChunks && g.boxesB > 1 && p.n % g.boxElemsB == 0;
     // (a driver that refuses the 4-d view leaves the operand on its per-chunk boxes)
@@ -1226,8 +1259,7 @@ cudaError_t launchUmma(const Problem& p) {
     // would let it write into the padding between m and ldd: those shapes keep the direct stores too.
     g.tmaStore = !e.pointerArrays && (reinterpret_cast<uintptr_t>(e.D) & 15) == 0 && (e.ldd * esD) % 16 == 0 && ((long long)p.m * esD) % 16 == 0 &&
                  (p.batch == 1 || (e.strideD * esD) % 16 == 0) && (p.batch == 1 || e.strideD != 0);
-    static const int noTmaStore = [] { const char* v = std::getenv("VKZB_UMMA_DIRECT_STORE"); return v ? std::atoi(v) : 0; }();
-    if (noTmaStore) g.tmaStore = 0;
+    if (measureKnob("VKZB_UMMA_DIRECT_STORE", 0)) g.tmaStore = 0;
     MirrorMaps mirrors{};
     g.mirrorCount = 0;
     if (g.tmaStore) {
