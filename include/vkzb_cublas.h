@@ -194,6 +194,41 @@ cublasStatus_t cublasSgemv_v2_64(cublasHandle_t handle, cublasOperation_t trans,
                                  const float* alpha, const float* A, int64_t lda, const float* x, int64_t incx,
                                  const float* beta, float* y, int64_t incy);              /* cublas.cpp:1204 */
 
+/* ---- triangular solves and batched LU / QR (LAPACK conventions; csrc/k_solve.cu) ----
+ * op(A) X = alpha B (left) or X op(A) = alpha B (right), X overwriting B; only the `uplo` triangle of A is read. */
+cublasStatus_t cublasStrsm_v2(cublasHandle_t handle, cublasSideMode_t side, cublasFillMode_t uplo, cublasOperation_t trans,
+                              cublasDiagType_t diag, int m, int n, const float* alpha, const float* A, int lda, float* B,
+                              int ldb);                                                   /* cublas.cpp:1402 */
+cublasStatus_t cublasDtrsm_v2(cublasHandle_t handle, cublasSideMode_t side, cublasFillMode_t uplo, cublasOperation_t trans,
+                              cublasDiagType_t diag, int m, int n, const double* alpha, const double* A, int lda, double* B,
+                              int ldb);                                                   /* cublas.cpp:1408 */
+cublasStatus_t cublasStrsmBatched(cublasHandle_t handle, cublasSideMode_t side, cublasFillMode_t uplo, cublasOperation_t trans,
+                                  cublasDiagType_t diag, int m, int n, const float* alpha, const float* const A[], int lda,
+                                  float* const B[], int ldb, int batchCount);             /* cublas.cpp:1264 */
+cublasStatus_t cublasDtrsmBatched(cublasHandle_t handle, cublasSideMode_t side, cublasFillMode_t uplo, cublasOperation_t trans,
+                                  cublasDiagType_t diag, int m, int n, const double* alpha, const double* const A[], int lda,
+                                  double* const B[], int ldb, int batchCount);            /* cublas.cpp:1414 */
+/* P A = L U per matrix, in place: P receives 1-based pivot rows (n per matrix; null: no pivoting), the DEVICE array `info`
+ * the first zero pivot of each matrix (0: none). */
+cublasStatus_t cublasSgetrfBatched(cublasHandle_t handle, int n, float* const A[], int lda, int* P, int* info,
+                                   int batchSize);                                        /* cublas.cpp:1336 */
+cublasStatus_t cublasDgetrfBatched(cublasHandle_t handle, int n, double* const A[], int lda, int* P, int* info,
+                                   int batchSize);                                        /* cublas.cpp:1340 */
+/* op(A) X = B from the factorization above, X overwriting B. `info` is a HOST integer: 0, or minus the position of the first
+ * invalid argument. */
+cublasStatus_t cublasSgetrsBatched(cublasHandle_t handle, cublasOperation_t trans, int n, int nrhs, const float* const A[],
+                                   int lda, const int* devIpiv, float* const B[], int ldb, int* info,
+                                   int batchSize);                                        /* cublas.cpp:1344 */
+cublasStatus_t cublasDgetrsBatched(cublasHandle_t handle, cublasOperation_t trans, int n, int nrhs, const double* const A[],
+                                   int lda, const int* devIpiv, double* const B[], int ldb, int* info,
+                                   int batchSize);                                        /* cublas.cpp:1349 */
+/* A = Q R per matrix, in place as LAPACK's geqrf stores it (R on and above the diagonal, the reflectors below, their scalars
+ * in tau[i][0 .. min(m, n))). `info` is a HOST integer as for getrs. */
+cublasStatus_t cublasSgeqrfBatched(cublasHandle_t handle, int m, int n, float* const A[], int lda, float* const tau[],
+                                   int* info, int batchSize);                             /* cublas.cpp:1420 */
+cublasStatus_t cublasDgeqrfBatched(cublasHandle_t handle, int m, int n, double* const A[], int lda, double* const tau[],
+                                   int* info, int batchSize);                             /* cublas.cpp:1425 */
+
 #ifdef __cplusplus
 }
 #endif

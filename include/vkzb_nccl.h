@@ -45,6 +45,7 @@ typedef enum {
     ncclInvalidUsage = 5, ncclRemoteError = 6, ncclInProgress = 7, ncclNumResults = 8
 } ncclResult_t;
 typedef enum { ncclSum = 0, ncclProd = 1, ncclMax = 2, ncclMin = 3, ncclAvg = 4, ncclNumOps = 5 } ncclRedOp_t;
+typedef enum { ncclScalarDevice = 0, ncclScalarHostImmediate = 1 } ncclScalarResidence_t;
 typedef enum {
     ncclInt8 = 0, ncclUint8 = 1, ncclInt32 = 2, ncclUint32 = 3, ncclInt64 = 4, ncclUint64 = 5, ncclFloat16 = 6, ncclFloat32 = 7,
     ncclFloat64 = 8, ncclBfloat16 = 9, ncclFloat8e4m3 = 10, ncclFloat8e5m2 = 11, ncclNumTypes = 12
@@ -85,6 +86,18 @@ ncclResult_t ncclAlltoAll(const void* sendbuff, void* recvbuff, size_t count, nc
                           cudaStream_t stream);                                                     /* nccl.cpp:696 */
 ncclResult_t ncclGather(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, int root, ncclComm_t comm,
                         cudaStream_t stream);                                                       /* nccl.cpp:701 */
+/* Point to point: the n-th send of a rank to a peer matches that peer's n-th receive from the rank. A send completes on its
+ * stream when the receiver has copied the data. Issue a send and the receive it depends on in one group (as NCCL asks). */
+ncclResult_t ncclSend(const void* sendbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm,
+                      cudaStream_t stream);                                                         /* nccl.cpp:706 */
+ncclResult_t ncclRecv(void* recvbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm,
+                      cudaStream_t stream);                                                         /* nccl.cpp:711 */
+/* A sum whose contributions are multiplied by a per-rank scalar first; usable wherever a ncclRedOp_t is until destroyed. */
+ncclResult_t ncclRedOpCreatePreMulSum(ncclRedOp_t* op, void* scalar, ncclDataType_t datatype, ncclScalarResidence_t residence,
+                                      ncclComm_t comm);                                             /* nccl.cpp:650 */
+ncclResult_t ncclRedOpDestroy(ncclRedOp_t op, ncclComm_t comm);                                     /* nccl.cpp:662 */
+/* Ranks passing the same color form a new communicator, ordered by (key, rank); NCCL_SPLIT_NOCOLOR yields none. */
+ncclResult_t ncclCommSplit(ncclComm_t comm, int color, int key, ncclComm_t* newcomm, ncclConfig_t* config); /* nccl.cpp:561 */
 /* Operations issued between GroupStart and GroupEnd are started together at GroupEnd (needed when one thread drives several
  * communicators). */
 ncclResult_t ncclGroupStart(void);                                                                  /* nccl.cpp:717 */
@@ -99,9 +112,13 @@ ncclResult_t vkzbNcclExchangeBuffer(ncclComm_t comm, void* buffer, void** peers)
  * stream has reached its barrier (so every earlier write into peer memory has landed). */
 ncclResult_t vkzbNcclBarrier(ncclComm_t comm, cudaStream_t stream);
 
-/* Not served yet, answering ncclInvalidUsage like the reference's stubs (src/nccl/nccl_stubs.cpp:30-36): ncclSend, ncclRecv,
- * ncclCommSplit, ncclCommInitRankScalable, ncclRedOpCreatePreMulSum, ncclRedOpDestroy, ncclGroupSimulateEnd and the 17 names
- * of nccl_stubs.cpp:11-27. */
+/* Diagnostic: launches the device-side barrier against a peer that does not exist, so its bounded wait (VKZB_NCCL_DEVICE_WAIT_MS,
+ * default 20 s) runs out; afterwards ncclCommGetAsyncError reports ncclRemoteError. Nothing faults, the context stays usable.
+ * Destroy the communicator afterwards. */
+ncclResult_t vkzbNcclSelfTestLostPeer(ncclComm_t comm, cudaStream_t stream);
+
+/* Not served, answering ncclInvalidUsage like the reference's stubs (src/nccl/nccl_stubs.cpp:30-36): ncclCommInitRankScalable,
+ * ncclGroupSimulateEnd and the 17 names of nccl_stubs.cpp:11-27. */
 
 #ifdef __cplusplus
 }

@@ -107,6 +107,65 @@ def main():
             comm.all_gather(src.data_ptr(), dst.data_ptr(), big, "float32", s)
         stream.synchronize()
         assert torch.equal(dst.view(nranks, big)[:, ::4096].cpu(), torch.arange(1, nranks + 1, dtype=torch.float32)[:, None].expand(nranks, big // 4096))
+    with torch.cuda.stream(stream):
+        # one group of ten collectives on this communicator, each with buffers of its own: more than the ring of posted
+        # addresses holds, so the group runs in batches and no operation may see another one's buffers
+        ins = [dev(val(rank) + 7 * j) for j in range(10)]
+        outs = [torch.zeros(n * nranks if j % 2 == 0 else n, device="cuda") for j in range(10)]
+        comm.group_start()
+        for j in range(10):
+            if j % 2 == 0:
+                comm.all_gather(ins[j].data_ptr(), outs[j].data_ptr(), n, "float32", s)
+            else:
+                comm.all_reduce(ins[j].data_ptr(), outs[j].data_ptr(), n, "float32", capi.NCCL_SUM, s)
+        comm.group_end()
+        stream.synchronize()
+        for j in range(10):
+            want = np.concatenate([val(r) + 7 * j for r in range(nranks)]) if j % 2 == 0 else sum(val(r) + 7 * j for r in range(nranks))
+            assert np.array_equal(outs[j].cpu().numpy(), want), f"grouped operation {j}"
+        # twenty ungrouped collectives in a row with changing buffers: the ring wraps twice, a fast rank may not overwrite
+        # addresses a slower one has yet to read
+        for j in range(20):
+            src_j = dev(val(rank) + j)
+            dst_j = torch.zeros(n * nranks, device="cuda")
+            comm.all_gather(src_j.data_ptr(), dst_j.data_ptr(), n, "float32", s)
+            stream.synchronize()
+            assert np.array_equal(dst_j.cpu().numpy(), np.concatenate([val(r) + j for r in range(nranks)])), f"gather {j}"
+        # a sum with premultiplied contributions: rank r scales by r + 1 (tests/nccl.cpp:122-133)
+        op = comm.premul_sum(float(rank + 1))
+        ones = torch.ones(16, device="cuda")
+        comm.all_reduce(ones.data_ptr(), ones.data_ptr(), 16, "float32", op, s)
+        stream.synchronize()
+        assert (ones.cpu().numpy() == nranks * (nranks + 1) / 2).all()
+        comm.destroy_op(op)
+        # point to point: a ring, then an exchange with every rank (itself included), each in one group (tests/nccl.cpp:178-200)
+        sbuf = torch.full((32,), rank, dtype=torch.int32, device="cuda")
+        rbuf = torch.full((32,), -1, dtype=torch.int32, device="cuda")
+        comm.group_start()
+        comm.send(sbuf.data_ptr(), 32, "int32", (rank + 1) % nranks, s)
+        comm.recv(rbuf.data_ptr(), 32, "int32", (rank + nranks - 1) % nranks, s)
+        comm.group_end()
+        stream.synchronize()
+        assert (rbuf.cpu().numpy() == (rank + nranks - 1) % nranks).all()
+        got = [torch.full((32,), -1, dtype=torch.int32, device="cuda") for _ in range(nranks)]
+        comm.group_start()
+        for q in range(nranks):
+            comm.send(sbuf.data_ptr(), 32, "int32", q, s)
+            comm.recv(got[q].data_ptr(), 32, "int32", q, s)
+        comm.group_end()
+        stream.synchronize()
+        for q in range(nranks):
+            assert (got[q].cpu().numpy() == q).all(), f"exchange with rank {q}"
+        # even and odd ranks part ways, keys descending so the order inside each half is reversed (tests/nccl.cpp:201-220)
+        half = comm.split(rank % 2, -rank)
+        members = [r for r in range(nranks) if r % 2 == rank % 2]
+        assert half.nranks == len(members) and half.rank == sum(1 for r in members if r > rank)
+        v = torch.full((4,), rank, dtype=torch.int32, device="cuda")
+        half.all_reduce(v.data_ptr(), v.data_ptr(), 4, "int32", capi.NCCL_SUM, s)
+        stream.synchronize()
+        assert (v.cpu().numpy() == sum(members)).all()
+        half.destroy()
+        assert comm.split(-1, 0) is None   # NCCL_SPLIT_NOCOLOR
     # a GEMM whose tiles are written to every rank's copy of D as they are produced (output mirrors): rank r computes
     # columns [r * w, (r + 1) * w) of D = A^T B, and afterwards every rank holds all of D
     from oracle import pyoracle as orc

@@ -49,10 +49,14 @@ def test_stub_surface_answers_not_supported():
     lib = vk.cublas_library()
     names = (ROOT / "vulkanizer_b200" / "csrc" / "blas_stub_names.def").read_text().split()
     assert len(names) >= 227
-    for name in names[:5] + ["cublasStrsm_v2", "cublasZgemm_v2"]:
+    for name in names[:5] + ["cublasStrsv_v2", "cublasZgemm_v2"]:
         fn = getattr(lib, name)
         fn.restype = C.c_int
         assert fn() == capi.STATUS_NOT_SUPPORTED
+    # the triangular solves and batched factorizations are served, not stubs: a null handle says so
+    assert "cublasStrsm_v2" not in names and "cublasSgetrfBatched" not in names
+    assert lib.cublasStrsm_v2(None, 0, 0, 0, 0, 1, 1, None, None, 1, None, 1) == capi.STATUS_NOT_INITIALIZED
+    assert lib.cublasSgeqrfBatched(None, 1, 1, None, 1, None, None, 1) == capi.STATUS_NOT_INITIALIZED
 
 
 def test_null_handle_and_status_strings():

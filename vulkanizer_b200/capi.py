@@ -20,6 +20,7 @@ INCLUDE_DIR = PKG_DIR.parent / "include"
 # ---- enum values (include/vkzb_cublas.h) ----
 CUDA_R_32F, CUDA_R_64F, CUDA_R_16F, CUDA_R_8I, CUDA_R_32I, CUDA_R_16BF = 0, 1, 2, 3, 10, 14
 OP_N, OP_T, OP_C = 0, 1, 2
+FILL_LOWER, FILL_UPPER, DIAG_NON_UNIT, DIAG_UNIT, SIDE_LEFT, SIDE_RIGHT = 0, 1, 0, 1, 0, 1
 POINTER_MODE_HOST, POINTER_MODE_DEVICE = 0, 1
 DEFAULT_MATH, TF32_TENSOR_OP_MATH = 0, 3
 COMPUTE_16F, COMPUTE_32F, COMPUTE_64F, COMPUTE_32I = 64, 68, 70, 72
@@ -102,6 +103,17 @@ def cublas_library() -> C.CDLL:
             "cublasGemmGroupedBatchedEx": [_vp] + [_vp] * 6 + [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i],
             "cublasSgemv_v2": [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _i],
             "cublasSgemv_v2_64": [_vp, _i, _ll, _ll, _vp, _vp, _ll, _vp, _ll, _vp, _vp, _ll],
+            # handle, side, uplo, trans, diag, m, n, alpha, A, lda, B, ldb (, batch)
+            "cublasStrsm_v2": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i],
+            "cublasDtrsm_v2": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i],
+            "cublasStrsmBatched": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _i],
+            "cublasDtrsmBatched": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _i],
+            "cublasSgetrfBatched": [_vp, _i, _vp, _i, _vp, _vp, _i],
+            "cublasDgetrfBatched": [_vp, _i, _vp, _i, _vp, _vp, _i],
+            "cublasSgetrsBatched": [_vp, _i, _i, _i, _vp, _i, _vp, _vp, _i, C.POINTER(_i), _i],
+            "cublasDgetrsBatched": [_vp, _i, _i, _i, _vp, _i, _vp, _vp, _i, C.POINTER(_i), _i],
+            "cublasSgeqrfBatched": [_vp, _i, _i, _vp, _i, _vp, C.POINTER(_i), _i],
+            "cublasDgeqrfBatched": [_vp, _i, _i, _vp, _i, _vp, C.POINTER(_i), _i],
         }
         for name, args in protos.items():
             fn = getattr(lib, name)
@@ -186,6 +198,12 @@ def nccl_library() -> C.CDLL:
             "ncclAlltoAll": coll + [_vp, _vp],
             "ncclGroupStart": [],
             "ncclGroupEnd": [],
+            "ncclSend": [_vp, _sz, _i, _i, _vp, _vp],
+            "ncclRecv": [_vp, _sz, _i, _i, _vp, _vp],
+            "ncclCommSplit": [_vp, _i, _i, C.POINTER(_vp), _vp],
+            "ncclRedOpCreatePreMulSum": [C.POINTER(_i), _vp, _i, _i, _vp],
+            "ncclRedOpDestroy": [_i, _vp],
+            "vkzbNcclSelfTestLostPeer": [_vp, _vp],
             "vkzbNcclExchangeBuffer": [_vp, _vp, C.POINTER(_vp)],
             "vkzbNcclBarrier": [_vp, _vp],
         }
@@ -206,8 +224,11 @@ class NcclComm:
     """One communicator of this repository's libnccl.so.2. The 128-byte unique id travels between the ranks by any means the
     caller has (the benchmark broadcasts it with torch.distributed, as an MPI program would with MPI_Bcast)."""
 
-    def __init__(self, nranks: int, rank: int, unique_id: bytes):
+    def __init__(self, nranks: int, rank: int, unique_id: bytes, _adopt=None):
         self.lib = nccl_library()
+        if _adopt is not None:  # a communicator made by ncclCommSplit
+            self.comm, self.nranks, self.rank = _adopt, nranks, rank
+            return
         uid = NcclUniqueId()
         C.memmove(C.addressof(uid), unique_id, 128)
         comm = _vp()
@@ -247,6 +268,44 @@ class NcclComm:
 
     def all_to_all(self, send, recv, count, dtype, stream=0):
         self._check("ncclAlltoAll", self.lib.ncclAlltoAll(send, recv, count, NCCL_TYPES[dtype], self.comm, stream), self.comm)
+
+    def send(self, buf, count, dtype, peer, stream=0):
+        self._check("ncclSend", self.lib.ncclSend(buf, count, NCCL_TYPES[dtype], peer, self.comm, stream), self.comm)
+
+    def recv(self, buf, count, dtype, peer, stream=0):
+        self._check("ncclRecv", self.lib.ncclRecv(buf, count, NCCL_TYPES[dtype], peer, self.comm, stream), self.comm)
+
+    def group_start(self):
+        self._check("ncclGroupStart", self.lib.ncclGroupStart(), None)
+
+    def group_end(self):
+        self._check("ncclGroupEnd", self.lib.ncclGroupEnd(), self.comm)
+
+    def split(self, color: int, key: int):
+        """The communicator of the ranks that passed `color` (None for NCCL_SPLIT_NOCOLOR = -1)."""
+        new = _vp()
+        self._check("ncclCommSplit", self.lib.ncclCommSplit(self.comm, color, key, C.byref(new), None), self.comm)
+        if not new.value:
+            return None
+        count, rank = _i(0), _i(0)
+        self.lib.ncclCommCount(new, C.byref(count))
+        self.lib.ncclCommUserRank(new, C.byref(rank))
+        return NcclComm(count.value, rank.value, b"", _adopt=new)
+
+    def premul_sum(self, factor: float) -> int:
+        """A reduction operator that multiplies this rank's contribution by `factor` (a host float) before the sum."""
+        op, value = _i(0), C.c_float(factor)
+        self._check("ncclRedOpCreatePreMulSum", self.lib.ncclRedOpCreatePreMulSum(C.byref(op), C.addressof(value), NCCL_TYPES["float32"], 1, self.comm), self.comm)
+        return op.value
+
+    def destroy_op(self, op: int):
+        self._check("ncclRedOpDestroy", self.lib.ncclRedOpDestroy(op, self.comm), self.comm)
+
+    def self_test_lost_peer(self, stream=0):
+        self._check("vkzbNcclSelfTestLostPeer", self.lib.vkzbNcclSelfTestLostPeer(self.comm, stream), self.comm)
+
+    def abort(self):
+        self.lib.ncclCommAbort(self.comm)
 
     def exchange_buffer(self, ptr: int) -> list[int]:
         """Addresses through which this process reaches each rank's buffer (extension vkzbNcclExchangeBuffer)."""

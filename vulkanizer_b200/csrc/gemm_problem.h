@@ -107,6 +107,19 @@ cudaError_t launchUmma(const Problem& p);     // tcgen05 tensor cores
 int ummaDeviceStatus();
 int gemvDeviceStatus();                      // 0, or 16 after a bulk copy of the matrix-vector kernel never arrived
 
+// Triangular solves and batched factorizations (k_solve.cu), T = float or double. Matrices are a pointer-array batch
+// (`arrays`), or single matrices with batch = 1.
+template <typename T>
+cudaError_t launchTrsm(bool right, bool upper, bool trans, bool unit, int m, int n, double alpha, const void* A, long long lda, const void* B,
+                       long long ldb, int batch, bool arrays, cudaStream_t stream);
+template <typename T>
+cudaError_t launchGetrf(int n, const void* A, long long lda, int* pivots, int* info, int batch, cudaStream_t stream);
+template <typename T>
+cudaError_t launchGetrs(bool trans, int n, int nrhs, const void* A, long long lda, const int* pivots, const void* B, long long ldb, int batch,
+                        cudaStream_t stream);
+template <typename T>
+cudaError_t launchGeqrf(int m, int n, const void* A, long long lda, const void* tau, int batch, cudaStream_t stream);
+
 void countLaunch(int n = 1);
 
 }  // namespace vkzb

@@ -46,8 +46,9 @@ namespace {
 
 constexpr int kMaxRanks = 16;
 constexpr uint32_t kMagic = 0x564B5A42u;
-constexpr int kPostRing = 4;
-constexpr unsigned long long kDeviceWaitNs = 20000000000ull;
+constexpr int kPostRing = 8;   // collective posts a rank may have outstanding before every peer has read the oldest
+constexpr int kP2pRing = 16;   // sends a rank may have posted to one peer before that peer has read the oldest
+constexpr int kMaxCustomOps = 16;
 
 struct IdPayload {
     uint32_t magic, reserved;
@@ -61,16 +62,31 @@ struct BufferPost {
 };
 struct OpPost {
     BufferPost send, recv;
+    double premul;  // factor this rank's contribution is multiplied by (premultiplied sums; 1 otherwise)
+    uint32_t bad;   // the rank could not describe its buffers: peers fail at once instead of waiting
+};
+struct P2pPost {
+    BufferPost buffer;
+    uint64_t bytes;
 };
 struct RankSlot {
     std::atomic<uint32_t> state;  // 0 empty, 1 published, 2 left
     int pid;
     char busId[32];
-    cudaIpcMemHandle_t arenaHandle;
+    BufferPost arenaPost;  // the flag arena: the allocation that holds it and its offset there
     uint64_t arenaRaw;
     std::atomic<uint64_t> postSeq;      // operations whose addresses are posted
+    std::atomic<uint64_t> readSeq;      // operations whose peer posts this rank has read (the posters' flow control)
     std::atomic<uint64_t> hostBarrier;  // host-side barriers passed (ranks sharing a GPU)
     OpPost posts[kPostRing];
+    // point to point, per destination rank: sends posted (addresses) and, for ranks that share a GPU, sends whose data is
+    // final; per source rank: posts read, and receives completed (the sender may reuse its buffer)
+    std::atomic<uint64_t> p2pPosted[kMaxRanks], p2pReady[kMaxRanks];
+    std::atomic<uint64_t> p2pRead[kMaxRanks], p2pDone[kMaxRanks];
+    P2pPost p2p[kMaxRanks][kP2pRing];
+    // ncclCommSplit: this rank's (color, key) of split number splitSeq, and how many splits it has finished reading
+    std::atomic<uint64_t> splitSeq, splitRead;
+    int splitColor, splitKey;
 };
 struct Shared {
     std::atomic<uint32_t> abort;
@@ -79,11 +95,13 @@ struct Shared {
 
 // Device memory of one rank that its peers map: flag words written by the peers, and a status word.
 struct Arena {
-    unsigned long long flags[kMaxRanks];
+    unsigned long long flags[kMaxRanks];     // barrier: written by peer p, sequence number of the barrier p has reached
+    unsigned long long p2pReady[kMaxRanks];  // written by sender p: its sends to this rank whose data is final
+    unsigned long long p2pDone[kMaxRanks];   // written by receiver p: sends of this rank to p that p has copied
     unsigned status;
 };
 
-enum OpKind { kAllGather, kBroadcast, kAllReduce, kReduceScatter, kReduce, kGather, kAllToAll, kBarrierOnly };
+enum OpKind { kAllGather, kBroadcast, kAllReduce, kReduceScatter, kReduce, kGather, kAllToAll, kBarrierOnly, kSend, kRecv };
 
 }  // namespace
 
@@ -93,9 +111,18 @@ struct ncclComm {
     std::string shmName;
     Arena* arena = nullptr;
     Arena* peerArena[kMaxRanks] = {};
+    cudaIpcMemHandle_t peerArenaHandle[kMaxRanks] = {};  // what was opened to reach peerArena[p] (other processes only)
     bool samePid[kMaxRanks] = {};
     bool hostSync = false;  // some ranks share a GPU
-    uint64_t opSeq = 0, deviceBarrierSeq = 0, hostBarrierSeq = 0;
+    uint64_t opSeq = 0, deviceBarrierSeq = 0, hostBarrierSeq = 0, splitCount = 0;
+    uint64_t sendSeq[kMaxRanks] = {}, recvSeq[kMaxRanks] = {};  // point-to-point messages sent to / received from each rank
+    uint64_t idToken[2] = {};                                   // of the unique id: children of ncclCommSplit derive theirs from it
+    struct CustomOp {
+        bool live = false;
+        double factor = 1.0;
+        const void* devicePointer = nullptr;  // ncclScalarDevice: read when the collective is issued
+        ncclDataType_t type = ncclFloat32;
+    } customOps[kMaxCustomOps];
     struct Mapping {
         cudaIpcMemHandle_t handle;
         void* local;
@@ -122,8 +149,22 @@ struct Op {
     uint64_t seq = 0;
     const char* peerSend[kMaxRanks] = {};
     char* peerRecv[kMaxRanks] = {};
+    double premul[kMaxRanks] = {};  // per rank, for premultiplied sums
+    bool scaled = false;
+    int peer = -1;                  // kSend / kRecv
+    uint64_t p2pSeq = 0;
 };
 thread_local std::vector<Op> t_queue;
+
+// How long a device-side wait may last before it gives up (VKZB_NCCL_DEVICE_WAIT_MS; default 20 s).
+unsigned long long deviceWaitNs() {
+    static const unsigned long long ns = [] {
+        const char* v = std::getenv("VKZB_NCCL_DEVICE_WAIT_MS");
+        const double ms = v ? std::atof(v) : 0;
+        return ms > 0 ? (unsigned long long)(ms * 1e6) : 20000000000ull;
+    }();
+    return ns;
+}
 
 double timeoutSeconds() {
     static const double s = [] {
@@ -164,13 +205,31 @@ ncclResult_t hostWait(ncclComm* c, F ready, const char* what) {
     }
 }
 
+// A scalar of an NCCL data type as a double (premultiplied sums).
+double scalarValue(const void* p, ncclDataType_t t) {
+    switch (t) {
+    case ncclInt8: return double(*static_cast<const signed char*>(p));
+    case ncclUint8: return double(*static_cast<const unsigned char*>(p));
+    case ncclInt32: return double(*static_cast<const int*>(p));
+    case ncclUint32: return double(*static_cast<const unsigned*>(p));
+    case ncclInt64: return double(*static_cast<const long long*>(p));
+    case ncclUint64: return double(*static_cast<const unsigned long long*>(p));
+    case ncclFloat16: return double(__half2float(*static_cast<const __half*>(p)));
+    case ncclBfloat16: return double(__bfloat162float(*static_cast<const __nv_bfloat16*>(p)));
+    case ncclFloat32: return double(*static_cast<const float*>(p));
+    case ncclFloat64: return *static_cast<const double*>(p);
+    default: return 1.0;
+    }
+}
+
 // ---- device side ----------------------------------------------------------------------------------------------------
 
 struct FlagTable {
     unsigned long long* peer[kMaxRanks];  // peer p's flag word for this rank
 };
 
-__global__ void barrierKernel(FlagTable peers, unsigned long long* mine, unsigned* status, int me, int n, unsigned long long seq) {
+__global__ void barrierKernel(FlagTable peers, unsigned long long* mine, unsigned* status, int me, int n, unsigned long long seq,
+                              unsigned long long waitNs) {
     const int p = threadIdx.x;
     if (p >= n || p == me) return;
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(peers.peer[p]), "l"(seq) : "memory");
@@ -182,8 +241,30 @@ __global__ void barrierKernel(FlagTable peers, unsigned long long* mine, unsigne
         if (v >= seq) return;
         unsigned long long now;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-        if (now - start > kDeviceWaitNs) {
+        if (now - start > waitNs) {
             atomicExch(status, 1u + unsigned(p));  // peer p never arrived
+            return;
+        }
+        __nanosleep(200);
+    }
+}
+
+// Point to point between ranks on different GPUs: one thread tells a peer "my message number seq is ready / is copied" ...
+__global__ void signalKernel(unsigned long long* flag, unsigned long long seq) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(flag), "l"(seq) : "memory");
+}
+// ... and one waits, bounded, for the peer's word to reach seq.
+__global__ void waitKernel(const unsigned long long* flag, unsigned long long seq, unsigned* status, unsigned code, unsigned long long waitNs) {
+    unsigned long long start;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+    for (;;) {
+        unsigned long long v;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+        if (v >= seq) return;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (now - start > waitNs) {
+            atomicExch(status, code);
             return;
         }
         __nanosleep(200);
@@ -192,6 +273,8 @@ __global__ void barrierKernel(FlagTable peers, unsigned long long* mine, unsigne
 
 struct SourceTable {
     const void* src[kMaxRanks];
+    double scale[kMaxRanks];  // premultiplied sums: contribution r is multiplied by scale[r] before it is added
+    int scaled;
 };
 
 template <typename T> struct AccOf { using type = double; };
@@ -215,8 +298,10 @@ __global__ void reduceKernel(T* out, SourceTable table, size_t n, int nranks, in
     using A = typename AccOf<T>::type;
     for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
         A acc = widen<A, T>(static_cast<const T*>(table.src[0])[i]);
+        if (table.scaled) acc = acc * A(table.scale[0]);
         for (int r = 1; r < nranks; ++r) {
-            const A v = widen<A, T>(static_cast<const T*>(table.src[r])[i]);
+            A v = widen<A, T>(static_cast<const T*>(table.src[r])[i]);
+            if (table.scaled) v = v * A(table.scale[r]);
             if (op == ncclProd) acc = acc * v;
             else if (op == ncclMax) acc = v > acc ? v : acc;
             else if (op == ncclMin) acc = v < acc ? v : acc;
@@ -274,6 +359,56 @@ bool describeBuffer(const void* ptr, BufferPost& out) {
     return cudaIpcGetMemHandle(&out.handle, reinterpret_cast<void*>(base)) == cudaSuccess;
 }
 
+// CUDA lets a process open the IPC handle of an allocation only once at a time, and several things of one peer can live in
+// the same allocation (cudaMalloc carves small requests out of larger blocks: the flag arenas of a communicator and of the
+// communicators split from it, say). So opened handles are shared process-wide and counted.
+struct IpcKey {
+    int device;
+    unsigned char bytes[sizeof(cudaIpcMemHandle_t)];
+    bool operator<(const IpcKey& o) const { return device != o.device ? device < o.device : std::memcmp(bytes, o.bytes, sizeof bytes) < 0; }
+};
+struct IpcOpened {
+    void* local;
+    int users;
+};
+std::mutex g_ipcMutex;
+std::map<IpcKey, IpcOpened> g_ipcOpened;
+
+IpcKey ipcKeyOf(const cudaIpcMemHandle_t& handle) {
+    IpcKey k{};
+    cudaGetDevice(&k.device);
+    std::memcpy(k.bytes, &handle, sizeof k.bytes);
+    return k;
+}
+
+void* ipcAcquire(const cudaIpcMemHandle_t& handle) {
+    const IpcKey key = ipcKeyOf(handle);
+    std::lock_guard<std::mutex> lock(g_ipcMutex);
+    auto it = g_ipcOpened.find(key);
+    if (it != g_ipcOpened.end()) {
+        ++it->second.users;
+        return it->second.local;
+    }
+    void* local = nullptr;
+    if (cudaIpcOpenMemHandle(&local, handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    g_ipcOpened.emplace(key, IpcOpened{local, 1});
+    return local;
+}
+
+void ipcRelease(const cudaIpcMemHandle_t& handle) {
+    const IpcKey key = ipcKeyOf(handle);
+    std::lock_guard<std::mutex> lock(g_ipcMutex);
+    auto it = g_ipcOpened.find(key);
+    if (it == g_ipcOpened.end()) return;
+    if (--it->second.users == 0) {
+        cudaIpcCloseMemHandle(it->second.local);
+        g_ipcOpened.erase(it);
+    }
+}
+
 // Local address of a peer's posted buffer: the raw pointer inside one process, an IPC mapping across processes.
 void* mapPeerBuffer(ncclComm* c, int peer, const BufferPost& post) {
     if (!post.base) return nullptr;
@@ -281,16 +416,13 @@ void* mapPeerBuffer(ncclComm* c, int peer, const BufferPost& post) {
     const auto key = std::make_pair(peer, post.base);
     auto it = c->mappings.find(key);
     if (it != c->mappings.end() && std::memcmp(&it->second.handle, &post.handle, sizeof post.handle) != 0) {
-        cudaIpcCloseMemHandle(it->second.local);  // the address was freed and allocated again: a different allocation
+        ipcRelease(it->second.handle);  // the address was freed and allocated again: a different allocation
         c->mappings.erase(it);
         it = c->mappings.end();
     }
     if (it == c->mappings.end()) {
-        void* local = nullptr;
-        if (cudaIpcOpenMemHandle(&local, post.handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
-            cudaGetLastError();
-            return nullptr;
-        }
+        void* local = ipcAcquire(post.handle);
+        if (!local) return nullptr;
         it = c->mappings.emplace(key, ncclComm::Mapping{post.handle, local}).first;
     }
     return static_cast<char*>(it->second.local) + post.offset;
@@ -305,7 +437,7 @@ ncclResult_t barrier(std::vector<Op*>& ops) {
         if (c->hostSync || c->nranks == 1) continue;
         FlagTable t{};
         for (int p = 0; p < c->nranks; ++p) t.peer[p] = p == c->rank ? nullptr : &c->peerArena[p]->flags[c->rank];
-        barrierKernel<<<1, 32, 0, o->stream>>>(t, c->arena->flags, &c->arena->status, c->rank, c->nranks, ++c->deviceBarrierSeq);
+        barrierKernel<<<1, 32, 0, o->stream>>>(t, c->arena->flags, &c->arena->status, c->rank, c->nranks, ++c->deviceBarrierSeq, deviceWaitNs());
         if (cudaGetLastError() != cudaSuccess) return fail(c, ncclUnhandledCudaError, "barrier kernel launch failed");
     }
     // host side where ranks share a GPU: drain the streams, publish, then wait for the peers
@@ -376,14 +508,17 @@ ncclResult_t runRound(Op& o, int round) {
         }
         break;
     case kBarrierOnly:
+    case kSend:
+    case kRecv:
         break;
     case kReduce:
     case kReduceScatter: {
         if (o.kind == kReduce && me != o.root) break;
         SourceTable t{};
         const size_t skip = o.kind == kReduceScatter ? size_t(me) * bytes : 0;  // rank r keeps block r of the reduction
-        for (int p = 0; p < n; ++p) t.src[p] = (local(p) ? static_cast<const char*>(o.send) : o.peerSend[p]) + skip;
-        e = launchReduce(o.recv, t, o.count, n, o.type, o.op, o.stream);
+        for (int p = 0; p < n; ++p) t.src[p] = (local(p) ? static_cast<const char*>(o.send) : o.peerSend[p]) + skip, t.scale[p] = o.premul[p];
+        t.scaled = o.scaled;
+        e = launchReduce(o.recv, t, o.count, n, o.type, o.scaled ? ncclSum : o.op, o.stream);
         break;
     }
     case kAllReduce: {
@@ -393,8 +528,9 @@ ncclResult_t runRound(Op& o, int round) {
             size_t first, len;
             sliceOf(o.count, n, me, first, len);
             SourceTable t{};
-            for (int p = 0; p < n; ++p) t.src[p] = (local(p) ? static_cast<const char*>(o.send) : o.peerSend[p]) + first * es;
-            e = launchReduce(static_cast<char*>(o.recv) + first * es, t, len, n, o.type, o.op, o.stream);
+            for (int p = 0; p < n; ++p) t.src[p] = (local(p) ? static_cast<const char*>(o.send) : o.peerSend[p]) + first * es, t.scale[p] = o.premul[p];
+            t.scaled = o.scaled;
+            e = launchReduce(static_cast<char*>(o.recv) + first * es, t, len, n, o.type, o.scaled ? ncclSum : o.op, o.stream);
         } else {
             for (int i = 0; i + 1 < n && e == cudaSuccess; ++i) {
                 const int p = (me + 1 + i) % n;
@@ -409,22 +545,154 @@ ncclResult_t runRound(Op& o, int round) {
     return e == cudaSuccess ? ncclSuccess : fail(c, ncclUnhandledCudaError, std::string("data movement failed: ") + cudaGetErrorString(e));
 }
 
-ncclResult_t execute(std::vector<Op>& ops) {
+// ---- point to point ---------------------------------------------------------------------------------------------------------
+//
+// A send posts its buffer's address for the receiver (a ring per ordered pair, matched by sequence number like the
+// reference's, nccl.cpp:340-347) and tells it when the data is final; the receiver pulls the bytes and tells the sender when
+// it has them, which is when the send completes on its stream. Between GPUs the two notices are flag words in the peers'
+// arenas, written and awaited by one-thread kernels on the operations' streams; ranks that share a GPU use counters in the
+// shared-memory object and synchronise their streams. Within a group every "data is final" notice goes out before anything
+// waits, so a ring of sends and receives, or an exchange with every peer, cannot wait on itself.
+ncclResult_t runPointToPoint(std::vector<Op*>& ops) {
+    std::vector<Op*> sends, recvs;
+    for (Op* o : ops) (o->kind == kSend ? sends : recvs).push_back(o);
+    // 1. post the send buffers' addresses
+    std::vector<std::pair<const void*, size_t>> toSelf;  // sends of a rank to itself, matched to its receives in order
+    size_t selfTaken = 0;
+    for (Op* o : sends) {
+        ncclComm* c = o->comm;
+        cudaSetDevice(c->device);
+        if (o->peer == c->rank) {
+            toSelf.emplace_back(o->send, o->count * typeSize(o->type));
+            continue;
+        }
+        RankSlot& slot = c->shared->ranks[c->rank];
+        o->p2pSeq = ++c->sendSeq[o->peer];
+        if (o->p2pSeq > kP2pRing) {  // the slot about to be reused must have been read by the receiver
+            const uint64_t need = o->p2pSeq - kP2pRing;
+            const ncclResult_t r = hostWait(c, [&] { return c->shared->ranks[o->peer].p2pRead[c->rank].load(std::memory_order_acquire) >= need; },
+                                            "a peer to take earlier point-to-point messages");
+            if (r != ncclSuccess) return r;
+        }
+        P2pPost& post = slot.p2p[o->peer][o->p2pSeq % kP2pRing];
+        post.bytes = o->count * typeSize(o->type);
+        if (!describeBuffer(o->send, post.buffer)) post.bytes = ~0ull;  // the receiver fails at once instead of waiting
+        slot.p2pPosted[o->peer].store(o->p2pSeq, std::memory_order_release);
+        if (post.bytes == ~0ull) return fail(c, ncclInvalidArgument, "the send buffer is not device memory that can be shared with the other ranks");
+    }
+    // 2. "my data is final": a flag store on the stream, or (shared GPU) a host counter once the stream has drained
+    for (Op* o : sends) {
+        ncclComm* c = o->comm;
+        if (o->peer == c->rank) continue;
+        cudaSetDevice(c->device);
+        if (c->hostSync) {
+            if (cudaStreamSynchronize(o->stream) != cudaSuccess) return fail(c, ncclUnhandledCudaError, "stream synchronize failed");
+            c->shared->ranks[c->rank].p2pReady[o->peer].store(o->p2pSeq, std::memory_order_release);
+        } else {
+            signalKernel<<<1, 1, 0, o->stream>>>(&c->peerArena[o->peer]->p2pReady[c->rank], o->p2pSeq);
+            if (cudaGetLastError() != cudaSuccess) return fail(c, ncclUnhandledCudaError, "signal kernel launch failed");
+        }
+    }
+    // 3. receives: find the matching post, wait for the data, pull it, say so
+    for (Op* o : recvs) {
+        ncclComm* c = o->comm;
+        cudaSetDevice(c->device);
+        const size_t bytes = o->count * typeSize(o->type);
+        if (o->peer == c->rank) {
+            if (selfTaken >= toSelf.size()) return fail(c, ncclInvalidUsage, "a receive from this rank itself needs a send to itself in the same group");
+            const auto& from = toSelf[selfTaken++];
+            if (from.second != bytes) return fail(c, ncclInvalidArgument, "send and receive sizes differ");
+            if (copyAsync(o->recv, from.first, bytes, o->stream) != cudaSuccess) return fail(c, ncclUnhandledCudaError, "copy failed");
+            continue;
+        }
+        o->p2pSeq = ++c->recvSeq[o->peer];
+        RankSlot& theirs = c->shared->ranks[o->peer];
+        ncclResult_t r = hostWait(c, [&] { return theirs.p2pPosted[c->rank].load(std::memory_order_acquire) >= o->p2pSeq; }, "the matching send to be posted");
+        if (r != ncclSuccess) return r;
+        const P2pPost post = theirs.p2p[c->rank][o->p2pSeq % kP2pRing];
+        c->shared->ranks[c->rank].p2pRead[o->peer].store(o->p2pSeq, std::memory_order_release);
+        if (post.bytes == ~0ull) return fail(c, ncclRemoteError, "the sender could not share its buffer");
+        if (post.bytes != bytes) return fail(c, ncclInvalidArgument, "send and receive sizes differ");
+        const void* src = mapPeerBuffer(c, o->peer, post.buffer);
+        if (!src && bytes) return fail(c, ncclUnhandledCudaError, "could not map the sender's buffer (cudaIpcOpenMemHandle)");
+        if (c->hostSync) {
+            r = hostWait(c, [&] { return theirs.p2pReady[c->rank].load(std::memory_order_acquire) >= o->p2pSeq; }, "the sender's data");
+            if (r != ncclSuccess) return r;
+            if (copyAsync(o->recv, src, bytes, o->stream) != cudaSuccess || cudaStreamSynchronize(o->stream) != cudaSuccess)
+                return fail(c, ncclUnhandledCudaError, "copy failed");
+            c->shared->ranks[c->rank].p2pDone[o->peer].store(o->p2pSeq, std::memory_order_release);
+        } else {
+            waitKernel<<<1, 1, 0, o->stream>>>(&c->arena->p2pReady[o->peer], o->p2pSeq, &c->arena->status, 101u + unsigned(o->peer), deviceWaitNs());
+            if (cudaGetLastError() != cudaSuccess || copyAsync(o->recv, src, bytes, o->stream) != cudaSuccess)
+                return fail(c, ncclUnhandledCudaError, "receive failed");
+            signalKernel<<<1, 1, 0, o->stream>>>(&c->peerArena[o->peer]->p2pDone[c->rank], o->p2pSeq);
+            if (cudaGetLastError() != cudaSuccess) return fail(c, ncclUnhandledCudaError, "signal kernel launch failed");
+        }
+    }
+    if (selfTaken != toSelf.size()) return fail(sends.front()->comm, ncclInvalidUsage, "a send to this rank itself needs a receive from itself in the same group");
+    // 4. a send is complete when the receiver has the data
+    for (Op* o : sends) {
+        ncclComm* c = o->comm;
+        if (o->peer == c->rank) continue;
+        cudaSetDevice(c->device);
+        if (c->hostSync) {
+            const ncclResult_t r = hostWait(c, [&] { return c->shared->ranks[o->peer].p2pDone[c->rank].load(std::memory_order_acquire) >= o->p2pSeq; },
+                                            "the receiver to take a message");
+            if (r != ncclSuccess) return r;
+        } else {
+            waitKernel<<<1, 1, 0, o->stream>>>(&c->arena->p2pDone[o->peer], o->p2pSeq, &c->arena->status, 201u + unsigned(o->peer), deviceWaitNs());
+            if (cudaGetLastError() != cudaSuccess) return fail(c, ncclUnhandledCudaError, "wait kernel launch failed");
+        }
+    }
+    return ncclSuccess;
+}
+
+// ---- collectives ------------------------------------------------------------------------------------------------------------
+
+// One batch: at most kPostRing operations per communicator, so no operation of the batch can overwrite the posted addresses
+// of another one that a peer has yet to read.
+ncclResult_t executeCollectives(std::vector<Op*>& ops) {
     // 1. every operation posts its buffers' addresses
-    for (Op& o : ops) {
+    for (Op* op : ops) {
+        Op& o = *op;
         ncclComm* c = o.comm;
-        if (c->aborted.load()) return fail(c, ncclInvalidUsage, "communicator was aborted");
         cudaSetDevice(c->device);
         o.seq = ++c->opSeq;
+        for (int p = 0; p < c->nranks; ++p) o.premul[p] = 1.0;
+        double myFactor = 1.0;
+        if (int(o.op) >= int(ncclNumOps)) {  // a premultiplied sum created by ncclRedOpCreatePreMulSum
+            const ncclComm::CustomOp& custom = c->customOps[int(o.op) - int(ncclNumOps)];
+            myFactor = custom.factor;
+            if (custom.devicePointer) {  // a scalar in device memory is read when the collective is issued, after the stream's earlier work
+                unsigned char raw[8] = {};
+                if (cudaStreamSynchronize(o.stream) != cudaSuccess || cudaMemcpy(raw, custom.devicePointer, typeSize(custom.type), cudaMemcpyDeviceToHost) != cudaSuccess)
+                    return fail(c, ncclUnhandledCudaError, "could not read the scalar of a premultiplied sum");
+                myFactor = scalarValue(raw, custom.type);
+            }
+            o.scaled = true;
+            o.premul[c->rank] = myFactor;
+        }
         if (c->nranks == 1) continue;
         RankSlot& slot = c->shared->ranks[c->rank];
+        if (o.seq > kPostRing) {  // flow control: the slot about to be rewritten was read by every peer
+            const uint64_t need = o.seq - kPostRing;
+            const ncclResult_t r = hostWait(c, [&] {
+                for (int p = 0; p < c->nranks; ++p)
+                    if (p != c->rank && c->shared->ranks[p].readSeq.load(std::memory_order_acquire) < need) return false;
+                return true;
+            }, "the other ranks to finish reading an earlier collective's addresses");
+            if (r != ncclSuccess) return r;
+        }
         OpPost& post = slot.posts[o.seq % kPostRing];
-        if (!describeBuffer(o.send, post.send) || !describeBuffer(o.recv, post.recv))
-            return fail(c, ncclInvalidArgument, "a buffer is not device memory that can be shared with the other ranks (cudaMalloc memory is)");
-        slot.postSeq.store(o.seq, std::memory_order_release);
+        post.premul = myFactor;
+        post.bad = !describeBuffer(o.send, post.send) || !describeBuffer(o.recv, post.recv);
+        const bool bad = post.bad != 0;
+        slot.postSeq.store(o.seq, std::memory_order_release);  // published even when bad, so that the peers do not wait for it
+        if (bad) return fail(c, ncclInvalidArgument, "a buffer is not device memory that can be shared with the other ranks (cudaMalloc memory is)");
     }
     // 2. ... and maps what the peers posted
-    for (Op& o : ops) {
+    for (Op* op : ops) {
+        Op& o = *op;
         ncclComm* c = o.comm;
         if (c->nranks == 1) continue;
         cudaSetDevice(c->device);
@@ -434,27 +702,33 @@ ncclResult_t execute(std::vector<Op>& ops) {
             return true;
         }, "the other ranks to enter the collective");
         if (r != ncclSuccess) return r;
-        for (int p = 0; p < c->nranks; ++p) {
+        ncclResult_t result = ncclSuccess;
+        for (int p = 0; p < c->nranks && result == ncclSuccess; ++p) {
             if (p == c->rank) continue;
-            const OpPost& post = c->shared->ranks[p].posts[o.seq % kPostRing];
+            const OpPost post = c->shared->ranks[p].posts[o.seq % kPostRing];
+            if (post.bad) {
+                result = fail(c, ncclRemoteError, "another rank could not share its buffers");
+                break;
+            }
+            o.premul[p] = post.premul;
             o.peerSend[p] = static_cast<const char*>(mapPeerBuffer(c, p, post.send));
             o.peerRecv[p] = static_cast<char*>(mapPeerBuffer(c, p, post.recv));
             const bool needSend = !(o.kind == kBroadcast && p != o.root) && !((o.kind == kGather || o.kind == kReduce) && c->rank != o.root);
             if ((needSend && post.send.base && !o.peerSend[p]) || (o.kind == kAllReduce && !o.peerRecv[p]))
-                return fail(c, ncclUnhandledCudaError, "could not map a peer's buffer (cudaIpcOpenMemHandle)");
+                result = fail(c, ncclUnhandledCudaError, "could not map a peer's buffer (cudaIpcOpenMemHandle)");
         }
+        c->shared->ranks[c->rank].readSeq.store(o.seq, std::memory_order_release);  // read (even if unusable): the slots may be reused
+        if (result != ncclSuccess) return result;
     }
     // 3. barrier, pulls, (barrier, pulls,) barrier
-    std::vector<Op*> all, second;
-    for (Op& o : ops) {
-        all.push_back(&o);
-        if (needsSecondRound(o)) second.push_back(&o);
-    }
-    ncclResult_t r = barrier(all);
-    for (Op& o : ops) {
+    std::vector<Op*> second;
+    for (Op* o : ops)
+        if (needsSecondRound(*o)) second.push_back(o);
+    ncclResult_t r = barrier(ops);
+    for (Op* o : ops) {
         if (r != ncclSuccess) return r;
-        cudaSetDevice(o.comm->device);
-        r = runRound(o, 0);
+        cudaSetDevice(o->comm->device);
+        r = runRound(*o, 0);
     }
     if (r == ncclSuccess && !second.empty()) {
         r = barrier(second);
@@ -466,21 +740,54 @@ ncclResult_t execute(std::vector<Op>& ops) {
     }
     if (r == ncclSuccess) {
         std::vector<Op*> closing;
-        for (Op& o : ops)
-            if (o.kind != kBarrierOnly) closing.push_back(&o);
+        for (Op* o : ops)
+            if (o->kind != kBarrierOnly) closing.push_back(o);
         r = barrier(closing);
     }
     return r;
 }
 
+// Everything one ncclGroupEnd (or one ungrouped call) starts: the collectives in batches that respect the posting ring, the
+// sends and receives together.
+ncclResult_t execute(std::vector<Op>& ops) {
+    std::vector<Op*> p2p, batch;
+    std::map<ncclComm*, int> inBatch;
+    const auto flush = [&]() {
+        const ncclResult_t r = batch.empty() ? ncclSuccess : executeCollectives(batch);
+        batch.clear();
+        inBatch.clear();
+        return r;
+    };
+    for (Op& o : ops) {
+        if (o.comm->aborted.load()) return fail(o.comm, ncclInvalidUsage, "communicator was aborted");
+        if (o.kind == kSend || o.kind == kRecv) {
+            p2p.push_back(&o);
+            continue;
+        }
+        if (inBatch[o.comm] == kPostRing)
+            if (const ncclResult_t r = flush(); r != ncclSuccess) return r;
+        batch.push_back(&o);
+        ++inBatch[o.comm];
+    }
+    if (const ncclResult_t r = flush(); r != ncclSuccess) return r;
+    return p2p.empty() ? ncclSuccess : runPointToPoint(p2p);
+}
+
 ncclResult_t submit(Op op) {
     if (!op.comm) return ncclInvalidArgument;
-    if (op.kind != kBarrierOnly && (typeSize(op.type) == 0 || (!op.recv && op.count && !(op.kind == kReduce || op.kind == kGather))))
+    const bool reduces = op.kind == kAllReduce || op.kind == kReduce || op.kind == kReduceScatter;
+    if (op.kind != kBarrierOnly && (typeSize(op.type) == 0 || (!op.recv && op.count && !(op.kind == kReduce || op.kind == kGather || op.kind == kSend))))
         return fail(op.comm, ncclInvalidArgument, "bad datatype or null buffer");
     if ((op.kind == kBroadcast || op.kind == kReduce || op.kind == kGather) && (op.root < 0 || op.root >= op.comm->nranks))
         return fail(op.comm, ncclInvalidArgument, "root out of range");
-    if (unsigned(op.op) >= unsigned(ncclNumOps) && (op.kind == kAllReduce || op.kind == kReduce || op.kind == kReduceScatter))
-        return fail(op.comm, ncclInvalidUsage, "custom reduction operators are not served");
+    if ((op.kind == kSend || op.kind == kRecv) && (op.peer < 0 || op.peer >= op.comm->nranks))
+        return fail(op.comm, ncclInvalidArgument, "peer out of range");
+    if (reduces && int(op.op) >= int(ncclNumOps)) {
+        const int index = int(op.op) - int(ncclNumOps);
+        if (index >= kMaxCustomOps || !op.comm->customOps[index].live) return fail(op.comm, ncclInvalidArgument, "unknown reduction operator");
+    } else if (reduces && int(op.op) < 0) {
+        return fail(op.comm, ncclInvalidArgument, "unknown reduction operator");
+    }
     if (t_groupDepth > 0) {
         t_queue.push_back(op);
         return ncclSuccess;
@@ -499,6 +806,28 @@ std::string shmNameOf(const IdPayload& id) {
     return name;
 }
 
+// Gives back what a communicator holds on this side (mappings, arena, the shared-memory view). `announce`: tell the peers
+// that this rank has left (and remove the shared-memory object's name once every rank has).
+void release(ncclComm* c, bool announce) {
+    for (auto& m : c->mappings) ipcRelease(m.second.handle);
+    c->mappings.clear();
+    for (int p = 0; p < c->nranks; ++p)
+        if (p != c->rank && c->peerArena[p] && !c->samePid[p]) ipcRelease(c->peerArenaHandle[p]), c->peerArena[p] = nullptr;
+    if (c->shared) {
+        if (announce) {
+            c->shared->ranks[c->rank].state.store(2, std::memory_order_release);
+            bool last = true;
+            for (int p = 0; p < c->nranks; ++p)
+                if (c->shared->ranks[p].state.load() != 2) last = false;
+            if (last) shm_unlink(c->shmName.c_str());
+        }
+        munmap(c->shared, sizeof(Shared));
+        c->shared = nullptr;
+    }
+    if (c->arena) cudaFree(c->arena);
+    c->arena = nullptr;
+}
+
 ncclResult_t initRank(ncclComm_t* out, int nranks, const ncclUniqueId& uid, int rank) {
     if (!out || nranks < 1 || rank < 0 || rank >= nranks) return ncclInvalidArgument;
     if (nranks > kMaxRanks) return ncclInvalidArgument;
@@ -508,33 +837,36 @@ ncclResult_t initRank(ncclComm_t* out, int nranks, const ncclUniqueId& uid, int 
     if (cudaFree(nullptr) != cudaSuccess) return ncclUnhandledCudaError;
     auto* c = new ncclComm;
     c->rank = rank, c->nranks = nranks;
+    c->idToken[0] = id.token[0], c->idToken[1] = id.token[1];
     cudaGetDevice(&c->device);
     c->shmName = shmNameOf(id);
+    // Any failure from here on gives back what was taken; once this rank's slot is published it is also marked as left, so
+    // that the peers' waits end with an error at once instead of running into their timeout.
+    const auto giveUp = [&](ncclResult_t r, const char* what, bool published) {
+        if (what) fail(nullptr, r, what);
+        if (published && c->shared) c->shared->abort.store(1);
+        release(c, published);
+        delete c;
+        return r;
+    };
     const int fd = shm_open(c->shmName.c_str(), O_CREAT | O_RDWR, 0600);
     if (fd < 0 || ftruncate(fd, sizeof(Shared)) != 0) {
         if (fd >= 0) close(fd);
-        delete c;
-        return ncclSystemError;
+        return giveUp(ncclSystemError, "shm_open failed", false);
     }
     void* mem = mmap(nullptr, sizeof(Shared), PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);  // a new object reads as zeros
     close(fd);
-    if (mem == MAP_FAILED) {
-        delete c;
-        return ncclSystemError;
-    }
+    if (mem == MAP_FAILED) return giveUp(ncclSystemError, "mmap failed", false);
     c->shared = static_cast<Shared*>(mem);
-    if (cudaMalloc(reinterpret_cast<void**>(&c->arena), sizeof(Arena)) != cudaSuccess || cudaMemset(c->arena, 0, sizeof(Arena)) != cudaSuccess) {
-        munmap(mem, sizeof(Shared));
-        delete c;
-        return ncclUnhandledCudaError;
-    }
+    if (cudaMalloc(reinterpret_cast<void**>(&c->arena), sizeof(Arena)) != cudaSuccess || cudaMemset(c->arena, 0, sizeof(Arena)) != cudaSuccess)
+        return giveUp(ncclUnhandledCudaError, "could not allocate the flag arena", false);
     RankSlot& slot = c->shared->ranks[rank];
     slot.pid = int(getpid());
     cudaDeviceGetPCIBusId(slot.busId, sizeof slot.busId, c->device);
     slot.arenaRaw = reinterpret_cast<uint64_t>(c->arena);
-    if (nranks > 1 && cudaIpcGetMemHandle(&slot.arenaHandle, c->arena) != cudaSuccess) {
+    if (nranks > 1 && !describeBuffer(c->arena, slot.arenaPost)) {
         cudaGetLastError();
-        return fail(c, ncclUnhandledCudaError, "cudaIpcGetMemHandle failed for the flag arena");
+        return giveUp(ncclUnhandledCudaError, "cudaIpcGetMemHandle failed for the flag arena", false);
     }
     slot.state.store(1, std::memory_order_release);
     const ncclResult_t r = hostWait(c, [&] {
@@ -542,7 +874,7 @@ ncclResult_t initRank(ncclComm_t* out, int nranks, const ncclUniqueId& uid, int 
             if (c->shared->ranks[p].state.load(std::memory_order_acquire) == 0) return false;
         return true;
     }, "every rank to join the communicator");
-    if (r != ncclSuccess) return r;
+    if (r != ncclSuccess) return giveUp(r, nullptr, true);
     for (int p = 0; p < nranks; ++p) {
         const RankSlot& s = c->shared->ranks[p];
         c->samePid[p] = s.pid == slot.pid;
@@ -554,9 +886,11 @@ ncclResult_t initRank(ncclComm_t* out, int nranks, const ncclUniqueId& uid, int 
             int peerDev = -1;
             cudaDeviceGetByPCIBusId(&peerDev, s.busId);
             if (peerDev >= 0 && peerDev != c->device && cudaDeviceEnablePeerAccess(peerDev, 0) != cudaSuccess) cudaGetLastError();
-        } else if (cudaIpcOpenMemHandle(reinterpret_cast<void**>(&c->peerArena[p]), s.arenaHandle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
-            cudaGetLastError();
-            return fail(c, ncclUnhandledCudaError, "cudaIpcOpenMemHandle failed for a peer's flag arena (no peer access between the GPUs?)");
+        } else {
+            void* base = ipcAcquire(s.arenaPost.handle);
+            if (!base) return giveUp(ncclUnhandledCudaError, "cudaIpcOpenMemHandle failed for a peer's flag arena (no peer access between the GPUs?)", true);
+            c->peerArenaHandle[p] = s.arenaPost.handle;
+            c->peerArena[p] = reinterpret_cast<Arena*>(static_cast<char*>(base) + s.arenaPost.offset);
         }
     }
     *out = c;
@@ -568,18 +902,7 @@ void destroy(ncclComm* c) {
     cudaGetDevice(&prev);
     cudaSetDevice(c->device);
     cudaDeviceSynchronize();
-    for (auto& m : c->mappings) cudaIpcCloseMemHandle(m.second.local);
-    for (int p = 0; p < c->nranks; ++p)
-        if (p != c->rank && c->peerArena[p] && !c->samePid[p]) cudaIpcCloseMemHandle(c->peerArena[p]);
-    if (c->shared) {
-        c->shared->ranks[c->rank].state.store(2, std::memory_order_release);
-        bool last = true;
-        for (int p = 0; p < c->nranks; ++p)
-            if (c->shared->ranks[p].state.load() != 2) last = false;
-        if (last) shm_unlink(c->shmName.c_str());
-        munmap(c->shared, sizeof(Shared));
-    }
-    if (c->arena) cudaFree(c->arena);
+    release(c, true);
     cudaSetDevice(prev);
     delete c;
 }
@@ -729,6 +1052,109 @@ ncclResult_t ncclAlltoAll(const void* sendbuff, void* recvbuff, size_t count, nc
     return submit({comm, kAllToAll, sendbuff, recvbuff, count, datatype, ncclSum, 0, stream});
 }
 
+// Point to point (nccl.cpp:706-715): the n-th send from a rank to a peer matches that peer's n-th receive from the rank.
+ncclResult_t ncclSend(const void* sendbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream) {
+    Op op{comm, kSend, sendbuff, nullptr, count, datatype, ncclSum, 0, stream};
+    op.peer = peer;
+    return submit(op);
+}
+ncclResult_t ncclRecv(void* recvbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream) {
+    Op op{comm, kRecv, nullptr, recvbuff, count, datatype, ncclSum, 0, stream};
+    op.peer = peer;
+    return submit(op);
+}
+
+// A sum whose contributions are multiplied by a per-rank scalar first (nccl.cpp:650-666). A scalar in host memory is read
+// now; one in device memory is read each time a collective with this operator is issued.
+ncclResult_t ncclRedOpCreatePreMulSum(ncclRedOp_t* op, void* scalar, ncclDataType_t datatype, ncclScalarResidence_t residence, ncclComm_t comm) {
+    if (!op || !scalar || !comm || typeSize(datatype) == 0 || datatype == ncclFloat8e4m3 || datatype == ncclFloat8e5m2) return ncclInvalidArgument;
+    for (int i = 0; i < kMaxCustomOps; ++i) {
+        ncclComm::CustomOp& slot = comm->customOps[i];
+        if (slot.live) continue;
+        slot.live = true, slot.type = datatype;
+        if (residence == ncclScalarHostImmediate) slot.factor = scalarValue(scalar, datatype), slot.devicePointer = nullptr;
+        else slot.factor = 1.0, slot.devicePointer = scalar;
+        *op = ncclRedOp_t(int(ncclNumOps) + i);
+        return ncclSuccess;
+    }
+    return fail(comm, ncclInvalidUsage, "too many reduction operators alive on this communicator");
+}
+
+ncclResult_t ncclRedOpDestroy(ncclRedOp_t op, ncclComm_t comm) {
+    const int index = int(op) - int(ncclNumOps);
+    if (!comm || index < 0 || index >= kMaxCustomOps || !comm->customOps[index].live) return ncclInvalidArgument;
+    comm->customOps[index].live = false;
+    return ncclSuccess;
+}
+
+// Ranks that pass the same color form a new communicator, ordered by (key, rank here); NCCL_SPLIT_NOCOLOR leaves a rank
+// without one (nccl.cpp:561-591). Collective over `comm` and blocking on the host: the (color, key) pairs travel through the
+// shared-memory object, and the members of a color derive their new communicator's id from this communicator's.
+ncclResult_t ncclCommSplit(ncclComm_t comm, int color, int key, ncclComm_t* newcomm, ncclConfig_t*) {
+    if (!comm || !newcomm) return ncclInvalidArgument;
+    *newcomm = nullptr;
+    const uint64_t seq = ++comm->splitCount;
+    RankSlot& mine = comm->shared->ranks[comm->rank];
+    // nobody may still be reading the previous split's pairs
+    ncclResult_t r = hostWait(comm, [&] {
+        for (int p = 0; p < comm->nranks; ++p)
+            if (comm->shared->ranks[p].splitRead.load(std::memory_order_acquire) < seq - 1) return false;
+        return true;
+    }, "the other ranks to finish the previous split");
+    if (r != ncclSuccess) return r;
+    mine.splitColor = color, mine.splitKey = key;
+    mine.splitSeq.store(seq, std::memory_order_release);
+    r = hostWait(comm, [&] {
+        for (int p = 0; p < comm->nranks; ++p)
+            if (comm->shared->ranks[p].splitSeq.load(std::memory_order_acquire) < seq) return false;
+        return true;
+    }, "the other ranks to enter ncclCommSplit");
+    if (r != ncclSuccess) return r;
+    int members = 0, myRank = 0;
+    for (int p = 0; p < comm->nranks; ++p) {
+        const RankSlot& s = comm->shared->ranks[p];
+        if (s.splitColor != color) continue;
+        ++members;
+        if (s.splitKey < key || (s.splitKey == key && p < comm->rank)) ++myRank;
+    }
+    mine.splitRead.store(seq, std::memory_order_release);
+    if (color == NCCL_SPLIT_NOCOLOR) return ncclSuccess;
+    if (color < 0) return fail(comm, ncclInvalidArgument, "a color is not negative");
+    ncclUniqueId id;
+    std::memset(&id, 0, sizeof id);
+    // the same words on every member, different for every (parent, split number, color)
+    IdPayload payload{kMagic, 0, {comm->idToken[0] * 0x9E3779B97F4A7C15ull + seq * 0xBF58476D1CE4E5B9ull + uint64_t(color) + 1,
+                                  comm->idToken[1] ^ (seq << 32) ^ (uint64_t(color) * 0x94D049BB133111EBull)}};
+    std::memcpy(id.internal, &payload, sizeof payload);
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(comm->device);
+    r = initRank(newcomm, members, id, myRank);
+    cudaSetDevice(prev);
+    return r;
+}
+
+// Diagnostic: runs this communicator's device-side barrier against a peer that does not exist (a flag word nobody writes),
+// so the bounded wait runs out: the kernel returns after the device wait limit (VKZB_NCCL_DEVICE_WAIT_MS) and
+// ncclCommGetAsyncError reports ncclRemoteError. Nothing faults and the context stays usable; lets an installation check
+// that a lost peer is noticed. The communicator should be destroyed afterwards (its status word stays set).
+ncclResult_t vkzbNcclSelfTestLostPeer(ncclComm_t comm, cudaStream_t stream) {
+    if (!comm) return ncclInvalidArgument;
+    if (comm->nranks > kMaxRanks - 2) return ncclInvalidUsage;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(comm->device);
+    // As "rank 0 of 2" on the two highest flag words of this rank's own arena, which no real peer uses below 15 ranks: the
+    // kernel stores its arrival into the first and waits for the second, which nobody ever writes.
+    FlagTable t{};
+    unsigned long long* spare = &comm->arena->flags[kMaxRanks - 2];
+    t.peer[1] = spare;
+    barrierKernel<<<1, 32, 0, stream>>>(t, spare, &comm->arena->status, 0, 2, 1ull, deviceWaitNs());
+    const cudaError_t e = cudaGetLastError();
+    cudaSetDevice(prev);
+    return e == cudaSuccess ? ncclSuccess : ncclUnhandledCudaError;
+}
+
 ncclResult_t ncclGroupStart(void) {
     ++t_groupDepth;
     return ncclSuccess;
@@ -792,12 +1218,7 @@ ncclResult_t vkzbNcclBarrier(ncclComm_t comm, cudaStream_t stream) {
 // Not served yet (include/vkzb_nccl.h lists them): parameterless like the reference's stubs, so any signature binds.
 #define VKZB_NCCL_STUB(name) \
     ncclResult_t name() { return ncclInvalidUsage; }
-VKZB_NCCL_STUB(ncclSend)
-VKZB_NCCL_STUB(ncclRecv)
-VKZB_NCCL_STUB(ncclCommSplit)
 VKZB_NCCL_STUB(ncclCommInitRankScalable)
-VKZB_NCCL_STUB(ncclRedOpCreatePreMulSum)
-VKZB_NCCL_STUB(ncclRedOpDestroy)
 VKZB_NCCL_STUB(ncclGroupSimulateEnd)
 VKZB_NCCL_STUB(ncclCommGetUniqueId)
 VKZB_NCCL_STUB(ncclCommGrow)
