@@ -230,6 +230,34 @@ def host_operand(torch, spec, count: int, first: int):
     return host
 
 
+def yardstick(torch, kind: str) -> float:
+    """The rate NVIDIA's own library reaches on this box for a dense product of `kind`, measured now with CUDA events: the
+    denominator for the kernels MEASURED_PEAKS.json has no figure for. 's8': int8 -> int32 8192^3 (TOP/s); 'f32': fp32 4096^3."""
+    size, reps = (8192, 10) if kind == "s8" else (4096, 5)
+    if kind == "s8":
+        a = torch.randint(-127, 128, (size, size), dtype=torch.int8, device="cuda")
+        b = torch.randint(-127, 128, (size, size), dtype=torch.int8, device="cuda").t()
+        run = lambda: torch._int_mm(a, b)
+    else:
+        torch.backends.cuda.matmul.allow_tf32 = False
+        a = torch.randn(size, size, device="cuda")
+        b = torch.randn(size, size, device="cuda")
+        run = lambda: torch.matmul(a, b)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    best = float("inf")
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(reps):
+        start.record()
+        run()
+        stop.record()
+        torch.cuda.synchronize()
+        best = min(best, start.elapsed_time(stop))
+    del a, b
+    return 2.0 * size ** 3 / (best * 1e-3) / 1e12
+
+
 def run_single_gpu(args):
     import torch
     from vulkanizer_b200 import capi
@@ -335,6 +363,31 @@ def run_single_gpu(args):
     value_tf = flops * steps_done / (total_ms * 1e-3) / 1e12
     assert blas.device_status() == 0, "a bounded wait in the tcgen05 kernel gave up"
 
+    # tensor-bound products of seconds' worth: the same call back to back for two seconds, against the sustained cuBLAS
+    # figure (the timed region above is a burst of a few milliseconds at the full clock)
+    sustained = None
+    if spec["bound"] == "tensor" and not use_graph and ab != "s8":
+        sampler2 = ClockSampler(physical_gpu_index(0))
+        with torch.cuda.stream(stream):
+            stream.synchronize()
+            t_s0 = time.time()
+            done_calls = 0
+            start.record(stream)
+            while time.time() - t_s0 < 2.0:
+                for _ in range(10):
+                    step()
+                done_calls += 10
+                stream.synchronize()
+            stop.record(stream)
+            stream.synchronize()
+        t_s1 = time.time()
+        clocks2 = sampler2.stop(t_s0, t_s1)
+        sus_tf = flops * done_calls / (start.elapsed_time(stop) * 1e-3) / 1e12
+        sus_peak = float(measured_peaks()[0].get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+        sustained = {"achieved": sus_tf, "peak": sus_peak, "frac": sus_tf / sus_peak, "unit": "TFLOP/s", "seconds": round(t_s1 - t_s0, 2), "calls": done_calls,
+                     "sm_mhz": clocks2.get("sm_mhz"), "reasons": clocks2.get("reasons"),
+                     "peak_source": "measured: cuBLAS bf16 8192^3 back to back for seconds (bf16_tflops_sustained)"}
+
     # End to end through the same C-ABI calls from pinned host buffers: copy A and B in, multiply, copy C out, every
     # step. A product with enough columns (or batch entries) goes in blocks: block j of B travels to the device while block
     # j - 1 is multiplied and block j - 2 of C travels back, on three streams, so both directions of the host link stay busy.
@@ -394,13 +447,18 @@ def run_single_gpu(args):
         peak = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
         achieved, unit, source = algorithmic_bytes / (kernel_ms * 1e-3) / 1e9, "GB/s", f"{peak_kind}: device copy bandwidth"
     elif bound == "ffma":
-        # no measured fp32 peak on record: nominal 148 SMs x 128 FMA x 2 x 1.965 GHz
-        peak, bound = 148 * 128 * 2 * 1.965e9 / 1e12, "tensor"
-        achieved, unit, source = flops / (kernel_ms * 1e-3) / 1e12, "TFLOP/s", "nominal fp32 FFMA rate at the maximum SM clock (CUDA cores, not tensor cores)"
-    else:
-        peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])) * (2.0 if ab == "s8" else 1.0)
+        # the fp32 yardstick is measured here: cuBLAS SGEMM (TF32 off) on 4096^3, the FFMA rate NVIDIA's own kernel reaches on this box
+        peak, bound = yardstick(torch, "f32"), "tensor"
+        achieved, unit, source = flops / (kernel_ms * 1e-3) / 1e12, "TFLOP/s", "measured here: cuBLAS fp32 4096^3 (TF32 off) through torch.matmul, best of 5 (CUDA cores, not tensor cores)"
+    elif ab == "s8":
+        # the int8 yardstick is measured here: no int8 figure is on record in MEASURED_PEAKS.json
+        peak = yardstick(torch, "s8")
         achieved, unit = flops / (kernel_ms * 1e-3) / 1e12, "TFLOP/s"
-        source = f"{peak_kind}: cuBLAS bf16 8192^3 burst" + (" x 2 (int8 issues at twice the bf16 rate; no int8 measurement on record)" if ab == "s8" else "")
+        source = "measured here: cuBLAS int8 8192^3 through torch._int_mm, best of 10, CUDA events"
+    else:
+        peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+        achieved, unit = flops / (kernel_ms * 1e-3) / 1e12, "TFLOP/s"
+        source = f"{peak_kind}: cuBLAS bf16 8192^3 burst"
     traffic = None
     traffic_file = ROOT / "profiles" / "traffic.json"
     if traffic_file.exists():
@@ -424,6 +482,7 @@ def run_single_gpu(args):
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "traffic": traffic,
                      "peak_source": source, "kernel": path_names.get(path, str(path)), "kernel_ms": kernel_ms,
                      "algorithmic_bytes": algorithmic_bytes, "algorithmic_flop": flops},
+        "roofline_sustained": sustained,
         "e2e": {"value": e2e_tf, "unit": "TFLOP/s", "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out,
                 "how": (f"{blocks} column blocks: copy in, cublasGemmEx and copy out overlap on three streams" if blocks > 1 else
                         "copy in, one call, copy out, on one stream")},
@@ -447,8 +506,8 @@ def main():
         return run_reference_arm(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1 or args.gpus > 1 or args.workload == "cfg5b_bf16_32768_nsharded":
-        from vulkanizer_b200 import multi_gpu_bench
-        return multi_gpu_bench.run(args)
+        import bench_multi_gpu
+        return bench_multi_gpu.run(args)
     return run_single_gpu(args)
 
 

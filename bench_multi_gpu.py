@@ -1,4 +1,5 @@
-"""Multi-GPU arm of bench.py: the N-sharded large GEMM with its column blocks gathered over NVLink.
+"""Multi-GPU arm of bench.py (benchmark code, not part of the library): the N-sharded large GEMM with its column blocks
+gathered over NVLink, and the batch-sharded attention-score product.
 
 Workload cfg5b_bf16_32768_nsharded: D = A^T B with A, B 32768 x 32768 bf16 (normal(0, 1), seed 5), D 32768 x 32768 fp32,
 alpha = 1, beta = 0, through cublasLtMatmul. The columns of B and D are dealt to the ranks block-cyclically: column chunk
@@ -9,11 +10,18 @@ multiplied; A (2 GiB) is replicated, every rank ends with the whole of D. This i
 `partOf(g, rows=false, first, count)` (src/cublas/cublas.cpp:542-546) applied across GPUs, with the exchange step its
 libnccl surface provides (src/nccl/nccl.cpp:691-695). Strong scaling: the total work is fixed.
 
-Two ways of getting every rank's columns everywhere are built. Default ("fused"): each rank multiplies its whole column
-block in one cublasLtMatmul call whose epilogue stores every finished tile not only to its own D but, through peer-mapped
+Two ways of getting every rank's columns everywhere are built. "Fused" (2 and 4 GPUs): each rank multiplies its column
+block with cublasLtMatmul calls whose epilogue stores every finished tile not only to its own D but, through peer-mapped
 addresses (vkzbNcclExchangeBuffer + vkzbSetOutputMirrors), to the other ranks' D as well, so the NVLink traffic is spread
 over the whole product and nothing is left to gather; barriers of libnccl.so.2 order the ranks around the step.
-VKZB_BENCH_GATHER=nccl: the block-cyclic, chunk-pipelined products + ncclAllGather described above.
+"Pipelined" (8 GPUs, where NVLink is busy for most of the step): the block-cyclic, chunk-pipelined products + ncclAllGather
+described above.
+
+Operands are the seeded synthetic ones of vulkanizer_b200/synth.py (seed 5; element i of A^T's storage is value i of the
+stream, element i of B's value m * k + i), made on the GPU by the torch form of that generator. After the timed region every
+rank checks a sample of D (rows across the matrix, columns from EVERY rank's block) against the fp64 oracle on operands
+regenerated on the host with the numpy form; the bench line carries the result as `parity_checked`. Every line for more than
+one GPU also carries `scaling_baseline`: the time of the same whole product on rank 0 alone, measured in the same run.
 
 torch.distributed (gloo) is only the plumbing: it carries the 128-byte communicator id, the barrier around the timed region and
 the maximum over the ranks' device times. All GPU work goes through this repository's libcublasLt.so.12 and libnccl.so.2.
@@ -22,14 +30,12 @@ from __future__ import annotations
 
 import json
 import os
-import statistics
 import time
+
+import numpy as np
 
 
 def round_widths(n: int, ranks: int):
-    forced = os.environ.get("VKZB_BENCH_WIDTHS")  # e.g. "1024,1024,1024,512,256,256": an experiment knob
-    if forced:
-        return [int(w) for w in forced.split(",")]
     return default_round_widths(n, ranks)
 
 
@@ -197,23 +203,23 @@ def run(args):
     torch.cuda.set_device(local)
     torch.zeros(1, device="cuda")
 
-    size = int(os.environ.get("VKZB_BENCH_SIZE", "32768"))
+    from vulkanizer_b200 import synth
+
+    size = 32768
     m = n = k = size
-    # fused (default): one product per rank whose tiles go straight to every rank's D; nccl: chunked products + ncclAllGather
-    # Which of the two is the default depends on how much of the step NVLink needs: every rank receives (G - 1) / G of D,
+    # fused: products whose tiles go straight to every rank's D; pipelined: chunked products + ncclAllGather.
+    # Which of the two runs depends on how much of the step NVLink needs: every rank receives (G - 1) / G of D,
     # 4 m n (G - 1) / G bytes at about 770 GB/s, against 2 m n k / G flop at about 1.45 PFLOP/s. Mirrored bulk stores reach
     # about 640 GB/s and push back into the epilogue when the link is busy most of the step (8 GPUs: 4.9 ms of traffic in a
     # 6.0 ms product, measured 9.1 ms fused against 8.3 ms chunk-pipelined), while the copy engines behind ncclAllGather
     # reach 700 GB/s; below that (2 and 4 GPUs) the fused form wins because nothing is left over at the end of the step.
     link_share = (4.0 * m * n * (world - 1) / world / 770e9) / (2.0 * m * n * k / world / 1.45e15) if world > 1 else 0.0
-    choice = os.environ.get("VKZB_BENCH_GATHER", "auto")
-    fused = world > 1 and (choice == "fused" or (choice == "auto" and link_share < 0.6))
-    # (fused: still 2048 columns per call. One call over a rank's whole share ran a quarter slower at 2 GPUs: over tens of
+    fused = world > 1 and link_share < 0.6
+    # (fused: 2048 columns per call. One call over a rank's whole share ran a quarter slower at 2 GPUs: over tens of
     # milliseconds the CTAs of one persistent kernel drift apart along k and stop finding each other's operand slices in L2.)
-    fused_width = int(os.environ.get("VKZB_BENCH_FUSED_WIDTH", "2048"))
     rounds = column_chunks(n, world, None)
     if fused:
-        per_rank, w = n // world, min(fused_width, n // world)
+        per_rank, w = n // world, min(2048, n // world)
         rounds = [(j, w, None, [r * per_rank + j * w for r in range(world)]) for j in range(per_rank // w)]
     mine_cols = sum(w for _, w, _, _ in rounds)  # columns this rank computes
 
@@ -222,22 +228,22 @@ def run(args):
     dist.broadcast_object_list(box, src=0)
     comm = capi.NcclComm(world, rank, box[0])
 
-    # operands: A identical on every rank; of B only the rank's own chunks, chunk c generated from seed (5, c)
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(5)
-    A = torch.empty(m * k, dtype=torch.bfloat16, device="cuda")  # stored k x m (op T), lda = k
-    step_elems = 1 << 26
-    for first in range(0, m * k, step_elems):
-        cnt = min(step_elems, m * k - first)
-        A[first:first + cnt] = torch.randn(cnt, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    # Operands, seed 5: A^T's storage (k x m, lda = k) holds values 0 .. m k - 1 of the stream, column j of B values
+    # m k + j k .. of it. A is identical on every rank: each makes its share and the shares are gathered through this
+    # repository's libnccl; of B a rank makes only the columns it multiplies.
+    A = torch.empty(m * k, dtype=torch.bfloat16, device="cuda")
+    a_first, a_count = shard(m, world, rank)
+    assert m % world == 0
+    synth.fill_normal_torch(torch, A[a_first * k:(a_first + a_count) * k], 5, 1.0, first=a_first * k)
+    if world > 1:
+        comm.all_gather(A.data_ptr() + 2 * a_first * k, A.data_ptr(), a_count * k, "bfloat16", 0)
+        torch.cuda.synchronize()
     Bmine = torch.empty(mine_cols * k, dtype=torch.bfloat16, device="cuda")  # the rank's chunks, one after another
     b_offset = []  # element offset of round j's chunk inside Bmine
     off = 0
     for j, w, _, firsts in rounds:
         b_offset.append(off)
-        for c0 in range(0, w, 256):  # every 256-column block of B has its own seed, whatever the chunking
-            gen.manual_seed(5 * 100003 + (firsts[rank] + c0) // 256)
-            Bmine[off + c0 * k:off + (c0 + 256) * k] = torch.randn(256 * k, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        synth.fill_normal_torch(torch, Bmine[off:off + w * k], 5, 1.0, first=m * k + firsts[rank] * k)
         off += w * k
     D = torch.zeros(m * n, dtype=torch.float32, device="cuda")  # column-major m x n, ldd = m: 4 GiB at full size
 
@@ -245,8 +251,6 @@ def run(args):
     compute, gather = torch.cuda.Stream(), torch.cuda.Stream()
     bf16, f32 = capi.CUDA_R_16BF, capi.CUDA_R_32F
     events = [torch.cuda.Event() for _ in rounds]
-
-    no_gemm, no_gather = bool(os.environ.get("VKZB_BENCH_NO_GEMM")), bool(os.environ.get("VKZB_BENCH_NO_GATHER"))  # experiment knobs
 
     if fused:
         peers = comm.exchange_buffer(D.data_ptr())
@@ -257,10 +261,9 @@ def run(args):
             comm.barrier(compute.cuda_stream)  # nobody still reads the D this step overwrites
         for j, w, round_first, firsts in rounds:
             mine = D.data_ptr() + 4 * firsts[rank] * m
-            if not no_gemm:
-                lt.matmul(capi.OP_T, capi.OP_N, m, w, k, 1.0, A.data_ptr(), bf16, k, Bmine.data_ptr() + 2 * b_offset[j], bf16, k, 0.0,
-                          mine, f32, m, mine, f32, m, stream=compute.cuda_stream)
-            if world > 1 and not no_gather and not fused:
+            lt.matmul(capi.OP_T, capi.OP_N, m, w, k, 1.0, A.data_ptr(), bf16, k, Bmine.data_ptr() + 2 * b_offset[j], bf16, k, 0.0,
+                      mine, f32, m, mine, f32, m, stream=compute.cuda_stream)
+            if world > 1 and not fused:
                 events[j].record(compute)
                 gather.wait_event(events[j])
                 comm.all_gather(mine, D.data_ptr() + 4 * round_first * m, w * m, "float32", gather.cuda_stream)
@@ -272,7 +275,7 @@ def run(args):
     for _ in range(max(3, args.warmup)):
         step()
     torch.cuda.synchronize()
-    assert no_gemm or lt.last_path() == capi.PATH_UMMA
+    assert lt.last_path() == capi.PATH_UMMA
     launches0 = lt.launch_count()
     sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
     dist.barrier()
@@ -293,20 +296,49 @@ def run(args):
     launches = lt.launch_count() - launches0
     assert comm.async_error() == 0, "a device-side barrier of the gather gave up"
 
-    # a spot check that the gather delivered every rank's columns: column sums of a few remote chunks against a local product
-    check_ok = True
-    if world > 1 and not (no_gemm or no_gather):
-        other = (rank + 1) % world
-        j, w, _, firsts = rounds[-1]
-        gen.manual_seed(5 * 100003 + firsts[other] // 256)
-        Bother = torch.randn(256 * k, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16).view(256, k)
-        rows = torch.arange(0, m, 997, device="cuda")
-        want = (A.view(m, k)[rows].float() @ Bother[:8].float().T)  # (rows, 8 columns)
-        got = D.view(n, m)[firsts[other]:firsts[other] + 8][:, rows].T
-        check_ok = bool(torch.allclose(got, want, rtol=2e-2, atol=2e-2 * (k ** 0.5)))
-    ok = torch.tensor([1 if check_ok else 0])
-    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    assert int(ok.item()) == 1, "gathered columns do not match a local product"
+    # Parity, outside the timed region: a sample of D on EVERY rank (each holds all of D after the step) against the fp64
+    # oracle, with operands regenerated on the host by the numpy form of the generator: rows spread over the matrix, and
+    # from every rank's column block its first and its last column.
+    from oracle import pyoracle as orc
+    rows = sorted(set(range(rank * 131 % 997, m, 997)) | {m - 1})
+    cols = sorted({c for _, w, _, firsts in (rounds[0], rounds[-1]) for q in range(world) for c in (firsts[q], firsts[q] + w - 1)})
+    a_rows = np.concatenate([orc.to_storage(synth.normal(5, k, 1.0, first=i * k), "bf16") for i in rows])   # row i of op(A): k values
+    b_cols = np.concatenate([orc.to_storage(synth.normal(5, k, 1.0, first=m * k + j * k), "bf16") for j in cols])
+    want = orc.dots_fp64(True, False, k, a_rows, "bf16", k, b_cols, "bf16", k, list(range(len(rows))), list(range(len(cols))))
+    got = D.view(n, m)[torch.tensor(cols, device="cuda")][:, torch.tensor(rows, device="cuda")].T.cpu().numpy().astype(np.float64)
+    rel = float(np.max(np.abs(got - want) / np.maximum(1.0, np.abs(want))))
+    worst = torch.tensor([rel], dtype=torch.float64)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    parity = {"rows": len(rows), "cols": len(cols), "ranks_checked": world, "max_rel": float(worst.item()), "tolerance": 1e-2,
+              "oracle": "oracle.pyoracle.dots_fp64 on operands regenerated by vulkanizer_b200.synth (numpy)"}
+    assert parity["max_rel"] <= parity["tolerance"], f"the gathered result differs from the oracle: {parity}"
+
+    # The same whole product on rank 0 alone, in the same run, as the denominator of the scaling efficiency: 32768 columns in
+    # calls of 2048, B made 2048 columns at a time into a buffer that the timed calls then reuse (its content is irrelevant
+    # to the time; A and D are the ones above).
+    baseline_ms = None
+    if world > 1:
+        if rank == 0:
+            Bblock = torch.empty(2048 * k, dtype=torch.bfloat16, device="cuda")
+            synth.fill_normal_torch(torch, Bblock, 5, 1.0, first=m * k)
+            lt.set_output_mirrors(0, 0, [])
+
+            def alone():
+                for c in range(0, n, 2048):
+                    lt.matmul(capi.OP_T, capi.OP_N, m, 2048, k, 1.0, A.data_ptr(), bf16, k, Bblock.data_ptr(), bf16, k, 0.0, D.data_ptr() + 4 * c * m, f32, m,
+                              D.data_ptr() + 4 * c * m, f32, m, stream=compute.cuda_stream)
+
+            alone()
+            torch.cuda.synchronize()
+            start.record(compute)
+            for _ in range(3):
+                alone()
+            stop.record(compute)
+            torch.cuda.synchronize()
+            baseline_ms = start.elapsed_time(stop) / 3
+            if fused:
+                lt.set_output_mirrors(D.data_ptr(), D.numel() * 4, [peers[p] for p in range(world) if p != rank])
+        dist.barrier()
 
     # end to end: the rank's inputs come from pinned host memory, its own columns of D go back
     hostA = torch.empty(m * k, dtype=torch.bfloat16).pin_memory()
@@ -356,8 +388,11 @@ def run(args):
                          "nvlink_floor_ms": gathered_bytes / 770e9 * 1e3},
             "e2e": {"value": flops * e2e_steps / (float(e2e_ms.item()) * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": (hostA.numel() + hostB.numel()) * 2 * world, "d2h_bytes_per_step": hostD.numel() * 4 * world},
-            "gpu_launches": launches * world, "clocks": clocks,
+            "gpu_launches": launches * world, "clocks": clocks, "parity_checked": parity,
         }
+        if baseline_ms:
+            line["scaling_baseline"] = {"workload": "the same 32768^3 product on rank 0 alone, 3 steps, this run", "ms_per_step_1gpu": baseline_ms,
+                                        "efficiency": baseline_ms / (world * total_ms / args.steps)}
         print(json.dumps(line), flush=True)
     if fused:
         lt.set_output_mirrors(0, 0, [])

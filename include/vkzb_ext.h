@@ -34,6 +34,12 @@ uint64_t vkzbLaunchCount(void);
 /* VKZB_PATH_* of the most recent GEMM call made on this thread. */
 int vkzbLastPath(void);
 /*
+ * How the most recent tensor-core (VKZB_PATH_UMMA) launch made on this thread was laid out: bits 0-9 the tile's column count
+ * (64, 128 or 256), bit 10 two-CTA pairs (tiles of 256 rows), bit 11 the wide-epilogue variant, bits 12-15 the number of
+ * splits along k (1: none).
+ */
+int vkzbLastPlan(void);
+/*
  * Device-side status word of the tcgen05 and matrix-vector kernels for the current device: 0 while every bounded
  * wait (mbarrier phase, TMEM allocation) completed; otherwise a code naming the wait that gave up (1-4: tcgen05
  * kernel roles, 16: a bulk copy of the matrix-vector kernel). Reads

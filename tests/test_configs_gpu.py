@@ -3,8 +3,8 @@
 Full fp64 references for 8192^3 would take the CPU minutes to hours, so, like k0zi/Vulkanizer's own large test
 (tests/cublas.cpp:550-585: every 7th row and column plus the last), results are compared with fp64 dot products on a sample of
 rows and columns, and the whole result is tied down with size-independent properties: a checksum identity
-(sum over rows of D equals (sum over rows of op(A)) * op(B)) and linearity in alpha. Tolerances are the north star's:
-1e-5 relative for fp32 FFMA, 1e-2 for f16 / bf16 (against fp64), exact for int8.
+(sum over rows of D equals (sum over rows of op(A)) * op(B)) and linearity in alpha. Tolerances are those stated for the
+configurations: 1e-5 relative for fp32 FFMA, 1e-2 for f16 / bf16 (against fp64), exact for int8.
 """
 import math
 
@@ -173,4 +173,43 @@ def test_config5b_lt_matmul_bf16_column_block(cuda):
     got = Dm[first:first + width][torch.tensor(cols, device="cuda")][:, torch.tensor(rows, device="cuda")].T.cpu().numpy()
     assert (np.abs(got - want) / np.maximum(1.0, np.abs(want))).max() <= 1e-2
     assert bool((Dm[:first] == 7.0).all()) and bool((Dm[first + width:] == 7.0).all()), "columns outside the block must stay untouched"
+    lt.destroy()
+
+
+@pytest.mark.gpu
+def test_config5b_full_height_column_block(cuda):
+    """The sharded product at its real height and depth: M = K = 32768 (A is 2 GiB of bf16) and one 256-column block of the
+    32768-column result, operands from the seeded generator's torch form, checked against the fp64 oracle on rows spread over
+    the whole height with the operands regenerated on the host by the numpy form (seed 5: value i of the stream for element i of
+    A^T's storage, value m k + i for element i of B)."""
+    torch = cuda
+    free, _ = torch.cuda.mem_get_info()
+    if free < (8 << 30):
+        pytest.skip("needs 8 GiB of free device memory")
+    m = k = 32768
+    width, first_col = 256, 20480   # a block from the middle of the result
+    A = torch.empty(m * k, dtype=torch.bfloat16, device="cuda")
+    synth.fill_normal_torch(torch, A, 5, 1.0, first=0)
+    B = torch.empty(width * k, dtype=torch.bfloat16, device="cuda")
+    synth.fill_normal_torch(torch, B, 5, 1.0, first=m * k + first_col * k)
+    D = torch.zeros(width * m, dtype=torch.float32, device="cuda")
+    lt = capi.CublasLt()
+    lt.matmul(T, N, m, width, k, 1.0, A.data_ptr(), capi.CUDA_R_16BF, k, B.data_ptr(), capi.CUDA_R_16BF, k, 0.0, D.data_ptr(), capi.CUDA_R_32F, m, D.data_ptr(),
+              capi.CUDA_R_32F, m)
+    torch.cuda.synchronize()
+    assert lt.last_path() == capi.PATH_UMMA
+    rows, cols = sample_indices(m, 1021), [0, 100, 255]
+    a_rows = np.concatenate([orc.to_storage(synth.normal(5, k, 1.0, first=i * k), "bf16") for i in rows])
+    b_cols = np.concatenate([orc.to_storage(synth.normal(5, k, 1.0, first=m * k + (first_col + j) * k), "bf16") for j in cols])
+    # what the device holds for those rows and columns is what the host form of the generator gives
+    assert np.array_equal(A.view(torch.int16).view(m, k)[torch.tensor(rows, device="cuda")].cpu().numpy().view(np.uint16).ravel(), a_rows)
+    want = orc.dots_fp64(True, False, k, a_rows, "bf16", k, b_cols, "bf16", k, list(range(len(rows))), list(range(len(cols))))
+    got = D.view(width, m)[torch.tensor(cols, device="cuda")][:, torch.tensor(rows, device="cuda")].T.cpu().numpy()
+    assert (np.abs(got - want) / np.maximum(1.0, np.abs(want))).max() <= 1e-2
+    # and the whole block through the checksum identity: 1^T D = (A 1)^T B, columns of D summed over all 32768 rows
+    asum = torch.zeros(k, dtype=torch.float64, device="cuda")      # sum over rows of op(A): length k, 2048 rows at a time
+    for i in range(0, m, 2048):
+        asum += A.view(m, k)[i:i + 2048].double().sum(dim=0)
+    ref = B.view(width, k).double() @ asum
+    assert torch.allclose(D.view(width, m).double().sum(dim=1), ref, rtol=0, atol=1e-3 * float(ref.abs().max()) + 1.0)
     lt.destroy()

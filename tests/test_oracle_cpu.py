@@ -141,3 +141,20 @@ def test_synthetic_generators_are_deterministic_and_shaped():
     i8 = synth.int8_uniform(2, 100000)
     assert i8.min() == -127 and i8.max() == 127 and i8.dtype == np.int8
     assert not np.array_equal(synth.normal(1, 100), synth.normal(2, 100))
+
+
+def test_synthetic_generator_has_the_same_values_on_a_torch_device():
+    """The benchmark makes its largest operands with the torch form of vulkanizer_b200/synth.py (on the GPU); the checks
+    regenerate samples with the numpy form. Both must give the same numbers: identical as bf16 / f16 storage, and as float32
+    except where the math libraries' last fp64 bit flips a float32 rounding (far rarer than 1 in 10^5)."""
+    import torch
+    from vulkanizer_b200 import synth
+    count, first = 1 << 18, (1 << 31) * 3 + 12345   # an offset beyond 32 bits, as the 32768 x 32768 operands have
+    want = synth.normal(5, count, 0.02, first=first)
+    got = synth.normal_torch(torch, 5, count, 0.02, first=first, device="cpu").numpy()
+    assert (want == got).mean() > 0.99999
+    assert np.array_equal(orc.to_storage(want, "bf16"), orc.to_storage(got, "bf16"))
+    assert np.array_equal(orc.to_storage(want, "f16"), orc.to_storage(got, "f16"))
+    out = torch.empty(1000, dtype=torch.bfloat16)
+    synth.fill_normal_torch(torch, out, 5, 1.0, first=77, block=256)
+    assert np.array_equal(out.view(torch.int16).numpy().view(np.uint16), orc.to_storage(synth.normal(5, 1000, 1.0, first=77), "bf16"))

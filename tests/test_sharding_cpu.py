@@ -7,7 +7,7 @@ from pathlib import Path
 
 import pytest
 
-from vulkanizer_b200.multi_gpu_bench import column_chunks, round_widths, shard
+from bench_multi_gpu import column_chunks, round_widths, shard
 
 ROOT = Path(__file__).resolve().parents[1]
 
@@ -55,7 +55,7 @@ WORKER = r'''
 import os, sys, hashlib
 sys.path.insert(0, sys.argv[1])
 import torch.distributed as dist
-from vulkanizer_b200.multi_gpu_bench import column_chunks, round_widths, shard
+from bench_multi_gpu import column_chunks, round_widths, shard
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 dist.init_process_group("gloo", rank=rank, world_size=world)
 box = [bytes(range(128)) if rank == 0 else None]          # stands in for ncclGetUniqueId on rank 0

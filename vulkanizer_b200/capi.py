@@ -14,7 +14,8 @@ import subprocess
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
-LIB_DIR = PKG_DIR / "lib"
+# VKZB_LIB_DIR: load the libraries from another build directory (e.g. lib_measure, made by `make MEASURE=1`)
+LIB_DIR = Path(os.environ["VKZB_LIB_DIR"]).resolve() if os.environ.get("VKZB_LIB_DIR") else PKG_DIR / "lib"
 INCLUDE_DIR = PKG_DIR.parent / "include"
 
 # ---- enum values (include/vkzb_cublas.h) ----
@@ -123,6 +124,7 @@ def cublas_library() -> C.CDLL:
         lib.cublasGetCudartVersion.argtypes, lib.cublasGetCudartVersion.restype = [], _sz
         lib.vkzbLaunchCount.argtypes, lib.vkzbLaunchCount.restype = [], C.c_uint64
         lib.vkzbLastPath.argtypes, lib.vkzbLastPath.restype = [], _i
+        lib.vkzbLastPlan.argtypes, lib.vkzbLastPlan.restype = [], _i
         lib.vkzbDeviceStatus.argtypes, lib.vkzbDeviceStatus.restype = [], _i
         lib.vkzbSetOutputMirrors.argtypes, lib.vkzbSetOutputMirrors.restype = [_vp, _vp, _sz, _i, C.POINTER(_vp)], _i
         lib.vkzbSgemmStaticScratch.argtypes = [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _i]
@@ -421,6 +423,11 @@ class Cublas:
 
     def last_path(self) -> int:
         return self.lib.vkzbLastPath()
+
+    def last_plan(self) -> dict:
+        """Layout of this thread's most recent tensor-core launch (extension vkzbLastPlan)."""
+        bits = self.lib.vkzbLastPlan()
+        return {"bn": bits & 1023, "pair": bool(bits >> 10 & 1), "wide": bool(bits >> 11 & 1), "splits": bits >> 12 & 15}
 
     def launch_count(self) -> int:
         return self.lib.vkzbLaunchCount()

@@ -29,6 +29,9 @@ namespace vkzb {
 
 static std::atomic<uint64_t> g_launches{0};
 static thread_local int t_lastPath = VKZB_PATH_NONE;
+static thread_local int t_lastPlan = 0;
+
+void setLastPlan(int packed) { t_lastPlan = packed; }
 
 void countLaunch(int n) { g_launches.fetch_add(uint64_t(n), std::memory_order_relaxed); }
 
@@ -679,6 +682,7 @@ cublasStatus_t cublasSgemv_v2_64(cublasHandle_t h, cublasOperation_t trans, int6
 // ---- extensions (include/vkzb_ext.h) ----
 uint64_t vkzbLaunchCount(void) { return g_launches.load(std::memory_order_relaxed); }
 int vkzbLastPath(void) { return t_lastPath; }
+int vkzbLastPlan(void) { return t_lastPlan; }
 int vkzbDeviceStatus(void) {
     const int umma = ummaDeviceStatus();
     return umma ? umma : gemvDeviceStatus();

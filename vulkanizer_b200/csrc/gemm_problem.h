@@ -121,5 +121,6 @@ template <typename T>
 cudaError_t launchGeqrf(int m, int n, const void* A, long long lda, const void* tau, int batch, cudaStream_t stream);
 
 void countLaunch(int n = 1);
+void setLastPlan(int packed);  // what vkzbLastPlan() reports for this thread's most recent tensor-core launch
 
 }  // namespace vkzb

@@ -77,6 +77,27 @@ __device__ __forceinline__ float dot8(const uint4& a, const uint4& b, float acc)
     return acc;
 }
 
+// The same with the mixed-precision FMA of sm_100 (two 16-bit factors, fp32 addend and result, one rounding): the products
+// and sums are bit for bit those of dot8, without the conversion instructions, which otherwise outnumber the FMAs two to one.
+template <bool BF16>
+__device__ __forceinline__ float dot8Mixed(const uint4& a, const uint4& b, float acc) {
+    const unsigned aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if constexpr (BF16)
+            asm("{\n\t.reg .b16 al, ah, bl, bh;\n\tmov.b32 {al, ah}, %1;\n\tmov.b32 {bl, bh}, %2;\n\t"
+                "fma.rn.f32.bf16 %0, al, bl, %0;\n\tfma.rn.f32.bf16 %0, ah, bh, %0;\n\t}"
+                : "+f"(acc)
+                : "r"(aw[i]), "r"(bw[i]));
+        else
+            asm("{\n\t.reg .b16 al, ah, bl, bh;\n\tmov.b32 {al, ah}, %1;\n\tmov.b32 {bl, bh}, %2;\n\t"
+                "fma.rn.f32.f16 %0, al, bl, %0;\n\tfma.rn.f32.f16 %0, ah, bh, %0;\n\t}"
+                : "+f"(acc)
+                : "r"(aw[i]), "r"(bw[i]));
+    }
+    return acc;
+}
+
 __device__ __forceinline__ uint4 streamLoad(const void* p) {
     // M is read exactly once: bypass L1 allocation so the vector stays cached
     uint4 r;
@@ -136,7 +157,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) gemvRowsVec16(const GemvA
 
 // ---- bulk-copy kernel --------------------------------------------------------------------------------------------
 
-constexpr int kBulkWarps = 16;  // at most
+constexpr int kBulkWarps = 16;  // of the kernel with the vector in registers
+constexpr int kBulkMaxWarps = 24;  // of the kernel with the vector in shared memory
 constexpr int kMaxVectors = 2;  // measured (4096 x n x 4096 f16): n = 2 10.8 us here against 15.5 on the tensor cores, n = 3 12.9,
                                 // n = 4 14.7, and slower than the tensor cores from n = 3 on when the rows are 11008 long
 constexpr int kPieceBytes = 8192;                   // one ring stage: a row of 4096 halves, or a piece of a longer one
@@ -193,7 +215,7 @@ struct BulkShape {
 };
 
 template <bool BF16, int NV>
-__global__ void __launch_bounds__(kBulkWarps * 32) gemvRowsBulk(const GemvArgs g, const BulkShape shape) {
+__global__ void __launch_bounds__(kBulkMaxWarps * 32) gemvRowsBulk(const GemvArgs g, const BulkShape shape) {
     extern __shared__ __align__(128) unsigned char shared[];
     const int stages = shape.stages, warps = shape.warps, pieceBytes = shape.pieceBytes, pieces = shape.pieces;
     unsigned char* vecShared = shared;
@@ -266,7 +288,7 @@ __global__ void __launch_bounds__(kBulkWarps * 32) gemvRowsBulk(const GemvArgs g
 #pragma unroll
                 for (int u = 0; u < 4; ++u) xv[u] = x[j * vectorChunks + c0 + 32 * u];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) acc[j][u] = dot8<BF16>(av[u], xv[u], acc[j][u]);
+                for (int u = 0; u < 4; ++u) acc[j][u] = dot8Mixed<BF16>(av[u], xv[u], acc[j][u]);
             }
         };
         int c = lane;
@@ -279,7 +301,7 @@ __global__ void __launch_bounds__(kBulkWarps * 32) gemvRowsBulk(const GemvArgs g
         for (; c < chunks; c += 32) {
             const uint4 av = a[c];
 #pragma unroll
-            for (int j = 0; j < NV; ++j) acc[j][0] = dot8<BF16>(av, x[j * vectorChunks + c], acc[j][0]);
+            for (int j = 0; j < NV; ++j) acc[j][0] = dot8Mixed<BF16>(av, x[j * vectorChunks + c], acc[j][0]);
         }
         __syncwarp();
         if (lane == 0 && item + stages < items) {
@@ -317,10 +339,143 @@ BulkShape bulkShape(int len, int vectors) {
     shape.pieceBytes = ((rowBytes + shape.pieces - 1) / shape.pieces + 511) / 512 * 512;  // equal pieces, whole warp-wide trips
     shape.stages = 1;
     shape.prefetchRows = 2;
-    for (shape.warps = 16; shape.warps >= 8; shape.warps -= 4)
+    static const int firstWarps = measureKnob("VKZB_GEMV_BULK_WARPS", 16);
+    for (shape.warps = firstWarps; shape.warps >= 8; shape.warps -= 4)
         if (shape.sharedBytes() <= size_t(kSharedLimit)) return shape;
     shape.warps = 0;  // a vector too long to sit in shared memory beside the ring
     return shape;
+}
+
+// ---- rows of up to 8 KB with the vector in registers ---------------------------------------------------------------------
+//
+// The decode shape proper: one right-hand side, rows of CHUNKS x 512 bytes (K = 4096 halves for CHUNKS = 16). Each lane keeps
+// its CHUNKS 16-byte pieces of the vector in registers for the whole launch, so shared memory carries nothing but the ring,
+// which takes all 227 KB: 28 rows of 8 KB. A 4096 x 4096 matrix gives a block of an 148-SM part 27 or 28 rows, so every byte
+// the block will read is requested in its first microsecond and the launch lasts one memory latency plus the stream time,
+// where a ring of one stage per warp (16 x 8 KB) needed two round trips (14 warps x 2 slots for 8 KB rows).
+// Issuing the first loads before the wait for the prior kernel (safe only under a caller's promise that nothing in flight
+// writes the matrix) was measured and gained under 3 %, so every load comes after the wait.
+template <bool BF16, int CHUNKS, bool MIXED>
+__global__ void __launch_bounds__(kBulkWarps * 32) gemvRowsResidentVector(const GemvArgs g, const int slotsPerWarp) {
+    extern __shared__ __align__(128) unsigned char shared[];
+    constexpr int kRowBytes = CHUNKS * 512;
+    const int warps = blockDim.x / 32, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int slots = warps * slotsPerWarp;
+    const unsigned barBase = sharedAddr(shared + size_t(slots) * kRowBytes);
+    const int firstRow = int((long long)g.rows * blockIdx.x / gridDim.x);
+    const int rows = int((long long)g.rows * (blockIdx.x + 1) / gridDim.x) - firstRow;
+    const char* M = static_cast<const char*>(g.M) + (long long)firstRow * g.rowStride * 2;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < slots; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(barBase + 8u * i) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    // Warp w multiplies block-local rows w, w + warps, ...; its j-th row goes through its own slot j % slotsPerWarp, so a
+    // slot is waited for, read and refilled by one warp, in that order.
+    const int myRows = (rows - warp + warps - 1) / warps;
+    unsigned char* myRing = shared + size_t(warp) * slotsPerWarp * kRowBytes;
+    const unsigned myBars = barBase + 8u * warp * slotsPerWarp;
+    const auto issue = [&](int j) {  // this warp's j-th row into its slot
+        const int slot = j % slotsPerWarp;
+        bulkLoad(sharedAddr(myRing + size_t(slot) * kRowBytes), M + (long long)(warp + j * warps) * g.rowStride * 2, unsigned(kRowBytes), myBars + 8u * slot);
+    };
+    const int first = min(slotsPerWarp, myRows);
+    if (g.overlap) {
+        if (lane < first) prefetchToL2(M + (long long)(warp + lane * warps) * g.rowStride * 2, unsigned(kRowBytes));
+        waitForPriorKernel();
+        releaseNextKernel();
+    }
+    if (lane < first) issue(lane);
+    if (myRows <= 0) return;
+    // the vector: this lane's pieces, straight from global memory (8 KB that every warp of the machine reads: L2 serves it)
+    uint4 x[CHUNKS];
+    const uint4* v = reinterpret_cast<const uint4*>(g.v);
+#pragma unroll
+    for (int q = 0; q < CHUNKS; ++q) x[q] = __ldg(v + lane + 32 * q);
+    for (int j = 0; j < myRows; ++j) {
+        const int slot = j % slotsPerWarp;
+        if (!bulkWait(myBars + 8u * slot, unsigned(j / slotsPerWarp) & 1u)) return;
+        const uint4* a = reinterpret_cast<const uint4*>(myRing + size_t(slot) * kRowBytes) + lane;
+        float acc[4] = {};
+#pragma unroll
+        for (int q = 0; q < CHUNKS; q += 2) {  // two 16-byte loads in flight per lane: with the vector in 64 registers more would spill
+            uint4 av[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) av[u] = a[32 * (q + u)];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if constexpr (MIXED) acc[(q + u) % 4] = dot8Mixed<BF16>(av[u], x[q + u], acc[(q + u) % 4]);
+                else acc[(q + u) % 4] = dot8<BF16>(av[u], x[q + u], acc[(q + u) % 4]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && j + slotsPerWarp < myRows) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the reads above come before the copy that overwrites them
+            issue(j + slotsPerWarp);
+        }
+        float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+        if (lane == 0) {  // the epilogue's state is set up here, once per row, rather than held in registers across the loop
+            Epilogue<float> epi;
+            epi.init(g.epi, 0);
+            storeY(epi, g.yIsRow, firstRow + warp + j * warps, sum);
+        }
+    }
+}
+
+// The kernel above serves rows of 2, 4 or 8 KB (K = 1024, 2048, 4096 16-bit values).
+int residentVectorChunks(int len) { return len == 4096 ? 16 : len == 2048 ? 8 : len == 1024 ? 4 : 0; }
+
+template <bool BF16, int CHUNKS, bool MIXED>
+cudaError_t launchResidentVectorFor(const Problem& p, const GemvArgs& g) {
+    static bool prepared[64] = {};
+    int device = 0, sms = 0;
+    if (cudaError_t e = cudaGetDevice(&device); e != cudaSuccess) return e;
+    if (cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device); e != cudaSuccess) return e;
+    if (device < 64 && !prepared[device]) {
+        if (cudaError_t e = cudaFuncSetAttribute(gemvRowsResidentVector<BF16, CHUNKS, MIXED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSharedLimit);
+            e != cudaSuccess)
+            return e;
+        prepared[device] = true;
+    }
+    // Sixteen warps per SM with one slot each. Measured on 4096 x 4096 and 11008 x 4096 f16 (one block of 16 warps per SM):
+    // 16 x 1 slots 6.6 / 15.1 us, 14 x 2 7.8 / 15.8, 12 x 2 7.7 / 15.6, 8 x 3 8.1 / 15.2: the multiply, not the bytes in
+    // flight, is what a block waits for, so warps count for more than slots. The same 16 warps as four blocks of four
+    // (blocks of the next launch then find room beside those of this one): 6.6 / 14.6 us; that form serves matrices with
+    // at least 64 rows per SM, where it gains 3 %.
+    const int rowBytes = CHUNKS * 512, maxSlots = (kSharedLimit - 1024) / (rowBytes + 8);
+    static const int forcedBlocks = measureKnob("VKZB_GEMV_BLOCKS_PER_SM", 0);
+    const int blocksPerSm = forcedBlocks ? forcedBlocks : g.rows >= 64 * sms ? 4 : 1;
+    const int blocks = std::min(sms * blocksPerSm, g.rows);
+    int warps = kBulkWarps / blocksPerSm, slotsPerWarp = 1;
+    static const int forcedWarps = measureKnob("VKZB_GEMV_WARPS", 0), forcedSlots = measureKnob("VKZB_GEMV_SLOTS", 0);
+    if (forcedWarps) warps = forcedWarps, slotsPerWarp = forcedSlots ? forcedSlots : std::max(1, maxSlots / blocksPerSm / warps);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(warps * 32);
+    cfg.dynamicSmemBytes = size_t(warps) * slotsPerWarp * (rowBytes + 8);
+    cfg.stream = p.stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = g.overlap ? 1 : 0;
+    countLaunch();
+    return cudaLaunchKernelEx(&cfg, gemvRowsResidentVector<BF16, CHUNKS, MIXED>, g, slotsPerWarp);
+}
+
+template <bool BF16>
+cudaError_t launchResidentVector(const Problem& p, const GemvArgs& g, int chunks) {
+    static const bool mixed = measureKnob("VKZB_GEMV_MIXED", 1) != 0;  // measurement builds can fall back to convert-then-FMA
+    if (!mixed) return chunks == 16 ? launchResidentVectorFor<BF16, 16, false>(p, g) : cudaErrorInvalidValue;
+    switch (chunks) {
+    case 16: return launchResidentVectorFor<BF16, 16, true>(p, g);
+    case 8: return launchResidentVectorFor<BF16, 8, true>(p, g);
+    case 4: return launchResidentVectorFor<BF16, 4, true>(p, g);
+    default: return cudaErrorInvalidValue;
+    }
 }
 
 template <bool BF16, int NV>
@@ -485,6 +640,9 @@ cudaError_t launchGemv(const Problem& p) {
     g.overlap = overlapMode();
     static const bool rowsOnly = measureKnob("VKZB_GEMV_ROWS_ONLY", 0) != 0;  // measurement builds: never the bulk-copy kernel
     const BulkShape shape = vec16 && p.batch == 1 && !rowsOnly ? bulkShape(g.len, 1) : BulkShape{};
+    static const bool noResident = measureKnob("VKZB_GEMV_NO_RESIDENT", 0) != 0;  // measurement builds only
+    if (shape.warps && !noResident && residentVectorChunks(g.len) && g.rows >= 64)
+        return g.typeM == kBF16 ? launchResidentVector<true>(p, g, residentVectorChunks(g.len)) : launchResidentVector<false>(p, g, residentVectorChunks(g.len));
     if (shape.warps) return g.typeM == kBF16 ? launchBulk<true>(p, g, shape) : launchBulk<false>(p, g, shape);
     if (vec16) {
         for (int first = 0; first < p.batch; first += kMaxGridY) {

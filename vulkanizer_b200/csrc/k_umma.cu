@@ -1284,6 +1284,7 @@ cudaError_t launchUmma(const Problem& p) {
     if (logChoice)
         std::fprintf(stderr, "vkzb: umma tile %d x %d%s, %lld tiles, %d k slices in %d splits, %s store, chunked loads A %d B %d\n", pair ? 256 : 128, bn, pair ? (wide ? " (two-CTA pairs, wide epilogue)" : " (two-CTA pairs)") : (wide ? " (wide epilogue)" : ""),
                      g.totalTiles, g.numKSlices, splits, g.tmaStore ? "TMA" : "direct", g.chunkedA, g.chunkedB);
+    setLastPlan(bn | (pair ? 1 << 10 : 0) | (wide ? 1 << 11 : 0) | splits << 12);
     if (wide) {
         if (pair) return bn == 256 ? launchWith<256, true, true>(g, mapA, mapB, mapD, mirrors, 8, p.stream) : launchWith<128, true, true>(g, mapA, mapB, mapD, mirrors, 9, p.stream);
         if (bn == 256) return launchWith<256, false, true>(g, mapA, mapB, mapD, mirrors, 5, p.stream);

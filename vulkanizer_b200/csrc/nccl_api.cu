@@ -111,7 +111,7 @@ struct ncclComm {
     std::string shmName;
     Arena* arena = nullptr;
     Arena* peerArena[kMaxRanks] = {};
-    cudaIpcMemHandle_t peerArenaHandle[kMaxRanks] = {};  // what was opened to reach peerArena[p] (other processes only)
+    uint64_t peerArenaBase[kMaxRanks] = {}, peerArenaGeneration[kMaxRanks] = {};  // what was opened to reach peerArena[p] (other processes only)
     bool samePid[kMaxRanks] = {};
     bool hostSync = false;  // some ranks share a GPU
     uint64_t opSeq = 0, deviceBarrierSeq = 0, hostBarrierSeq = 0, splitCount = 0;
@@ -126,6 +126,7 @@ struct ncclComm {
     struct Mapping {
         cudaIpcMemHandle_t handle;
         void* local;
+        uint64_t generation;  // of the process-wide mapping this one uses
     };
     std::map<std::pair<int, uint64_t>, Mapping> mappings;  // (peer, remote base) -> local mapping
     std::string lastError;
@@ -359,50 +360,70 @@ bool describeBuffer(const void* ptr, BufferPost& out) {
     return cudaIpcGetMemHandle(&out.handle, reinterpret_cast<void*>(base)) == cudaSuccess;
 }
 
-// CUDA lets a process open the IPC handle of an allocation only once at a time, and several things of one peer can live in
-// the same allocation (cudaMalloc carves small requests out of larger blocks: the flag arenas of a communicator and of the
-// communicators split from it, say). So opened handles are shared process-wide and counted.
+// CUDA maps an allocation of another process into this one only once at a time, and the handles it gives out do not name
+// allocations one to one: small cudaMalloc requests share blocks, and two buffers of one block come with different handles
+// of which only one can be open ("resource already mapped" for the second). So what this process has opened is kept
+// process-wide, keyed by the owner's process and the allocation's base address there, and counted: a second buffer of a
+// block that is already open reuses the mapping, whichever communicator asks.
 struct IpcKey {
-    int device;
-    unsigned char bytes[sizeof(cudaIpcMemHandle_t)];
-    bool operator<(const IpcKey& o) const { return device != o.device ? device < o.device : std::memcmp(bytes, o.bytes, sizeof bytes) < 0; }
+    int device, pid;
+    uint64_t base;
+    bool operator<(const IpcKey& o) const { return device != o.device ? device < o.device : pid != o.pid ? pid < o.pid : base < o.base; }
 };
 struct IpcOpened {
+    cudaIpcMemHandle_t handle;
     void* local;
     int users;
+    uint64_t generation;
 };
 std::mutex g_ipcMutex;
 std::map<IpcKey, IpcOpened> g_ipcOpened;
+uint64_t g_ipcGeneration = 0;
 
-IpcKey ipcKeyOf(const cudaIpcMemHandle_t& handle) {
+IpcKey ipcKeyOf(int pid, uint64_t base) {
     IpcKey k{};
     cudaGetDevice(&k.device);
-    std::memcpy(k.bytes, &handle, sizeof k.bytes);
+    k.pid = pid, k.base = base;
     return k;
 }
 
-void* ipcAcquire(const cudaIpcMemHandle_t& handle) {
-    const IpcKey key = ipcKeyOf(handle);
+// The local address of the allocation of process `pid` that starts at `base` there. `generation` identifies the mapping for
+// ipcRelease (a later allocation at the same address is a different mapping).
+void* ipcAcquire(int pid, uint64_t base, const cudaIpcMemHandle_t& handle, uint64_t& generation) {
+    const IpcKey key = ipcKeyOf(pid, base);
     std::lock_guard<std::mutex> lock(g_ipcMutex);
     auto it = g_ipcOpened.find(key);
-    if (it != g_ipcOpened.end()) {
+    if (it != g_ipcOpened.end() && std::memcmp(&it->second.handle, &handle, sizeof handle) == 0) {
         ++it->second.users;
+        generation = it->second.generation;
         return it->second.local;
     }
     void* local = nullptr;
-    if (cudaIpcOpenMemHandle(&local, handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
-        cudaGetLastError();
-        return nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&local, handle, cudaIpcMemLazyEnablePeerAccess);
+    if (e == cudaSuccess) {
+        if (it != g_ipcOpened.end()) {  // the owner freed the old allocation and got this address again: the old mapping is dead
+            cudaIpcCloseMemHandle(it->second.local);
+            g_ipcOpened.erase(it);
+        }
+        generation = ++g_ipcGeneration;
+        g_ipcOpened.emplace(key, IpcOpened{handle, local, 1, generation});
+        return local;
     }
-    g_ipcOpened.emplace(key, IpcOpened{local, 1});
-    return local;
+    cudaGetLastError();
+    if (e == cudaErrorAlreadyMapped && it != g_ipcOpened.end()) {  // another handle of the block that is open already
+        ++it->second.users;
+        generation = it->second.generation;
+        return it->second.local;
+    }
+    if (std::getenv("VKZB_LOG")) std::fprintf(stderr, "vkzb nccl: cudaIpcOpenMemHandle: %s (%zu allocations open)\n", cudaGetErrorString(e), g_ipcOpened.size());
+    return nullptr;
 }
 
-void ipcRelease(const cudaIpcMemHandle_t& handle) {
-    const IpcKey key = ipcKeyOf(handle);
+void ipcRelease(int pid, uint64_t base, uint64_t generation) {
+    const IpcKey key = ipcKeyOf(pid, base);
     std::lock_guard<std::mutex> lock(g_ipcMutex);
     auto it = g_ipcOpened.find(key);
-    if (it == g_ipcOpened.end()) return;
+    if (it == g_ipcOpened.end() || it->second.generation != generation) return;
     if (--it->second.users == 0) {
         cudaIpcCloseMemHandle(it->second.local);
         g_ipcOpened.erase(it);
@@ -413,17 +434,19 @@ void ipcRelease(const cudaIpcMemHandle_t& handle) {
 void* mapPeerBuffer(ncclComm* c, int peer, const BufferPost& post) {
     if (!post.base) return nullptr;
     if (c->samePid[peer]) return reinterpret_cast<void*>(post.base + post.offset);
+    const int pid = c->shared->ranks[peer].pid;
     const auto key = std::make_pair(peer, post.base);
     auto it = c->mappings.find(key);
     if (it != c->mappings.end() && std::memcmp(&it->second.handle, &post.handle, sizeof post.handle) != 0) {
-        ipcRelease(it->second.handle);  // the address was freed and allocated again: a different allocation
+        ipcRelease(pid, post.base, it->second.generation);  // another buffer of the block, or the address was freed and allocated again
         c->mappings.erase(it);
         it = c->mappings.end();
     }
     if (it == c->mappings.end()) {
-        void* local = ipcAcquire(post.handle);
+        uint64_t generation = 0;
+        void* local = ipcAcquire(pid, post.base, post.handle, generation);
         if (!local) return nullptr;
-        it = c->mappings.emplace(key, ncclComm::Mapping{post.handle, local}).first;
+        it = c->mappings.emplace(key, ncclComm::Mapping{post.handle, local, generation}).first;
     }
     return static_cast<char*>(it->second.local) + post.offset;
 }
@@ -806,13 +829,66 @@ std::string shmNameOf(const IdPayload& id) {
     return name;
 }
 
+// Flag arenas come from one block per device and process, exported once: CUDA maps an allocation into a peer process only
+// once at a time, and small cudaMalloc requests share blocks, so a second communicator of the same processes (ncclCommSplit,
+// or simply another ncclCommInitRank) whose arena had landed in a block its peers already hold open could not be mapped
+// ("resource already mapped"). With every arena in the one block and every post carrying the block's one handle, the peers
+// open it once and count its users.
+constexpr size_t kArenaSlotBytes = 1024, kArenaPoolBytes = size_t(2) << 20;
+static_assert(sizeof(Arena) <= kArenaSlotBytes, "arena slot");
+struct ArenaPool {
+    char* base = nullptr;
+    cudaIpcMemHandle_t handle{};
+    std::vector<bool> taken;
+};
+std::mutex g_arenaMutex;
+ArenaPool g_arenaPools[64];
+
+Arena* arenaTake(int device, BufferPost& post) {
+    if (device < 0 || device >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_arenaMutex);
+    ArenaPool& pool = g_arenaPools[device];
+    if (!pool.base) {
+        void* block = nullptr;
+        if (cudaMalloc(&block, kArenaPoolBytes) != cudaSuccess || cudaIpcGetMemHandle(&pool.handle, block) != cudaSuccess) {
+            cudaGetLastError();
+            if (block) cudaFree(block);
+            return nullptr;
+        }
+        pool.base = static_cast<char*>(block);
+        pool.taken.assign(kArenaPoolBytes / kArenaSlotBytes, false);
+    }
+    for (size_t i = 0; i < pool.taken.size(); ++i) {
+        if (pool.taken[i]) continue;
+        char* slot = pool.base + i * kArenaSlotBytes;
+        if (cudaMemset(slot, 0, kArenaSlotBytes) != cudaSuccess) return nullptr;
+        pool.taken[i] = true;
+        std::memset(&post, 0, sizeof post);
+        post.handle = pool.handle;
+        post.base = reinterpret_cast<uint64_t>(pool.base);
+        post.offset = i * kArenaSlotBytes;
+        return reinterpret_cast<Arena*>(slot);
+    }
+    return nullptr;
+}
+
+void arenaGive(int device, Arena* arena) {
+    if (!arena || device < 0 || device >= 64) return;
+    std::lock_guard<std::mutex> lock(g_arenaMutex);
+    ArenaPool& pool = g_arenaPools[device];
+    if (pool.base) pool.taken[size_t(reinterpret_cast<char*>(arena) - pool.base) / kArenaSlotBytes] = false;
+}
+
 // Gives back what a communicator holds on this side (mappings, arena, the shared-memory view). `announce`: tell the peers
 // that this rank has left (and remove the shared-memory object's name once every rank has).
 void release(ncclComm* c, bool announce) {
-    for (auto& m : c->mappings) ipcRelease(m.second.handle);
+    if (c->shared) {
+        for (auto& m : c->mappings) ipcRelease(c->shared->ranks[m.first.first].pid, m.first.second, m.second.generation);
+        for (int p = 0; p < c->nranks; ++p)
+            if (p != c->rank && c->peerArena[p] && !c->samePid[p])
+                ipcRelease(c->shared->ranks[p].pid, c->peerArenaBase[p], c->peerArenaGeneration[p]), c->peerArena[p] = nullptr;
+    }
     c->mappings.clear();
-    for (int p = 0; p < c->nranks; ++p)
-        if (p != c->rank && c->peerArena[p] && !c->samePid[p]) ipcRelease(c->peerArenaHandle[p]), c->peerArena[p] = nullptr;
     if (c->shared) {
         if (announce) {
             c->shared->ranks[c->rank].state.store(2, std::memory_order_release);
@@ -824,7 +900,7 @@ void release(ncclComm* c, bool announce) {
         munmap(c->shared, sizeof(Shared));
         c->shared = nullptr;
     }
-    if (c->arena) cudaFree(c->arena);
+    arenaGive(c->device, c->arena);
     c->arena = nullptr;
 }
 
@@ -858,16 +934,12 @@ ncclResult_t initRank(ncclComm_t* out, int nranks, const ncclUniqueId& uid, int 
     close(fd);
     if (mem == MAP_FAILED) return giveUp(ncclSystemError, "mmap failed", false);
     c->shared = static_cast<Shared*>(mem);
-    if (cudaMalloc(reinterpret_cast<void**>(&c->arena), sizeof(Arena)) != cudaSuccess || cudaMemset(c->arena, 0, sizeof(Arena)) != cudaSuccess)
-        return giveUp(ncclUnhandledCudaError, "could not allocate the flag arena", false);
     RankSlot& slot = c->shared->ranks[rank];
+    c->arena = arenaTake(c->device, slot.arenaPost);
+    if (!c->arena) return giveUp(ncclUnhandledCudaError, "could not allocate or export the flag arena", false);
     slot.pid = int(getpid());
     cudaDeviceGetPCIBusId(slot.busId, sizeof slot.busId, c->device);
     slot.arenaRaw = reinterpret_cast<uint64_t>(c->arena);
-    if (nranks > 1 && !describeBuffer(c->arena, slot.arenaPost)) {
-        cudaGetLastError();
-        return giveUp(ncclUnhandledCudaError, "cudaIpcGetMemHandle failed for the flag arena", false);
-    }
     slot.state.store(1, std::memory_order_release);
     const ncclResult_t r = hostWait(c, [&] {
         for (int p = 0; p < nranks; ++p)
@@ -887,9 +959,9 @@ ncclResult_t initRank(ncclComm_t* out, int nranks, const ncclUniqueId& uid, int 
             cudaDeviceGetByPCIBusId(&peerDev, s.busId);
             if (peerDev >= 0 && peerDev != c->device && cudaDeviceEnablePeerAccess(peerDev, 0) != cudaSuccess) cudaGetLastError();
         } else {
-            void* base = ipcAcquire(s.arenaPost.handle);
+            void* base = ipcAcquire(s.pid, s.arenaPost.base, s.arenaPost.handle, c->peerArenaGeneration[p]);
             if (!base) return giveUp(ncclUnhandledCudaError, "cudaIpcOpenMemHandle failed for a peer's flag arena (no peer access between the GPUs?)", true);
-            c->peerArenaHandle[p] = s.arenaPost.handle;
+            c->peerArenaBase[p] = s.arenaPost.base;
             c->peerArena[p] = reinterpret_cast<Arena*>(static_cast<char*>(base) + s.arenaPost.offset);
         }
     }
