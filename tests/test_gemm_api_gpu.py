@@ -11,7 +11,7 @@ import math
 import numpy as np
 import pytest
 
-from harness import CUDA_TYPE, DeviceBuffer, N, T
+from harness import CUDA_TYPE, ELEM, DeviceBuffer, N, T
 from oracle import pyoracle as orc
 from vulkanizer_b200 import capi
 
@@ -431,3 +431,66 @@ def test_more_columns_than_one_grid_dimension_holds(cuda, blas):
     blas.sgemm(N, N, m, n, k, 1.0, dA.ptr, m, dB.ptr, k, 0.0, dD.ptr, m)
     want = (av.reshape(k, m).T.astype(np.float64) @ bv.reshape(n, k).T.astype(np.float64)).T.ravel()
     assert np.allclose(dD.download(), want, atol=1e-5)
+
+
+# ---- pointer-array batches on the tensor cores ---------------------------------------------------------------------------
+
+POINTER_CASES = [
+    # name, ta, tb, m, n, k, type ab, type c, alpha, beta, batch, byte offset of entry 1's A (0: aligned)
+    ("f16 TN -> f32", T, N, 256, 192, 128, "f16", "f32", 1.0, 0.0, 24, 0),
+    ("bf16 NN -> bf16 with beta", N, N, 128, 136, 256, "bf16", "bf16", 0.5, 1.5, 16, 0),
+    ("f16 NT ragged -> f16", N, T, 200, 72, 192, "f16", "f16", 1.0, 0.0, 20, 0),
+    ("int8 TN -> s32", T, N, 256, 128, 512, "s8", "s32", 1, 0, 12, 0),
+    ("f16 TN, one entry not 16-byte aligned", T, N, 256, 192, 128, "f16", "f32", 1.0, 0.5, 24, 2),
+    ("f16 TN, C rows not a multiple of 16 bytes (direct stores)", T, N, 250, 64, 128, "f16", "f32", 1.0, 0.0, 24, 0),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", POINTER_CASES, ids=lambda c: c[0])
+def test_pointer_array_batch_on_tensor_cores(cuda, blas, case):
+    """cublasGemmBatchedEx with aligned matrices runs on the tcgen05 kernel through per-entry tensor maps built on the device
+    (the reference serves pointer arrays from its scalar shader, src/cublas/cublas.cpp:787, 1131-1139). Whether an entry's
+    address suits TMA only the device can tell: when one does not, the CUDA-core kernel queued behind does the work instead,
+    and the results are the same either way."""
+    from vulkanizer_b200 import synth
+    name, ta, tb, m, n, k, kind, kind_c, alpha, beta, batch, misalign = case
+    rows_a, cols_a = (k, m) if ta == T else (m, k)
+    rows_b, cols_b = (n, k) if tb == T else (k, n)
+    lda, ldb, ldc = (rows_a + 7) // 8 * 8, (rows_b + 7) // 8 * 8, m
+    es, es_c = ELEM[kind], ELEM[kind_c]
+    pitch_a, pitch_b, pitch_c = lda * cols_a + 64, ldb * cols_b + 64, ldc * n + 64   # entries lie apart, each 16-byte aligned
+    if kind == "s8":
+        A, B = synth.int8_uniform(2, pitch_a * batch), synth.int8_uniform(2, pitch_b * batch, first=1 << 20)
+        C0 = (synth.int8_uniform(9, pitch_c * batch).astype(np.int32)) * 100
+    else:
+        A, _ = orc.fill_lcg(kind, pitch_a * batch, 51)
+        B, _ = orc.fill_lcg(kind, pitch_b * batch, 52)
+        C0, _ = orc.fill_lcg(kind_c, pitch_c * batch, 53)
+    dA, dB, dC = DeviceBuffer(cuda, A), DeviceBuffer(cuda, B), DeviceBuffer(cuda, C0)
+    offs_a = [e * pitch_a * es + (misalign if e == 1 else 0) for e in range(batch)]
+    ptrs = np.array([dA.ptr + o for o in offs_a] + [dB.ptr + e * pitch_b * es for e in range(batch)] + [dC.ptr + e * pitch_c * es_c for e in range(batch)],
+                    dtype=np.uint64)
+    dP = DeviceBuffer(cuda, ptrs)
+    compute = capi.COMPUTE_32I if kind == "s8" else capi.COMPUTE_32F
+    blas.gemm_batched_ex(ta, tb, m, n, k, alpha, dP.ptr, CUDA_TYPE[kind], lda, dP.ptr + 8 * batch, CUDA_TYPE[kind], ldb, beta, dP.ptr + 16 * batch,
+                         CUDA_TYPE[kind_c], ldc, batch, compute=compute)
+    assert blas.last_path() == capi.PATH_UMMA
+    got_all = dC.download()
+    for e in (0, 1, batch - 1):
+        a0 = offs_a[e] // es
+        Ae, Be, Ce = A[a0:a0 + lda * cols_a], B[e * pitch_b:e * pitch_b + ldb * cols_b], C0[e * pitch_c:e * pitch_c + ldc * n]
+        got = got_all[e * pitch_c:e * pitch_c + ldc * n]
+        if kind == "s8":
+            want = orc.gemm_s8(ta == T, tb == T, m, n, k, 1, alpha, np.ascontiguousarray(Ae), lda, 0, np.ascontiguousarray(Be), ldb, 0, beta, Ce.copy(), ldc, 0)
+            assert np.array_equal(got, want), f"entry {e}"
+        else:
+            want, _ = orc.gemm_fp64(ta == T, tb == T, m, n, k, 1, alpha, np.ascontiguousarray(Ae), kind, lda, 0, np.ascontiguousarray(Be), kind, ldb, 0, beta,
+                                    np.ascontiguousarray(Ce), kind_c, ldc, 0)
+            rel = 1e-5 if kind_c == "f32" else 2e-3 if kind_c == "f16" else 1.6e-2
+            tol = rel * np.maximum(1.0, np.abs(want)) * math.sqrt(k + 1.0)
+            assert (np.abs(orc.to_float(got, kind_c) - want) <= tol).all(), f"entry {e}"
+    # the gaps between the entries of C are untouched
+    for e in range(batch):
+        assert np.array_equal(got_all[e * pitch_c + ldc * n:(e + 1) * pitch_c], C0[e * pitch_c + ldc * n:(e + 1) * pitch_c])
+    assert blas.device_status() == 0

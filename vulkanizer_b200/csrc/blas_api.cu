@@ -209,7 +209,7 @@ static bool acquireScratch(cublasHandle_t h, cudaStream_t stream) {
     if (!h->scratch) {
         if (h->scratchTried || capturing) return false;
         h->scratchTried = true;
-        if (cudaMalloc(&h->scratch, kScratchBytes) != cudaSuccess || cudaMemset(h->scratch, 0, kSplitKCounters * sizeof(unsigned)) != cudaSuccess ||
+        if (cudaMalloc(&h->scratch, kScratchBytes) != cudaSuccess || cudaMemset(h->scratch, 0, kSplitKCounters * sizeof(unsigned) + 256) != cudaSuccess ||  // the counters and the flag word behind them
             cudaEventCreateWithFlags(&h->scratchEvent, cudaEventDisableTiming) != cudaSuccess) {
             cudaGetLastError();
             if (h->scratch) cudaFree(h->scratch);
@@ -267,7 +267,16 @@ cublasStatus_t dispatch(cublasHandle_t h, Problem& p, cudaStream_t stream) {
     } else if (forcedPath() == VKZB_PATH_GENERIC) {
         path = VKZB_PATH_GENERIC;
         err = launchGeneric(p);
-    } else if (forcedPath() != -int(VKZB_PATH_UMMA) && ummaEligible(p)) {
+    } else if (forcedPath() != -int(VKZB_PATH_UMMA) && p.pointerArrays && ummaEligible(p) && acquireScratch(h, stream)) {
+        p.scratch = h->scratch, p.scratchBytes = h->scratchBytes;
+        // Pointer arrays on the tensor cores: a kernel builds a tensor map per batch entry in the handle's scratch memory,
+        // the tcgen05 kernel runs on them, and the CUDA-core kernel is queued behind it for the one case only the device can
+        // see, matrices whose addresses TMA cannot take: exactly one of the two does the work.
+        path = VKZB_PATH_UMMA;
+        p.launchSerial = ++h->launchSerial ? h->launchSerial : ++h->launchSerial;  // never 0, the word's initial content
+        err = launchUmma(p);
+        if (err == cudaSuccess) err = launchGenericStandIn(p, ummaEntryFlag(p), p.launchSerial);
+    } else if (forcedPath() != -int(VKZB_PATH_UMMA) && !p.pointerArrays && ummaEligible(p)) {
         path = VKZB_PATH_UMMA;
         if (wantsScratch(p, true) && acquireScratch(h, stream)) p.scratch = h->scratch, p.scratchBytes = h->scratchBytes;
         err = launchUmma(p);

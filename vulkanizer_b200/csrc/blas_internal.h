@@ -24,6 +24,7 @@ struct cublasContext {
     cudaStream_t scratchStream = nullptr;  // stream of the last call that used the scratch memory
     bool scratchUsed = false;
     cudaEvent_t scratchEvent = nullptr;
+    unsigned launchSerial = 0;  // numbers the pointer-array launches that use the scratch memory's flag word
     // output mirrors (vkzbSetOutputMirrors): results inside [mirrorLocal, mirrorLocal + mirrorBytes) are also written there
     const char* mirrorLocal = nullptr;
     size_t mirrorBytes = 0;

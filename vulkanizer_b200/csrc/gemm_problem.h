@@ -82,6 +82,7 @@ struct Problem {
     void* mirrorD[kMaxMirrors] = {};
     void* scratch = nullptr;          // the handle's scratch memory (split-k partial sums); calls sharing it must not overlap
     size_t scratchBytes = 0;
+    unsigned launchSerial = 0;          // pointer-array launches on the tensor cores: this launch's number on its handle (see ummaEntryFlag)
     cudaStream_t stream = nullptr;
 };
 
@@ -96,6 +97,10 @@ cudaError_t launchGemv(const Problem& p);     // m = 1 or n = 1 (or gemvTakesFew
 bool sgemmEligible(const Problem& p);
 cudaError_t launchSgemm(const Problem& p);    // fp32 FFMA (split along k through p.scratch when the product is small)
 constexpr int kSplitKCounters = 4096;          // arrival counters at the start of split-k scratch memory
+// Pointer-array launches on the tensor cores: the device word that holds p.launchSerial when the tensor-core kernel stood down
+// (an entry's address does not suit TMA), and the CUDA-core stand-in that then does the work.
+const unsigned* ummaEntryFlag(const Problem& p);
+cudaError_t launchGenericStandIn(const Problem& p, const unsigned* runIfEquals, unsigned value);
 size_t sgemmSplitKScratchBytes(int m, int n, int splits);
 int sgemmSplitKPlan(const Problem& p, size_t scratchBytes);
 cudaError_t launchSgemmSplitK(const Problem& p, int splits, void* scratch);

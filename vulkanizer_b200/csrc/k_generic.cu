@@ -24,11 +24,10 @@ struct GenericArgs {
     EpilogueArgs epi;
 };
 
+// One 64 x 64 tile of one batch entry.
 template <typename Acc>
-__global__ void __launch_bounds__(kThreads) genericGemmKernel(const GenericArgs g) {
-    __shared__ Acc sA[kStep][kTile + 1];
-    __shared__ Acc sB[kStep][kTile + 1];
-    const long long entry = (long long)blockIdx.z + g.batchOffset;
+__device__ __forceinline__ void genericTile(const GenericArgs& g, int tileRow, int tileCol, long long entry, Acc (&sA)[kStep][kTile + 1],
+                                            Acc (&sB)[kStep][kTile + 1]) {
     const char* A;
     const char* B;
     if (g.pointerArrays) {
@@ -38,7 +37,7 @@ __global__ void __launch_bounds__(kThreads) genericGemmKernel(const GenericArgs 
         A = static_cast<const char*>(g.A) + entry * g.strideA * dtypeSize(g.typeA);
         B = static_cast<const char*>(g.B) + entry * g.strideB * dtypeSize(g.typeB);
     }
-    const int row0 = blockIdx.x * kTile, col0 = (blockIdx.y + g.colTileBase) * kTile;
+    const int row0 = tileRow * kTile, col0 = tileCol * kTile;
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     Acc acc[4][4] = {};
     for (int k0 = 0; k0 < g.k; k0 += kStep) {
@@ -81,6 +80,26 @@ __global__ void __launch_bounds__(kThreads) genericGemmKernel(const GenericArgs 
             const int row = row0 + tx + 16 * i, col = col0 + ty + 16 * j;
             if (row < g.m && col < g.n) epi.store(row, col, acc[i][j]);
         }
+}
+
+template <typename Acc>
+__global__ void __launch_bounds__(kThreads) genericGemmKernel(const GenericArgs g) {
+    __shared__ Acc sA[kStep][kTile + 1];
+    __shared__ Acc sB[kStep][kTile + 1];
+    genericTile<Acc>(g, blockIdx.x, blockIdx.y + g.colTileBase, (long long)blockIdx.z + g.batchOffset, sA, sB);
+}
+
+// The same as a stand-in queued behind a tensor-core launch that may have stood down (a pointer-array batch with an address
+// TMA cannot take): a few blocks per SM that leave at once unless *runIfSet says the work is theirs, and then walk all the
+// tiles. (A full grid of blocks that only look and leave would cost more than the tensor-core launch itself.)
+template <typename Acc>
+__global__ void __launch_bounds__(kThreads) genericGemmStandIn(const GenericArgs g, const unsigned* runIfEquals, unsigned value, int entries) {
+    __shared__ Acc sA[kStep][kTile + 1];
+    __shared__ Acc sB[kStep][kTile + 1];
+    if (*runIfEquals != value) return;
+    const long long tilesM = (g.m + kTile - 1) / kTile, tilesN = (g.n + kTile - 1) / kTile, total = tilesM * tilesN * entries;
+    for (long long t = blockIdx.x; t < total; t += gridDim.x)
+        genericTile<Acc>(g, int(t % tilesM), int(t / tilesM % tilesN), t / (tilesM * tilesN), sA, sB);
 }
 
 // k = 0 (or alpha's product absent): D = act(beta C + bias), the "k = 0 scales C" case of the
@@ -155,6 +174,19 @@ cudaError_t launchGeneric(const Problem& p) {
             if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
         }
     return cudaSuccess;
+}
+
+cudaError_t launchGenericStandIn(const Problem& p, const unsigned* runIfEquals, unsigned value) {
+    GenericArgs g{p.A, p.B, p.lda, p.ldb, p.strideA, p.strideB, p.typeA, p.typeB, p.m, p.n, p.k,
+                  p.transA, p.transB, p.pointerArrays, 0, 0, p.epi};
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const long long tiles = (long long)((p.m + kTile - 1) / kTile) * ((p.n + kTile - 1) / kTile) * p.batch;
+    const unsigned grid = unsigned(std::min<long long>(tiles, 4LL * sms));
+    if (p.accType == kS32) genericGemmStandIn<int><<<grid, kThreads, 0, p.stream>>>(g, runIfEquals, value, p.batch);
+    else genericGemmStandIn<float><<<grid, kThreads, 0, p.stream>>>(g, runIfEquals, value, p.batch);
+    countLaunch();
+    return cudaGetLastError();
 }
 
 cudaError_t launchScale(const Problem& p) {

@@ -78,6 +78,13 @@ struct UmmaArgs {
     int boxBytesA, boxBytesB;
     int boxElemsA, boxElemsB;       // elements of m / n per box when MN-major
     int batchMulA, batchMulB;       // 0: the operand is shared by every batch entry
+    // Pointer-array batches: the matrices of entry e have their own tensor maps, entryMaps[3 e] (A), [3 e + 1] (B) and
+    // [3 e + 2] (D), written to device memory by buildEntryMaps just before this launch; *entryFlag is non-zero when an
+    // entry's pointers cannot be served by TMA, in which case this launch does nothing and the CUDA-core kernel behind it
+    // does the work.
+    const CUtensorMap* entryMaps;
+    const unsigned* entryFlag;
+    unsigned entrySerial;           // *entryFlag == entrySerial: stand down (the word needs no clearing between launches)
     int tmaStore;                   // D is 16-byte aligned in every dimension: results leave through shared memory and TMA
     int mirrorCount;                // every bulk store of D is repeated into this many other buffers (peer GPUs)
     // Split along k: a unit of work is (tile, split); the splits of a tile run on different CTAs at the same time, each
@@ -145,6 +152,11 @@ template <unsigned SLEEP_NS = 0>
 __device__ __forceinline__ bool mbarWait(unsigned bar, unsigned parity, volatile int* abortFlag, unsigned code) {
     if (mbarTryWait(bar, parity)) return true;
     return mbarWaitSlow<SLEEP_NS>(bar, parity, abortFlag, code);
+}
+
+// A tensor map that a kernel wrote to global memory is read through the tensor-map proxy only after this fence.
+__device__ __forceinline__ void tensorMapAcquire(const CUtensorMap* map) {
+    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(reinterpret_cast<unsigned long long>(map)) : "memory");
 }
 
 __device__ __forceinline__ void tmaLoad3d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1, int c2) {
@@ -672,7 +684,7 @@ struct SmemPlan {
 // The TMA producer's loop. KMAJOR: both operands are contiguous along k (op(A) = A^T, op(B) = B), one box each per stage;
 // otherwise an operand that is contiguous along m or n arrives as several boxes of 128 bytes by slice-length rows.
 template <int BN, bool PAIR, bool WIDE, bool KMAJOR>
-__device__ __forceinline__ void producerLoop(const UmmaArgs& g, const CUtensorMap* mapA, const CUtensorMap* mapB, unsigned smemBase,
+__device__ __forceinline__ void producerLoop(const UmmaArgs& g, const CUtensorMap* launchMapA, const CUtensorMap* launchMapB, unsigned smemBase,
                                              unsigned fullBar, unsigned emptyBar, unsigned ctaRank, long long firstUnit, long long unitStride,
                                              volatile int* abortFlag) {
     using Plan = SmemPlan<BN, PAIR, WIDE>;
@@ -688,7 +700,11 @@ __device__ __forceinline__ void producerLoop(const UmmaArgs& g, const CUtensorMa
         const int split = int(unit % g.splits);
         const TileCoord t = tileCoord(g, unit / g.splits);
         const int row0 = t.row * kTileRows + int(ctaRank) * kBM, col0 = t.col * BN + int(ctaRank) * Plan::kCtaB;
-        const int batchA = t.batch * g.batchMulA, batchB = t.batch * g.batchMulB;
+        // a pointer-array batch: this entry's own maps (batch coordinate 0), made by the kernel before this one
+        const CUtensorMap* mapA = g.entryMaps ? g.entryMaps + 3 * t.batch : launchMapA;
+        const CUtensorMap* mapB = g.entryMaps ? g.entryMaps + 3 * t.batch + 1 : launchMapB;
+        if (g.entryMaps) tensorMapAcquire(mapA), tensorMapAcquire(mapB);
+        const int batchA = g.entryMaps ? 0 : t.batch * g.batchMulA, batchB = g.entryMaps ? 0 : t.batch * g.batchMulB;
         const int ksEnd = int((long long)slices * (split + 1) / g.splits);
         for (int ks = int((long long)slices * split / g.splits); ks < ksEnd; ++ks) {
             if (!mbarWait(emptyBar + 8 * stage, phase ^ 1, abortFlag, kStatusProducerWait)) return;
@@ -781,6 +797,7 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                const __grid_constant__ CUtensorMap mapD, const __grid_constant__ MirrorMaps mirrors) {
     using Plan = SmemPlan<BN, PAIR, WIDE>;
     constexpr int kStages = Plan::kStages;
+    if (g.entryFlag && *g.entryFlag == g.entrySerial) return;  // an entry of the pointer-array batch is not fit for TMA: every CTA leaves at once
     extern __shared__ unsigned char smemRaw[];
     // the swizzled layout is defined on 1024-byte aligned addresses
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
@@ -874,6 +891,9 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
             const unsigned taddr = tmemBase + acc * BN + (unsigned(quarter * 32) << 16);
             const bool rowOk = row < g.m;
             const int rowInTile = quarter * 32 + lane;
+            const CUtensorMap* unitMapD = g.entryMaps ? g.entryMaps + 3 * t.batch + 2 : &mapD;
+            const int storeEntry = g.entryMaps ? 0 : t.batch;  // the batch coordinate of the bulk stores
+            if (g.entryMaps && issuer) tensorMapAcquire(unitMapD);
             // After a split along k: hand the accumulator over. True when this CTA goes on to write D; `splitBase` is then
             // set for the staged stores, which add the other splits' accumulators on their way, while for the direct
             // stores the sum has been put back into TMEM.
@@ -894,8 +914,8 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                 if (!handOver(staged, int(0))) {
                     // another split of this tile writes D
                 } else if (staged) {
-                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreS32, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
-                    else drainAccumulatorStaged<BN, kStoreS32, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
+                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreS32, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, storeEntry, unitMapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else drainAccumulatorStaged<BN, kStoreS32, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, storeEntry, unitMapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else {
                     drainAccumulator<BN>(epi, taddr, row, rowOk, col0, g.n, group);
                 }
@@ -909,20 +929,20 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
                 if (!handOver(staged, float(0))) {
                     // another split of this tile writes D
                 } else if (stagedPost && epi.typedMode == kStoreF32) {
-                    drainAccumulatorStagedPost<BN, kStoreF32, kBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
+                    drainAccumulatorStagedPost<BN, kStoreF32, kBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, storeEntry, unitMapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else if (stagedPost && epi.typedMode == kStoreF16) {
-                    drainAccumulatorStagedPost<BN, kStoreF16, kBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
+                    drainAccumulatorStagedPost<BN, kStoreF16, kBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, storeEntry, unitMapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else if (stagedPost && epi.typedMode == kStoreBF16) {
-                    drainAccumulatorStagedPost<BN, kStoreBF16, kBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
+                    drainAccumulatorStagedPost<BN, kStoreBF16, kBuffers>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, storeEntry, unitMapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else if (staged && epi.mode == kStoreF32) {
-                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF32, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
-                    else drainAccumulatorStaged<BN, kStoreF32, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
+                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF32, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, storeEntry, unitMapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else drainAccumulatorStaged<BN, kStoreF32, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, storeEntry, unitMapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else if (staged && epi.mode == kStoreF16) {
-                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF16, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
-                    else drainAccumulatorStaged<BN, kStoreF16, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
+                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreF16, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, storeEntry, unitMapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else drainAccumulatorStaged<BN, kStoreF16, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, storeEntry, unitMapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else if (staged && epi.mode == kStoreBF16) {
-                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreBF16, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
-                    else drainAccumulatorStaged<BN, kStoreBF16, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, t.batch, &mapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
+                    if (splitBase) drainAccumulatorStagedSplit<BN, kStoreBF16, 2>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, storeEntry, unitMapD, staging, storeStep, issuer, group, splitBase, g.splits, split);
+                    else drainAccumulatorStaged<BN, kStoreBF16, (WIDE ? kWideBuffers : 2)>(epi, taddr, rowInTile, row, rowOk, tileRow0, col0, g.n, storeEntry, unitMapD, &mirrors, g.mirrorCount, staging, storeStep, issuer, group);
                 } else {
                     drainAccumulator<BN>(epi, taddr, row, rowOk, col0, g.n, group);
                 }
@@ -949,6 +969,31 @@ ummaGemmKernel(const UmmaArgs g, const __grid_constant__ CUtensorMap mapA, const
         else
             asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(unsigned(Plan::kTmemCols)) : "memory");
     }
+}
+
+// Pointer-array batches: one thread per batch entry copies the launch's template maps (right shape, strides and boxes, a
+// placeholder address) to entryMaps[3 e ..] and puts the entry's own addresses in with tensormap.replace. An entry whose
+// pointers TMA cannot take (not 16-byte aligned; D only when the launch stores D through TMA) writes the launch's serial
+// number to the flag word instead.
+__global__ void buildEntryMaps(const __grid_constant__ CUtensorMap templateA, const __grid_constant__ CUtensorMap templateB,
+                               const __grid_constant__ CUtensorMap templateD, const void* const* A, const void* const* B, void* const* D, int batch,
+                               int storeThroughTma, CUtensorMap* entryMaps, unsigned* flag, unsigned serial) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= batch) return;
+    const unsigned long long a = reinterpret_cast<unsigned long long>(A[e]), b = reinterpret_cast<unsigned long long>(B[e]),
+                             d = reinterpret_cast<unsigned long long>(D[e]);
+    if ((a & 15) || (b & 15) || (storeThroughTma && (d & 15)) || !a || !b || !d) {
+        *flag = serial;  // this launch's own number: nothing else ever writes it, so the word is never cleared
+        return;
+    }
+    CUtensorMap* mine = entryMaps + 3 * e;
+    mine[0] = templateA, mine[1] = templateB, mine[2] = templateD;
+    __threadfence();
+    const auto setAddress = [](CUtensorMap* map, unsigned long long address) {
+        asm volatile("tensormap.replace.tile.global_address.global.b1024.b64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long>(map)), "l"(address) : "memory");
+    };
+    setAddress(mine, a), setAddress(mine + 1, b), setAddress(mine + 2, d);
+    asm volatile("fence.proxy.tensormap::generic.release.gpu;" ::: "memory");
 }
 
 // ---- host side ---------------------------------------------------------------------------------------------------
@@ -1100,9 +1145,18 @@ int pairClusters() {  // before the first launch has asked the device: half the 
 }  // namespace
 
 bool ummaEligible(const Problem& p) {
-    if (p.pointerArrays || p.k <= 0 || ummaKindOf(p) < 0) return false;
+    if (p.k <= 0 || ummaKindOf(p) < 0) return false;
     if (!deviceInfo().sm100 || !encodeTiled()) return false;
     const int es = elemSizeOf(p.typeA);
+    if (p.pointerArrays) {
+        // The matrices' addresses are in device memory and are checked there (buildEntryMaps). What the host can see must
+        // fit TMA, the entry maps need the handle's scratch memory, and the launch has to be worth its three kernels:
+        // below about 2^24 flop the CUDA-core kernel is as fast.
+        // (the caller then acquires that memory: 384 bytes per entry behind the counters; a batch too large for it stays
+        // on the CUDA cores)
+        return (p.lda * es) % 16 == 0 && (p.ldb * es) % 16 == 0 && size_t(p.batch) * 3 * sizeof(CUtensorMap) <= (size_t(32) << 20) &&
+               2.0 * p.m * p.n * p.k * p.batch >= double(1 << 24) && p.m >= 32 && p.n >= 16;
+    }
     const auto ok = [&](const void* ptr, long long ld, long long stride) {
         return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && (ld * es) % 16 == 0 &&
                (p.batch == 1 || stride == 0 || (stride * es) % 16 == 0);
@@ -1196,6 +1250,8 @@ UmmaPlan planUmma(const Problem& p, size_t scratchBytes) {
 bool ummaWantsScratch(const Problem& p, size_t scratchBytesOnOffer) { return planUmma(p, scratchBytesOnOffer).splits > 1; }
 
 cudaError_t launchUmma(const Problem& p) {
+    if (p.pointerArrays && (!p.scratch || p.scratchBytes < kSplitKCounters * sizeof(unsigned) + 256 + size_t(p.batch) * 3 * sizeof(CUtensorMap)))
+        return cudaErrorInvalidValue;  // the dispatch layer hands pointer-array batches over only with scratch memory for their maps
     const int kind = ummaKindOf(p);
     const int es = elemSizeOf(p.typeA);
     const UmmaPlan plan = planUmma(p, p.scratch ? p.scratchBytes : 0);
@@ -1232,9 +1288,17 @@ cudaError_t launchUmma(const Problem& p) {
     g.boxesA = g.mnMajorA ? kBM / g.boxElemsA : 1;
     const int ctaB = pair ? bn / 2 : bn;  // B rows one CTA stages
     g.boxesB = g.mnMajorB ? ctaB / g.boxElemsB : 1;
-    g.batchMulA = p.batch > 1 && p.strideA != 0;
-    g.batchMulB = p.batch > 1 && p.strideB != 0;
+    g.batchMulA = p.batch > 1 && p.strideA != 0 && !p.pointerArrays;
+    g.batchMulB = p.batch > 1 && p.strideB != 0 && !p.pointerArrays;
     g.epi = p.epi;
+    // Pointer arrays: the maps encoded here are templates (placeholder address: the scratch block, which is 256-byte aligned);
+    // buildEntryMaps makes one set per batch entry from them, in scratch memory behind the counters and the flag word.
+    unsigned* const entryFlag = p.pointerArrays ? static_cast<unsigned*>(p.scratch) + kSplitKCounters : nullptr;
+    CUtensorMap* const entryMaps = p.pointerArrays ? reinterpret_cast<CUtensorMap*>(static_cast<char*>(p.scratch) + kSplitKCounters * sizeof(unsigned) + 256) : nullptr;
+    const void* const baseA = p.pointerArrays ? p.scratch : p.A;
+    const void* const baseB = p.pointerArrays ? p.scratch : p.B;
+    void* const baseD = p.pointerArrays ? p.scratch : p.epi.D;
+    g.entryMaps = entryMaps, g.entryFlag = entryFlag, g.entrySerial = p.launchSerial;
 
     CUtensorMap mapA, mapB;
     const long long batchA = g.batchMulA ? p.batch : 1, batchB = g.batchMulB ? p.batch : 1;
@@ -1242,12 +1306,12 @@ cudaError_t launchUmma(const Problem& p) {
     g.chunkedA = g.mnMajorA && !noChunks && g.boxesA > 1 && p.m % g.boxElemsA == 0;
     g.chunkedB = g.mnMajorB && !noChunks && g.boxesB > 1 && p.n % g.boxElemsB == 0;
     // (a driver that refuses the 4-d view leaves the operand on its per-chunk boxes)
-    if (g.chunkedA && !encodeChunked(&mapA, p.A, p.typeA, p.m, p.k, p.lda, batchA, p.strideA, g.boxElemsA, g.sliceElems, g.boxesA)) g.chunkedA = 0;
-    if (g.chunkedB && !encodeChunked(&mapB, p.B, p.typeB, p.n, p.k, p.ldb, batchB, p.strideB, g.boxElemsB, g.sliceElems, g.boxesB)) g.chunkedB = 0;
-    const bool okA = g.chunkedA || (g.mnMajorA ? encodeOperand(&mapA, p.A, p.typeA, p.m, p.k, p.lda, batchA, p.strideA, g.boxElemsA, g.sliceElems)
-                                               : encodeOperand(&mapA, p.A, p.typeA, p.k, p.m, p.lda, batchA, p.strideA, g.sliceElems, kBM));
-    const bool okB = g.chunkedB || (g.mnMajorB ? encodeOperand(&mapB, p.B, p.typeB, p.n, p.k, p.ldb, batchB, p.strideB, g.boxElemsB, g.sliceElems)
-                                               : encodeOperand(&mapB, p.B, p.typeB, p.k, p.n, p.ldb, batchB, p.strideB, g.sliceElems, ctaB));
+    if (g.chunkedA && !encodeChunked(&mapA, baseA, p.typeA, p.m, p.k, p.lda, batchA, p.strideA, g.boxElemsA, g.sliceElems, g.boxesA)) g.chunkedA = 0;
+    if (g.chunkedB && !encodeChunked(&mapB, baseB, p.typeB, p.n, p.k, p.ldb, batchB, p.strideB, g.boxElemsB, g.sliceElems, g.boxesB)) g.chunkedB = 0;
+    const bool okA = g.chunkedA || (g.mnMajorA ? encodeOperand(&mapA, baseA, p.typeA, p.m, p.k, p.lda, batchA, p.strideA, g.boxElemsA, g.sliceElems)
+                                               : encodeOperand(&mapA, baseA, p.typeA, p.k, p.m, p.lda, batchA, p.strideA, g.sliceElems, kBM));
+    const bool okB = g.chunkedB || (g.mnMajorB ? encodeOperand(&mapB, baseB, p.typeB, p.n, p.k, p.ldb, batchB, p.strideB, g.boxElemsB, g.sliceElems)
+                                               : encodeOperand(&mapB, baseB, p.typeB, p.k, p.n, p.ldb, batchB, p.strideB, g.sliceElems, ctaB));
     if (!okA || !okB) return cudaErrorInvalidValue;
 
     // D through TMA when every address the bulk stores start at is 16-byte aligned; otherwise direct stores.
@@ -1257,28 +1321,36 @@ cudaError_t launchUmma(const Problem& p) {
     const int esD = dtypeSize(e.typeD);
     // TMA clips a store at the tensor's edge in units of 16 bytes, so a column length that is not a multiple of 16 bytes
     // would let it write into the padding between m and ldd: those shapes keep the direct stores too.
-    g.tmaStore = !e.pointerArrays && (reinterpret_cast<uintptr_t>(e.D) & 15) == 0 && (e.ldd * esD) % 16 == 0 && ((long long)p.m * esD) % 16 == 0 &&
-                 (p.batch == 1 || (e.strideD * esD) % 16 == 0) && (p.batch == 1 || e.strideD != 0);
+    g.tmaStore = (e.ldd * esD) % 16 == 0 && ((long long)p.m * esD) % 16 == 0 &&
+                 (e.pointerArrays || ((reinterpret_cast<uintptr_t>(e.D) & 15) == 0 && (p.batch == 1 || (e.strideD * esD) % 16 == 0) && (p.batch == 1 || e.strideD != 0)));
     if (measureKnob("VKZB_UMMA_DIRECT_STORE", 0)) g.tmaStore = 0;
     MirrorMaps mirrors{};
     g.mirrorCount = 0;
     if (g.tmaStore) {
         const CUtensorMapDataType dt = e.typeD == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : e.typeD == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                        : e.typeD == kS32 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-        const cuuint64_t dims[3] = {cuuint64_t(p.m), cuuint64_t(p.n), cuuint64_t(p.batch)};
-        const cuuint64_t strides[2] = {cuuint64_t(e.ldd) * esD, p.batch > 1 ? cuuint64_t(e.strideD) * esD : cuuint64_t(e.ldd) * esD * cuuint64_t(p.n)};
+        const cuuint64_t dims[3] = {cuuint64_t(p.m), cuuint64_t(p.n), cuuint64_t(e.pointerArrays ? 1 : p.batch)};
+        const cuuint64_t strides[2] = {cuuint64_t(e.ldd) * esD, p.batch > 1 && !e.pointerArrays ? cuuint64_t(e.strideD) * esD : cuuint64_t(e.ldd) * esD * cuuint64_t(p.n)};
         const cuuint32_t box[3] = {cuuint32_t(kBM), cuuint32_t(kStepCols), 1}, ones[3] = {1, 1, 1};
         const auto encode = [&](CUtensorMap* map, void* base) {
             return encodeTiled()(map, dt, 3, base, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
         };
-        if (!encode(&mapD, e.D)) g.tmaStore = 0;
+        if (!encode(&mapD, baseD)) g.tmaStore = 0;
         for (int q = 0; g.tmaStore && q < p.mirrorCount; ++q) {
             if (!encode(&mirrors.map[q], p.mirrorD[q])) return cudaErrorInvalidValue;
             g.mirrorCount = q + 1;
         }
     }
     if (p.mirrorCount > 0 && g.mirrorCount != p.mirrorCount) return cudaErrorInvalidValue;  // never skip mirrors silently
+
+    if (p.pointerArrays) {
+        if (!g.tmaStore) mapD = mapA;  // never used; the builder copies three maps whatever they hold
+        buildEntryMaps<<<(p.batch + 127) / 128, 128, 0, p.stream>>>(mapA, mapB, mapD, static_cast<const void* const*>(p.A), static_cast<const void* const*>(p.B),
+                                                                     static_cast<void* const*>(e.D), p.batch, g.tmaStore, entryMaps, entryFlag, p.launchSerial);
+        countLaunch();
+        if (cudaError_t err = cudaGetLastError(); err != cudaSuccess) return err;
+    }
 
     static const bool logChoice = [] { const char* v = std::getenv("VKZB_LOG"); return v && !std::strcmp(v, "debug"); }();
     if (logChoice)
@@ -1296,6 +1368,8 @@ cudaError_t launchUmma(const Problem& p) {
     if (bn == 128) return launchWith<128, false, false>(g, mapA, mapB, mapD, mirrors, 1, p.stream);
     return launchWith<64, false, false>(g, mapA, mapB, mapD, mirrors, 2, p.stream);
 }
+
+const unsigned* ummaEntryFlag(const Problem& p) { return p.pointerArrays && p.scratch ? static_cast<const unsigned*>(p.scratch) + kSplitKCounters : nullptr; }
 
 int ummaDeviceStatus() {
     unsigned status = 0;
