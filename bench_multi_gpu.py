@@ -35,7 +35,10 @@ import time
 import numpy as np
 
 
-def round_widths(n: int, ranks: int):
+def round_widths(n: int, ranks: int, forced: int = 0):
+    if forced:
+        assert (n // ranks) % forced == 0 and forced % 256 == 0, "--chunk-columns must be a multiple of 256 that divides a rank's share"
+        return [forced] * (n // ranks // forced)
     return default_round_widths(n, ranks)
 
 
@@ -214,10 +217,10 @@ def run(args):
     # 6.0 ms product, measured 9.1 ms fused against 8.3 ms chunk-pipelined), while the copy engines behind ncclAllGather
     # reach 700 GB/s; below that (2 and 4 GPUs) the fused form wins because nothing is left over at the end of the step.
     link_share = (4.0 * m * n * (world - 1) / world / 770e9) / (2.0 * m * n * k / world / 1.45e15) if world > 1 else 0.0
-    fused = world > 1 and link_share < 0.6
+    fused = world > 1 and (args.gather == "fused" or (args.gather == "auto" and link_share < 0.6))
     # (fused: 2048 columns per call. One call over a rank's whole share ran a quarter slower at 2 GPUs: over tens of
     # milliseconds the CTAs of one persistent kernel drift apart along k and stop finding each other's operand slices in L2.)
-    rounds = column_chunks(n, world, None)
+    rounds = column_chunks(n, world, round_widths(n, world, getattr(args, "chunk_columns", 0)))
     if fused:
         per_rank, w = n // world, min(2048, n // world)
         rounds = [(j, w, None, [r * per_rank + j * w for r in range(world)]) for j in range(per_rank // w)]
@@ -295,6 +298,35 @@ def run(args):
     clocks = sampler.stop(t0, t1) if sampler else None
     launches = lt.launch_count() - launches0
     assert comm.async_error() == 0, "a device-side barrier of the gather gave up"
+
+    if getattr(args, "timeline", False) and world > 1 and not fused:
+        # one more step with an event around every round's product and gather: where the step's time goes (rank 0, stderr)
+        marks = {"g0": [], "g1": [], "c0": [], "c1": []}
+        dist.barrier()
+        torch.cuda.synchronize()
+        origin = torch.cuda.Event(enable_timing=True)
+        origin.record(compute)
+        gather.wait_event(origin)
+        for j, w, round_first, firsts in rounds:
+            mine = D.data_ptr() + 4 * firsts[rank] * m
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record(compute)
+            lt.matmul(capi.OP_T, capi.OP_N, m, w, k, 1.0, A.data_ptr(), bf16, k, Bmine.data_ptr() + 2 * b_offset[j], bf16, k, 0.0, mine, f32, m, mine, f32, m,
+                      stream=compute.cuda_stream)
+            ev[1].record(compute)
+            gather.wait_event(ev[1])
+            ev[2].record(gather)
+            comm.all_gather(mine, D.data_ptr() + 4 * round_first * m, w * m, "float32", gather.cuda_stream)
+            ev[3].record(gather)
+            for key, e in zip(("c0", "c1", "g0", "g1"), ev):
+                marks[key].append(e)
+        compute.wait_stream(gather)
+        torch.cuda.synchronize()
+        if rank == 0:
+            import sys
+            rows_t = [{"round": j, "product_ms": [round(origin.elapsed_time(marks["c0"][j]), 3), round(origin.elapsed_time(marks["c1"][j]), 3)],
+                       "gather_ms": [round(origin.elapsed_time(marks["g0"][j]), 3), round(origin.elapsed_time(marks["g1"][j]), 3)]} for j in range(len(rounds))]
+            print(json.dumps({"timeline": rows_t}), file=sys.stderr, flush=True)
 
     # Parity, outside the timed region: a sample of D on EVERY rank (each holds all of D after the step) against the fp64
     # oracle, with operands regenerated on the host by the numpy form of the generator: rows spread over the matrix, and
