@@ -158,3 +158,29 @@ def gemm_s8(ta, tb, m, n, k, batch, alpha, A, lda, stride_a, B, ldb, stride_b, b
     oracle().oracle_gemm_s8(int(ta), int(tb), m, n, k, batch, int(alpha), _ptr(A), lda, stride_a, _ptr(B), ldb, stride_b, int(beta),
                             _ptr(Cm), ldc, stride_c)
     return Cm
+
+
+def attention_fp64(q, k, v, scale, mask):
+    """softmax(scale q k^T + mask) v and its logsumexp in fp64, as the reference's own test computes what it expects
+    (tests/attention.cpp:190-228): q is [batches, heads, numQ, dim], k and v [batches, kvHeads, numK, dim]; query head h reads
+    head h // (heads // kvHeads); mask 1 hides key j from query i when j > i, mask 2 when j > i + numK - numQ; a row that sees
+    no key gives zeros and a logsumexp of 0."""
+    q, k, v = (np.asarray(x, dtype=np.float64) for x in (q, k, v))
+    batches, heads, num_q, _ = q.shape
+    kv_heads, num_k = k.shape[1], k.shape[2]
+    group = heads // kv_heads
+    out = np.zeros(q.shape[:3] + (v.shape[3],))
+    lse = np.zeros(q.shape[:3])
+    diag = num_k - num_q if mask == 2 else 0
+    hidden = (np.arange(num_k)[None, :] > np.arange(num_q)[:, None] + diag) if mask else np.zeros((num_q, num_k), dtype=bool)
+    for b in range(batches):
+        for h in range(heads):
+            s = scale * (q[b, h] @ k[b, h // group].T)
+            s[hidden] = -np.inf
+            mx = s.max(axis=1, initial=-np.inf)
+            seen = np.isfinite(mx)
+            e = np.where(np.isfinite(s), np.exp(s - np.where(seen, mx, 0.0)[:, None]), 0.0)
+            total = e.sum(axis=1)
+            out[b, h][seen] = (e @ v[b, h // group])[seen] / total[seen, None]
+            lse[b, h][seen] = mx[seen] + np.log(total[seen])
+    return out, lse

@@ -18,7 +18,7 @@ ROOT = Path(__file__).resolve().parents[1]
 
 def test_cublas_exports_every_declared_symbol():
     lib = vk.cublas_library()
-    for name in vk.declared_symbols("vkzb_cublas.h") + vk.declared_symbols("vkzb_ext.h"):
+    for name in vk.declared_symbols("vkzb_cublas.h") + vk.declared_symbols("vkzb_ext.h") + vk.declared_symbols("vkzb_attention.h"):
         assert hasattr(lib, name), name
 
 

@@ -158,3 +158,23 @@ def test_synthetic_generator_has_the_same_values_on_a_torch_device():
     out = torch.empty(1000, dtype=torch.bfloat16)
     synth.fill_normal_torch(torch, out, 5, 1.0, first=77, block=256)
     assert np.array_equal(out.view(torch.int16).numpy().view(np.uint16), orc.to_storage(synth.normal(5, 1000, 1.0, first=77), "bf16"))
+
+
+def test_attention_oracle_against_plain_loops():
+    """attention_fp64 against the loop form of the reference's own expected-value computation (tests/attention.cpp:190-228) on a
+    case small enough for pure Python: both masks, grouped heads, a row that sees no key."""
+    rng = np.random.default_rng(3)
+    batches, heads, kv_heads, num_q, num_k, dim = 1, 2, 1, 5, 3, 4
+    q, k, v = rng.standard_normal((batches, heads, num_q, dim)), rng.standard_normal((batches, kv_heads, num_k, dim)), rng.standard_normal((batches, kv_heads, num_k, dim))
+    for mask in (0, 1, 2):
+        out, lse = orc.attention_fp64(q, k, v, 0.5, mask)
+        diag = num_k - num_q if mask == 2 else 0
+        for h in range(heads):
+            for i in range(num_q):
+                s = [0.5 * float(q[0, h, i] @ k[0, 0, j]) if not (mask and j > i + diag) else -math.inf for j in range(num_k)]
+                mx = max(s)
+                e = [0.0 if math.isinf(x) else math.exp(x - mx) for x in s]
+                total = sum(e)
+                want = sum(e[j] * v[0, 0, j] for j in range(num_k)) / total if total else np.zeros(dim)
+                assert np.allclose(out[0, h, i], want, rtol=1e-12, atol=1e-12)
+                assert abs(lse[0, h, i] - (mx + math.log(total) if total else 0.0)) < 1e-12

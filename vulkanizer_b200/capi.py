@@ -71,6 +71,12 @@ _cublaslt = None
 _vp, _i, _ll, _sz = C.c_void_p, C.c_int, C.c_longlong, C.c_size_t
 
 
+class AttentionProblem(C.Structure):
+    """vkzbAttentionProblem of include/vkzb_attention.h."""
+    _fields_ = ([(n, _i) for n in ("dataType", "batches", "heads", "kvHeads", "numQ", "numK", "headDim", "mask")] + [("scale", C.c_float)] +
+                [f for t in "qkvo" for f in ((t, _vp), (t + "Row", _ll), (t + "Head", _ll), (t + "Batch", _ll))] + [("logSumExp", _vp)])
+
+
 def cublas_library() -> C.CDLL:
     global _cublas
     if _cublas is None:
@@ -129,8 +135,19 @@ def cublas_library() -> C.CDLL:
         lib.vkzbSetOutputMirrors.argtypes, lib.vkzbSetOutputMirrors.restype = [_vp, _vp, _sz, _i, C.POINTER(_vp)], _i
         lib.vkzbSgemmStaticScratch.argtypes = [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _i]
         lib.vkzbSgemmStaticScratch.restype = _i
+        lib.vkzbAttentionForward.argtypes, lib.vkzbAttentionForward.restype = [_vp, C.POINTER(AttentionProblem)], _i
+        lib.vkzbAttentionStatus.argtypes, lib.vkzbAttentionStatus.restype = [], _i
         _cublas = lib
     return _cublas
+
+
+def attention_forward(stream, data_type, batches, heads, kv_heads, num_q, num_k, head_dim, mask, scale, q, q_strides, k, k_strides, v, v_strides,
+                      o, o_strides, log_sum_exp=None) -> int:
+    """vkzbAttentionForward (include/vkzb_attention.h): O = softmax(scale Q K^T + mask) V on device pointers. Each *_strides is
+    (row, head, batch) in elements. Returns the status; raises nothing, so tests can check refusals."""
+    a = AttentionProblem(data_type, batches, heads, kv_heads, num_q, num_k, head_dim, mask, scale, q, *q_strides, k, *k_strides, v, *v_strides,
+                         o, *o_strides, log_sum_exp)
+    return cublas_library().vkzbAttentionForward(stream, C.byref(a))
 
 
 def cublaslt_library() -> C.CDLL:

@@ -1,0 +1,487 @@
+// vkzbAttentionForward: O = softmax(scale Q K^T + mask) V in one kernel, for f16 / bf16 and head dimensions 64 and 128.
+//
+// What it replaces: the batched product Q K^T (the benchmark's batched-attention shape) writes batch x numQ x numK scores to
+// memory (1 GiB of fp32 for 256 heads of 1024 x 1024), a softmax pass reads and writes them again and a second batched
+// product reads them a third time. Here a CTA owns 128 queries of one head and walks the keys in tiles of 128: the scores
+// of a tile live in tensor memory only, the probabilities go through shared memory into the second product, and what
+// reaches HBM is Q, K, V once (K and V once per query tile, from L2) and O.
+//
+// Roles in a CTA of 192 threads (same scheme as the GEMM kernel of k_umma.cu):
+//   warp 0      one lane issues the TMA loads: the Q tile once, then K and V tiles through a two-stage ring;
+//   warp 1      one elected lane issues tcgen05.mma: S = Q K_j^T into tensor memory, and, when the probabilities of the
+//               tile are in shared memory, O += P_j V_j into a second range of tensor-memory columns;
+//   warps 2-5   one thread per query row: read the row of S, keep the running maximum and sum (the online softmax of
+//               Milakov and Gimelshein, as used by FlashAttention), write P_j as 16-bit values in the swizzled layout the
+//               tensor cores read, rescale the row of O when its maximum moved, and at the end divide by the sum and store.
+// Every wait is bounded: a wait that runs out records a code in g_attentionStatus, raises the CTA's abort flag and all
+// roles leave through the common exit, which frees the tensor memory.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <mutex>
+#include <type_traits>
+
+#include "../../include/vkzb_attention.h"
+#include "gemm_problem.h"
+
+namespace vkzb {
+namespace {
+
+constexpr int kTileQ = 128;                 // queries per CTA = TMEM lanes
+constexpr int kTileK = 128;                 // keys per step
+constexpr int kAttnThreads = 192;
+constexpr int kAtomBytes = 128 * 128;       // 128 rows of one 128-byte swizzle span
+constexpr int kVBoxBytes = 64 * 128;        // 64 keys x 64 values of V
+constexpr unsigned long long kAttnWaitLimitNs = 4000000000ull;
+constexpr unsigned kTmemColumns = 256;      // S: columns 0-127, O: columns 128-255
+
+enum : unsigned { kAttnOk = 0, kAttnProducerWait = 33, kAttnMmaWait = 34, kAttnSoftmaxWait = 35 };
+__device__ unsigned g_attentionStatus;
+
+struct AttentionArgs {
+    int numQ, numK, heads, kvGroup;
+    int mask;            // 0 none, 1 causal from the top left, 2 from the bottom right
+    float scaleLog2;     // scale * log2(e): the exponentials are taken in base 2
+    void* o;
+    long long oRow, oHead, oBatch;
+    float* logSumExp;    // [batch][head][numQ], or null
+    unsigned idescS, idescO;
+};
+
+// ---- PTX wrappers (the same instructions as in k_umma.cu; this file is a translation unit of its own) -----------------
+
+__device__ __forceinline__ unsigned smemAddr(const void* p) { return unsigned(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbarInit(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbarArriveExpectTx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbarArrive(unsigned bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ bool mbarTryWait(unsigned bar, unsigned parity) {
+    unsigned done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ unsigned long long globalTimerNs() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// False when the CTA is aborting or the wait ran out of time (the code is then recorded and the abort flag raised).
+__device__ __noinline__ bool mbarWaitSlow(unsigned bar, unsigned parity, volatile int* abortFlag, unsigned code) {
+    const unsigned long long start = globalTimerNs();
+    for (unsigned spins = 0;; ++spins) {
+        if (mbarTryWait(bar, parity)) return true;
+        if ((spins & 63u) == 63u) {
+            if (*abortFlag) return false;
+            if (globalTimerNs() - start > kAttnWaitLimitNs) {
+                atomicCAS(&g_attentionStatus, kAttnOk, code);
+                *abortFlag = 1;
+                __threadfence_block();
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbarWait(unsigned bar, unsigned parity, volatile int* abortFlag, unsigned code) {
+    if (mbarTryWait(bar, parity)) return true;
+    return mbarWaitSlow(bar, parity, abortFlag, code);
+}
+__device__ __forceinline__ void tmaLoad4d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ bool electOne() {
+    unsigned elected;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+    return elected != 0;
+}
+__device__ __forceinline__ void tcgen05FenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05FenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05Commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mmaF16(unsigned tmemD, unsigned long long descA, unsigned long long descB, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// Generic-proxy writes to shared memory before, asynchronous-proxy reads (the tensor cores') after.
+__device__ __forceinline__ void fenceAsyncShared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// 32 lanes x 32 columns of 32-bit cells: thread i of the warp receives row i.
+__device__ __forceinline__ void tmemLoad32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmemStore32(unsigned taddr, const unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+        "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+        "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float exp2Approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+template <bool BF16>
+__device__ __forceinline__ unsigned packPair(float lo, float hi) {
+    if constexpr (BF16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const unsigned*>(&v);
+    } else {
+        const __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const unsigned*>(&v);
+    }
+}
+
+// Shared-memory plan for head dimension D (elements of 2 bytes). Q and K tiles: D / 64 atoms of 128 rows x 128 bytes
+// (64 values of the head dimension per row: the K-major operand layout under the 128-byte swizzle). V tiles: the
+// head dimension is the contiguous one and is the N side of the second product, so V is staged as boxes of 64 keys x 64
+// values, ordered [half of the keys][chunk of the head dimension]. P: two atoms of 128 rows x 64 keys.
+template <int D>
+struct AttnPlan {
+    static constexpr int kAtoms = D / 64;
+    static constexpr int kQBytes = kAtoms * kAtomBytes;
+    static constexpr int kKBytes = kQBytes;
+    static constexpr int kVBytes = 2 * kAtoms * kVBoxBytes;
+    static constexpr int kPBytes = 2 * kAtomBytes;
+    static constexpr int kOffK = kQBytes;
+    static constexpr int kOffV = kOffK + 2 * kKBytes;
+    static constexpr int kOffP = kOffV + 2 * kVBytes;
+    static constexpr int kOffBars = kOffP + kPBytes;
+    static constexpr int kSmemBytes = kOffBars + 128 + 1024;  // barriers and flags; slack to align the base to 1024 bytes
+};
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                const __grid_constant__ CUtensorMap mapV) {
+    using Plan = AttnPlan<D>;
+    constexpr int kAtoms = Plan::kAtoms;
+    extern __shared__ unsigned char smemRaw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + Plan::kOffBars);
+    // bars: 0 Q loaded; 1-2 K/V stage loaded; 3-4 K/V stage read; 5 S ready; 6 P ready (and S read); 7 O updated
+    unsigned* tmemSlot = reinterpret_cast<unsigned*>(bars + 8);
+    volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const unsigned base = smemAddr(smem);
+    const unsigned barQ = smemAddr(bars), barKvFull = barQ + 8, barKvEmpty = barQ + 24, barS = barQ + 40, barP = barQ + 48, barO = barQ + 56;
+    const int q0 = blockIdx.x * kTileQ, head = blockIdx.y, batch = blockIdx.z;
+    const int kvHead = head / g.kvGroup;
+    // keys a query may see: index <= query + diag
+    const int diag = g.mask == 2 ? g.numK - g.numQ : 0;
+    const int lastQuery = min(q0 + kTileQ, g.numQ) - 1;
+    const int keysInReach = g.mask ? max(0, min(g.numK, lastQuery + diag + 1)) : g.numK;
+    const int tiles = (keysInReach + kTileK - 1) / kTileK;
+
+    if (threadIdx.x == 0) {
+        mbarInit(barQ, 1);
+        for (int s = 0; s < 2; ++s) mbarInit(barKvFull + 8 * s, 1), mbarInit(barKvEmpty + 8 * s, 1);
+        mbarInit(barS, 1);
+        mbarInit(barP, 4);  // one arrival per softmax warp
+        mbarInit(barO, 1);
+        *abortFlag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fenceAsyncShared();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(tmemSlot)), "r"(kTmemColumns) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05FenceBefore();
+    __syncthreads();
+    tcgen05FenceAfter();
+    const unsigned tmemBase = *tmemSlot;
+    const unsigned tmemS = tmemBase, tmemO = tmemBase + 128;
+
+    if (warp == 0) {
+        // ---- TMA producer ----
+        if (lane == 0 && tiles > 0) {
+            mbarArriveExpectTx(barQ, Plan::kQBytes);
+            for (int a = 0; a < kAtoms; ++a) tmaLoad4d(base + a * kAtomBytes, &mapQ, barQ, 64 * a, q0, head, batch);
+            for (int j = 0; j < tiles; ++j) {
+                const int stage = j & 1;
+                if (!mbarWait(barKvEmpty + 8 * stage, ((j >> 1) & 1) ^ 1, abortFlag, kAttnProducerWait)) break;
+                const unsigned bar = barKvFull + 8 * stage;
+                mbarArriveExpectTx(bar, Plan::kKBytes + Plan::kVBytes);
+                const unsigned dstK = base + Plan::kOffK + stage * Plan::kKBytes, dstV = base + Plan::kOffV + stage * Plan::kVBytes;
+                const int k0 = j * kTileK;
+                for (int a = 0; a < kAtoms; ++a) tmaLoad4d(dstK + a * kAtomBytes, &mapK, bar, 64 * a, k0, kvHead, batch);
+                for (int half = 0; half < 2; ++half)
+                    for (int c = 0; c < kAtoms; ++c)
+                        tmaLoad4d(dstV + (half * kAtoms + c) * kVBoxBytes, &mapV, bar, 64 * c, k0 + 64 * half, kvHead, batch);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        // shared-memory descriptors: stride offset 1024 bytes (8 rows of 128 bytes), version 1, 128-byte swizzle; the leading
+        // offset is unused for K-major operands (1) and the distance between 64-value chunks for V
+        const unsigned long long hi = static_cast<unsigned long long>((1024u >> 4) | 1u << 14 | 2u << 29) << 32;
+        const auto desc = [&](unsigned addr, unsigned lbo) { return hi | (((addr & 0x3FFFFu) >> 4) | lbo << 16); };
+        // the whole warp takes every decision together: a wait that gave up in one lane ends the loop for all
+        const auto waitAll = [&](unsigned bar, unsigned parity) { return __all_sync(0xFFFFFFFFu, mbarWait(bar, parity, abortFlag, kAttnMmaWait)) != 0; };
+        bool ok = tiles == 0 || waitAll(barQ, 0);
+        for (int j = 0; ok && j < tiles; ++j) {
+            const int stage = j & 1;
+            if (!(ok = waitAll(barKvFull + 8 * stage, (j >> 1) & 1))) break;
+            tcgen05FenceAfter();
+            if (electOne()) {
+                // S = Q K^T: the previous tile's probabilities were announced, so S has been read
+#pragma unroll
+                for (int a = 0; a < kAtoms; ++a) {
+                    const unsigned long long dq = desc(base + a * kAtomBytes, 1), dk = desc(base + Plan::kOffK + stage * Plan::kKBytes + a * kAtomBytes, 1);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) mmaF16(tmemS, dq + 2 * q, dk + 2 * q, g.idescS, (a | q) ? 1u : 0u);
+                }
+                tcgen05Commit(barS);
+            }
+            __syncwarp();
+            if (!(ok = waitAll(barP, j & 1))) break;
+            tcgen05FenceAfter();
+            if (electOne()) {
+                // O += P V: 16 keys per instruction, 64 keys per atom of P and per half of the V stage
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const unsigned long long dp = desc(base + Plan::kOffP + half * kAtomBytes, 1);
+                    const unsigned long long dv = desc(base + Plan::kOffV + stage * Plan::kVBytes + half * kAtoms * kVBoxBytes, kVBoxBytes >> 4);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) mmaF16(tmemO, dp + 2 * q, dv + q * (2048 >> 4), g.idescO, (j | half | q) ? 1u : 0u);
+                }
+                tcgen05Commit(barKvEmpty + 8 * stage);
+                tcgen05Commit(barO);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ---- softmax and output: one thread per query ----
+        const int quarter = warp % 4;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31
+        const int rowInTile = quarter * 32 + lane, query = q0 + rowInTile;
+        const unsigned laneBits = unsigned(quarter * 32) << 16;
+        const int visible = g.mask ? max(0, min(g.numK, query + diag + 1)) : g.numK;  // keys [0, visible) count for this row
+        const float c = g.scaleLog2;
+        float runMax = -INFINITY, runSum = 0.f;
+        unsigned char* sP = smem + Plan::kOffP;
+        // tcgen05.ld and .st are warp-wide: the warp takes every decision together
+        const auto waitAll = [&](unsigned bar, unsigned parity) { return __all_sync(0xFFFFFFFFu, mbarWait(bar, parity, abortFlag, kAttnSoftmaxWait)) != 0; };
+        bool ok = true;
+        for (int j = 0; j < tiles; ++j) {
+            if (!(ok = waitAll(barS, j & 1))) break;
+            tcgen05FenceAfter();
+            const int limit = visible - j * kTileK;  // columns [0, limit) of this tile count
+            unsigned v[32];
+            float tileMax = -INFINITY;
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk) {
+                tmemLoad32(tmemS + laneBits + 32 * chunk, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (chunk * 32 + i < limit) tileMax = fmaxf(tileMax, __uint_as_float(v[i]) * c);
+            }
+            const float newMax = fmaxf(runMax, tileMax);
+            const float shift = newMax == -INFINITY ? 0.f : newMax;  // a row that has seen no key yet
+            const float correction = exp2Approx(runMax - shift);     // 0 for the first keys of a row
+            runMax = newMax;
+            // the previous tile's P V has read P and updated O
+            if (j > 0 && !(ok = waitAll(barO, (j - 1) & 1))) break;
+            tcgen05FenceAfter();
+            float tileSum = 0.f;
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk) {
+                tmemLoad32(tmemS + laneBits + 32 * chunk, v);
+                unsigned packed[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int col = chunk * 32 + 2 * i;
+                    const float p0 = col < limit ? exp2Approx(fmaf(__uint_as_float(v[2 * i]), c, -shift)) : 0.f;
+                    const float p1 = col + 1 < limit ? exp2Approx(fmaf(__uint_as_float(v[2 * i + 1]), c, -shift)) : 0.f;
+                    tileSum += p0 + p1;
+                    packed[i] = packPair<BF16>(p0, p1);
+                }
+                // 16-byte pieces of this row: piece (4 chunk + t) of 16 sits in atom (piece / 8), at position (piece % 8) ^ (row % 8)
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const int piece = 4 * chunk + t;
+                    uint4* dst = reinterpret_cast<uint4*>(sP + (piece / 8) * kAtomBytes + rowInTile * 128 + (((piece % 8) ^ (rowInTile & 7)) * 16));
+                    *dst = make_uint4(packed[4 * t], packed[4 * t + 1], packed[4 * t + 2], packed[4 * t + 3]);
+                }
+            }
+            runSum = runSum * correction + tileSum;
+            if (j > 0 && !__all_sync(0xFFFFFFFFu, correction == 1.f)) {
+#pragma unroll
+                for (int chunk = 0; chunk < D / 32; ++chunk) {
+                    tmemLoad32(tmemO + laneBits + 32 * chunk, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * correction);
+                    tmemStore32(tmemO + laneBits + 32 * chunk, v);
+                }
+            }
+            tcgen05FenceBefore();
+            fenceAsyncShared();
+            __syncwarp();
+            if (lane == 0) mbarArrive(barP);
+        }
+        if (ok && tiles > 0) ok = waitAll(barO, (tiles - 1) & 1);
+        tcgen05FenceAfter();
+        if (ok) {
+            using Elem = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+            Elem* out = reinterpret_cast<Elem*>(g.o) + (size_t(batch) * g.oBatch + size_t(head) * g.oHead + size_t(query) * g.oRow);
+            const float inverse = runSum > 0.f ? 1.f / runSum : 0.f;
+#pragma unroll
+            for (int chunk = 0; chunk < D / 32; ++chunk) {
+                unsigned v[32];
+                if (tiles > 0) {
+                    tmemLoad32(tmemO + laneBits + 32 * chunk, v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0u;
+                }
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    unsigned w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        w[i] = packPair<BF16>(__uint_as_float(v[8 * t + 2 * i]) * inverse, __uint_as_float(v[8 * t + 2 * i + 1]) * inverse);
+                    if (query < g.numQ) *reinterpret_cast<uint4*>(out + chunk * 32 + t * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            if (g.logSumExp && query < g.numQ)  // natural logarithm of the sum of exp(score); 0 for a row without visible keys
+                g.logSumExp[(size_t(batch) * g.heads + head) * g.numQ + query] = runSum > 0.f ? (runMax + log2f(runSum)) * 0.6931471805599453f : 0.f;
+        }
+    }
+
+    // ---- common exit ----
+    if (*abortFlag) __nanosleep(20000);  // let copies still in flight land before the shared memory is released
+    tcgen05FenceBefore();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05FenceAfter();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(kTmemColumns) : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encodeTiled() {
+    static const EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// (value of the head dimension, position in the sequence, head, batch entry); strides in elements.
+bool encodeSequence(CUtensorMap* map, const void* base, bool bf16, int headDim, int length, int heads, int batches, long long row, long long head,
+                    long long batch, unsigned boxRows) {
+    const cuuint64_t dims[4] = {cuuint64_t(headDim), cuuint64_t(length), cuuint64_t(heads), cuuint64_t(batches)};
+    // a dimension of extent 1 still needs a legal stride (a multiple of 16 bytes): its value is never used
+    const cuuint64_t strides[3] = {cuuint64_t(row) * 2, heads > 1 ? cuuint64_t(head) * 2 : cuuint64_t(row) * 2, batches > 1 ? cuuint64_t(batch) * 2 : cuuint64_t(row) * 2};
+    const cuuint32_t box[4] = {64, boxRows, 1, 1};
+    const cuuint32_t elemStrides[4] = {1, 1, 1, 1};
+    return encodeTiled()(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box,
+                         elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D, bool BF16>
+cudaError_t launchAttention(const AttentionArgs& g, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, dim3 grid, cudaStream_t stream) {
+    static std::mutex mutex;
+    static bool attributeSet[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    device = device < 0 || device >= 64 ? 0 : device;
+    {
+        std::lock_guard<std::mutex> lock(mutex);
+        if (!attributeSet[device]) {
+            const cudaError_t e = cudaFuncSetAttribute(attentionKernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnPlan<D>::kSmemBytes);
+            if (e != cudaSuccess) return e;
+            attributeSet[device] = true;
+        }
+    }
+    attentionKernel<D, BF16><<<grid, kAttnThreads, AttnPlan<D>::kSmemBytes, stream>>>(g, mq, mk, mv);
+    countLaunch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+}  // namespace vkzb
+
+extern "C" __attribute__((visibility("default"))) int vkzbAttentionForward(cudaStream_t stream, const vkzbAttentionProblem* a) {
+    using namespace vkzb;
+    enum { kSuccess = 0, kNotInitialized = 1, kInvalidValue = 7, kExecutionFailed = 13, kNotSupported = 15 };  // cublasStatus_t values
+    if (!a || a->batches < 0 || a->heads < 0 || a->kvHeads <= 0 || a->numQ < 0 || a->numK < 0 || unsigned(a->mask) > 2u) return kInvalidValue;
+    if (a->heads % a->kvHeads) return kInvalidValue;
+    if (a->dataType != 2 /* CUDA_R_16F */ && a->dataType != 14 /* CUDA_R_16BF */) return kNotSupported;
+    if (a->headDim != 64 && a->headDim != 128) return kNotSupported;
+    if (a->batches == 0 || a->heads == 0 || a->numQ == 0) return kSuccess;
+    if (!a->q || !a->k || !a->v || !a->o) return kInvalidValue;
+    if (a->heads > 65535 || a->batches > 65535) return kNotSupported;
+    // TMA and the 16-byte stores of O: every base and every stride a multiple of 16 bytes
+    const long long strides[] = {a->qRow, a->qHead, a->qBatch, a->kRow, a->kHead, a->kBatch, a->vRow, a->vHead, a->vBatch, a->oRow, a->oHead, a->oBatch};
+    for (long long s : strides)
+        if (s < 0 || s % 8) return kNotSupported;
+    if (a->qRow < a->headDim || a->kRow < a->headDim || a->vRow < a->headDim || a->oRow < a->headDim) return kInvalidValue;
+    for (const void* p : {a->q, a->k, a->v, static_cast<const void*>(a->o)})
+        if (reinterpret_cast<uintptr_t>(p) % 16) return kNotSupported;
+    if (!encodeTiled()) return kNotInitialized;
+    const bool bf16 = a->dataType == 14;
+    const int numK = a->numK;
+    CUtensorMap mq, mk, mv;
+    // with no keys the kernel loads nothing; the maps still have to describe some memory, so they get extent 1
+    if (!encodeSequence(&mq, a->q, bf16, a->headDim, a->numQ, a->heads, a->batches, a->qRow, a->qHead, a->qBatch, kTileQ) ||
+        !encodeSequence(&mk, a->k, bf16, a->headDim, numK > 0 ? numK : 1, a->kvHeads, a->batches, a->kRow, a->kHead, a->kBatch, kTileK) ||
+        !encodeSequence(&mv, a->v, bf16, a->headDim, numK > 0 ? numK : 1, a->kvHeads, a->batches, a->vRow, a->vHead, a->vBatch, 64))
+        return kNotSupported;
+    AttentionArgs g{};
+    g.numQ = a->numQ, g.numK = numK, g.heads = a->heads, g.kvGroup = a->heads / a->kvHeads;
+    g.mask = a->mask;
+    g.scaleLog2 = a->scale * 1.4426950408889634f;
+    g.o = a->o, g.oRow = a->oRow, g.oHead = a->oHead, g.oBatch = a->oBatch;
+    g.logSumExp = a->logSumExp;
+    const unsigned format = bf16 ? 1u : 0u;
+    // accumulate in f32; A and B in `format`; M = 128; S: N = 128 keys, both operands K-major; O: N = head dimension, B (V) N-major
+    g.idescS = 1u << 4 | format << 7 | format << 10 | unsigned(kTileK >> 3) << 17 | unsigned(kTileQ >> 4) << 24;
+    g.idescO = 1u << 4 | format << 7 | format << 10 | 1u << 16 | unsigned(a->headDim >> 3) << 17 | unsigned(kTileQ >> 4) << 24;
+    const dim3 grid(unsigned((a->numQ + kTileQ - 1) / kTileQ), unsigned(a->heads), unsigned(a->batches));
+    cudaError_t e;
+    if (a->headDim == 128) e = bf16 ? launchAttention<128, true>(g, mq, mk, mv, grid, stream) : launchAttention<128, false>(g, mq, mk, mv, grid, stream);
+    else e = bf16 ? launchAttention<64, true>(g, mq, mk, mv, grid, stream) : launchAttention<64, false>(g, mq, mk, mv, grid, stream);
+    return e == cudaSuccess ? kSuccess : kExecutionFailed;
+}
+
+extern "C" __attribute__((visibility("default"))) int vkzbAttentionStatus(void) {
+    unsigned status = 0;
+    if (cudaMemcpyFromSymbol(&status, vkzb::g_attentionStatus, sizeof status) != cudaSuccess) return -1;
+    return int(status);
+}
