@@ -494,13 +494,153 @@ def run_single_gpu(args):
     blas.destroy()
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# GPU arm, one GPU: the fused attention that follows configuration 4's Q K^T (vkzbAttentionForward)
+# ---------------------------------------------------------------------------------------------------------------------
+
+ATTENTION_WORKLOADS = {
+    # configuration 4's operands (256 heads of 1024 queries and keys, head dimension 128, f16) with a V of the same shape
+    "f4_attention_f16_256x1024x1024x128": dict(ab="f16", heads=256, num_q=1024, num_k=1024, dim=128, mask=0, dist=("normal", 1.0), seed=3, bound="tensor"),
+    "f4_attention_f16_256x1024x1024x128_causal": dict(ab="f16", heads=256, num_q=1024, num_k=1024, dim=128, mask=1, dist=("normal", 1.0), seed=3, bound="tensor"),
+    "f4_attention_bf16_64x4096x4096x128": dict(ab="bf16", heads=64, num_q=4096, num_k=4096, dim=128, mask=0, dist=("normal", 1.0), seed=3, bound="tensor"),
+    # a few heads for profiler captures
+    "profile_attention_f16_64x1024x1024x128": dict(ab="f16", heads=64, num_q=1024, num_k=1024, dim=128, mask=0, dist=("normal", 1.0), seed=3, bound="tensor"),
+}
+
+
+def run_attention(args):
+    """One step = one vkzbAttentionForward over all heads. FLOPs counted: 4 numQ numK dim per head (half of that under the
+    causal mask), the two products only. The check against the fp64 oracle runs on one head, outside the timed region."""
+    import numpy as np
+    import torch
+    from vulkanizer_b200 import capi
+
+    name = args.workload
+    spec = ATTENTION_WORKLOADS[name]
+    torch.cuda.set_device(0)
+    torch.zeros(1, device="cuda")
+    heads, num_q, num_k, dim, mask, ab = spec["heads"], spec["num_q"], spec["num_k"], spec["dim"], spec["mask"], spec["ab"]
+    scale = dim ** -0.5
+    tdt = torch.float16 if ab == "f16" else torch.bfloat16
+    cuda_type = capi.CUDA_R_16F if ab == "f16" else capi.CUDA_R_16BF
+    count_q, count_k = heads * num_q * dim, heads * num_k * dim
+    hostQ = host_operand(torch, spec, count_q, 0)
+    hostK = host_operand(torch, spec, count_k, count_q)
+    hostV = host_operand(torch, spec, count_k, count_q + count_k)
+    hostO = torch.empty(count_q, dtype=tdt).pin_memory()
+    algorithmic_bytes = (2 * count_q + 2 * count_k) * 2
+    copies = 1 if algorithmic_bytes > 2 * L2_BYTES else int(2 * L2_BYTES // algorithmic_bytes) + 2
+    dQ, dK, dV = ([h.cuda() for _ in range(copies)] for h in (hostQ, hostK, hostV))
+    dO = [torch.zeros(count_q, dtype=tdt, device="cuda") for _ in range(copies)]
+    lib = capi.cublas_library()
+    stream = torch.cuda.Stream()
+    counter = [0]
+
+    def call(i):
+        j = i % copies
+        status = capi.attention_forward(stream.cuda_stream, cuda_type, 1, heads, heads, num_q, num_k, dim, mask, scale, dQ[j].data_ptr(), (dim, num_q * dim, 0),
+                                        dK[j].data_ptr(), (dim, num_k * dim, 0), dV[j].data_ptr(), (dim, num_k * dim, 0), dO[j].data_ptr(), (dim, num_q * dim, 0))
+        assert status == 0, f"vkzbAttentionForward: status {status}"
+
+    def step():
+        call(counter[0])
+        counter[0] += 1
+
+    flops = 4.0 * heads * num_q * num_k * dim * (0.5 if mask else 1.0)
+    with torch.cuda.stream(stream):
+        for _ in range(max(3, args.warmup)):
+            step()
+        stream.synchronize()
+    launches0 = int(lib.vkzbLaunchCount())
+    sampler = ClockSampler(physical_gpu_index(0))
+    time.sleep(0.3)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    with torch.cuda.stream(stream):
+        start.record(stream)
+        for _ in range(args.steps):
+            step()
+        stop.record(stream)
+        stream.synchronize()
+    t1 = time.time()
+    clocks = sampler.stop(t0, t1)
+    launches = int(lib.vkzbLaunchCount()) - launches0
+    kernel_ms = start.elapsed_time(stop) / args.steps
+    value_tf = flops / (kernel_ms * 1e-3) / 1e12
+    assert lib.vkzbAttentionStatus() == 0, "a bounded wait in the attention kernel gave up"
+
+    # parity: the last head of the first operand set against the fp64 oracle, with the tolerance of the reference's attention test
+    from oracle import pyoracle as orc
+    call(0)
+    stream.synchronize()
+    h = heads - 1
+    pick = lambda t, n: t[h * n * dim:(h + 1) * n * dim].float().cpu().numpy().reshape(1, 1, n, dim)
+    want, _ = orc.attention_fp64(pick(dQ[0], num_q), pick(dK[0], num_k), pick(dV[0], num_k), scale, mask)
+    err = float((np.abs(pick(dO[0], num_q) - want) / (1.0 + np.abs(want))).max())
+    tolerance = 6e-3 if ab == "f16" else 4e-2
+    assert err <= tolerance, f"attention differs from the fp64 oracle: {err}"
+
+    def step_e2e():
+        dQ[0].copy_(hostQ, non_blocking=True)
+        dK[0].copy_(hostK, non_blocking=True)
+        dV[0].copy_(hostV, non_blocking=True)
+        call(0)
+        hostO.copy_(dO[0], non_blocking=True)
+
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            step_e2e()
+        stream.synchronize()
+        e2e_steps = max(3, min(args.steps, 10))
+        start.record(stream)
+        for _ in range(e2e_steps):
+            step_e2e()
+        stop.record(stream)
+        stream.synchronize()
+    e2e_tf = flops * e2e_steps / (start.elapsed_time(stop) * 1e-3) / 1e12
+
+    # the host cores on one head of the same problem through the oracle (numpy, fp64)
+    t_c0 = time.time()
+    orc.attention_fp64(pick(dQ[0], num_q), pick(dK[0], num_k), pick(dV[0], num_k), scale, mask)
+    cpu_tf = flops / heads / (time.time() - t_c0) / 1e12
+
+    peaks, peak_kind = measured_peaks()
+    peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    traffic = None
+    traffic_file = ROOT / "profiles" / "traffic.json"
+    if traffic_file.exists():
+        try:
+            traffic = json.loads(traffic_file.read_text()).get(name)
+        except Exception:
+            traffic = None
+    line = {
+        "metric": "attention_tflops", "value": value_tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": kernel_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": ab, "data": "synthetic",
+        "config": {"workload": name, "call": "vkzbAttentionForward", "heads": heads, "num_q": num_q, "num_k": num_k, "head_dim": dim, "mask": mask,
+                   "scale": scale, "seed": spec["seed"], "distribution": list(spec["dist"]),
+                   "l2": (f"{copies} rotating operand sets, {copies * algorithmic_bytes >> 20} MiB > L2" if copies > 1 else
+                          f"operands of one step hold {algorithmic_bytes >> 20} MiB > L2") + ", no flush",
+                   "timing": "back-to-back calls on one stream"},
+        "roofline": {"bound": "tensor", "achieved": value_tf, "peak": peak, "unit": "TFLOP/s", "frac": value_tf / peak, "traffic": traffic,
+                     "peak_source": f"{peak_kind}: cuBLAS bf16 8192^3 burst", "kernel": "attentionKernel", "kernel_ms": kernel_ms,
+                     "algorithmic_bytes": algorithmic_bytes, "algorithmic_flop": flops},
+        "parity_checked": {"head": h, "max_error": err, "tolerance": tolerance, "against": "fp64 oracle (oracle/pyoracle.py attention_fp64)"},
+        "e2e": {"value": e2e_tf, "unit": "TFLOP/s", "h2d_bytes_per_step": (count_q + 2 * count_k) * 2, "d2h_bytes_per_step": count_q * 2,
+                "how": "copy Q, K, V in, one call, copy O out, on one stream"},
+        "cpu_baseline": {"value": cpu_tf, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                         "sample": f"one head ({num_q} x {num_k} x {dim}) through the numpy fp64 oracle, BLAS threads as numpy chooses"},
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, help="one of the names in WORKLOADS (default: the headline configuration)")
+    ap.add_argument("--workload", default=None, help="one of the names in WORKLOADS or ATTENTION_WORKLOADS (default: the headline configuration)")
     ap.add_argument("--chunk-columns", type=int, default=0, help="sharded run: columns per rank and round of the pipelined gather (default: chosen by rank count)")
     ap.add_argument("--gather", default="auto", choices=["auto", "fused", "pipelined"], help="sharded run: how the column blocks reach every rank")
     ap.add_argument("--timeline", action="store_true", help="sharded run: device time of every round's product and gather of one extra step, on stderr")
@@ -511,6 +651,8 @@ def main():
     if world > 1 or args.gpus > 1 or args.workload == "cfg5b_bf16_32768_nsharded":
         import bench_multi_gpu
         return bench_multi_gpu.run(args)
+    if args.workload in ATTENTION_WORKLOADS:
+        return run_attention(args)
     return run_single_gpu(args)
 
 

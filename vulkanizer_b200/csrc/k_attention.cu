@@ -2,17 +2,20 @@
 //
 // What it replaces: the batched product Q K^T (the benchmark's batched-attention shape) writes batch x numQ x numK scores to
 // memory (1 GiB of fp32 for 256 heads of 1024 x 1024), a softmax pass reads and writes them again and a second batched
-// product reads them a third time. Here a CTA owns 128 queries of one head and walks the keys in tiles of 128: the scores
-// of a tile live in tensor memory only, the probabilities go through shared memory into the second product, and what
-// reaches HBM is Q, K, V once (K and V once per query tile, from L2) and O.
+// product reads them a third time. Here a CTA owns 256 queries of one head, as two tiles of 128, and walks the keys in tiles
+// of 128: scores and probabilities live in tensor memory only, and what reaches HBM is Q, K, V once (K and V once per CTA,
+// from L2) and O.
 //
-// Roles in a CTA of 192 threads (same scheme as the GEMM kernel of k_umma.cu):
-//   warp 0      one lane issues the TMA loads: the Q tile once, then K and V tiles through a two-stage ring;
-//   warp 1      one elected lane issues tcgen05.mma: S = Q K_j^T into tensor memory, and, when the probabilities of the
-//               tile are in shared memory, O += P_j V_j into a second range of tensor-memory columns;
-//   warps 2-5   one thread per query row: read the row of S, keep the running maximum and sum (the online softmax of
-//               Milakov and Gimelshein, as used by FlashAttention), write P_j as 16-bit values in the swizzled layout the
-//               tensor cores read, rescale the row of O when its maximum moved, and at the end divide by the sum and store.
+// Roles in a CTA of 320 threads (the scheme of the GEMM kernel in k_umma.cu, with the two-tile alternation of FlashAttention-4):
+//   warp 0      one lane issues the TMA loads: the two Q tiles once, then K and V tiles through two-stage rings;
+//   warp 1      one elected lane issues tcgen05.mma. Tensor memory holds S and O of both query tiles (4 x 128 columns). Per
+//               key tile and query tile t: S_t = Q_t K_j^T; and, when the probabilities are there, O_t += P_t V_j with P_t
+//               read from tensor memory (it overlays S_t). While the softmax warps of one query tile work on their scores
+//               the tensor cores run the other tile's products;
+//   warps 2-5 and 6-9   query tile 0 and 1, one thread per query row: read the row of S, keep the running maximum and sum
+//               (the online softmax of Milakov and Gimelshein, as used by FlashAttention), write P as 16-bit pairs over the
+//               columns of S already read, rescale the row of O when the maximum moved far, and at the end divide by the
+//               sum and store the row.
 // Every wait is bounded: a wait that runs out records a code in g_attentionStatus, raises the CTA's abort flag and all
 // roles leave through the common exit, which frees the tensor memory.
 #include <cuda.h>
@@ -33,11 +36,12 @@ namespace {
 
 constexpr int kTileQ = 128;                 // queries per CTA = TMEM lanes
 constexpr int kTileK = 128;                 // keys per step
-constexpr int kAttnThreads = 192;
+constexpr int kQueriesPerCta = 256;         // two query tiles share the K and V tiles a CTA loads
+constexpr int kAttnThreads = 320;           // loader, issuer, four softmax warps per query tile
 constexpr int kAtomBytes = 128 * 128;       // 128 rows of one 128-byte swizzle span
 constexpr int kVBoxBytes = 64 * 128;        // 64 keys x 64 values of V
 constexpr unsigned long long kAttnWaitLimitNs = 4000000000ull;
-constexpr unsigned kTmemColumns = 256;      // S: columns 0-127, O: columns 128-255
+constexpr unsigned kTmemColumns = 512;      // S and O of two query tiles, 128 columns each
 
 enum : unsigned { kAttnOk = 0, kAttnProducerWait = 33, kAttnMmaWait = 34, kAttnSoftmaxWait = 35 };
 __device__ unsigned g_attentionStatus;
@@ -115,6 +119,12 @@ __device__ __forceinline__ void mmaF16(unsigned tmemD, unsigned long long descA,
                  ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
+// The same with A (the probabilities) read from tensor memory: row i in lane i, two 16-bit values of k per 32-bit column.
+__device__ __forceinline__ void mmaF16FromTmem(unsigned tmemD, unsigned tmemA, unsigned long long descB, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmemD), "r"(tmemA), "l"(descB), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
 // Generic-proxy writes to shared memory before, asynchronous-proxy reads (the tensor cores') after.
 __device__ __forceinline__ void fenceAsyncShared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 // 32 lanes x 32 columns of 32-bit cells: thread i of the warp receives row i.
@@ -142,6 +152,15 @@ __device__ __forceinline__ void tmemStore32(unsigned taddr, const unsigned (&r)[
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmemStore16(unsigned taddr, const unsigned (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+        "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float exp2Approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -161,20 +180,23 @@ __device__ __forceinline__ unsigned packPair(float lo, float hi) {
 // Shared-memory plan for head dimension D (elements of 2 bytes). Q and K tiles: D / 64 atoms of 128 rows x 128 bytes
 // (64 values of the head dimension per row: the K-major operand layout under the 128-byte swizzle). V tiles: the
 // head dimension is the contiguous one and is the N side of the second product, so V is staged as boxes of 64 keys x 64
-// values, ordered [half of the keys][chunk of the head dimension]. P: two atoms of 128 rows x 64 keys.
+// values, ordered [half of the keys][chunk of the head dimension]. Two query tiles, two stages of K, two of V.
 template <int D>
 struct AttnPlan {
     static constexpr int kAtoms = D / 64;
-    static constexpr int kQBytes = kAtoms * kAtomBytes;
-    static constexpr int kKBytes = kQBytes;
-    static constexpr int kVBytes = 2 * kAtoms * kVBoxBytes;
-    static constexpr int kPBytes = 2 * kAtomBytes;
-    static constexpr int kOffK = kQBytes;
-    static constexpr int kOffV = kOffK + 2 * kKBytes;
-    static constexpr int kOffP = kOffV + 2 * kVBytes;
-    static constexpr int kOffBars = kOffP + kPBytes;
-    static constexpr int kSmemBytes = kOffBars + 128 + 1024;  // barriers and flags; slack to align the base to 1024 bytes
+    static constexpr int kTileBytes = kAtoms * kAtomBytes;       // a Q or K tile
+    static constexpr int kVBytes = 2 * kAtoms * kVBoxBytes;      // a V tile: the same size
+    static constexpr int kOffK = 2 * kTileBytes;
+    static constexpr int kOffV = kOffK + 2 * kTileBytes;
+    static constexpr int kOffBars = kOffV + 2 * kVBytes;
+    static constexpr int kUsedBytes = kOffBars + 256 + 1024;     // barriers and flags; slack to align the base to 1024 bytes
+    // a CTA takes all 512 columns of tensor memory, so a second CTA on the SM could only wait for it: ask for more than
+    // half of the SM's shared memory even where the tiles need less
+    static constexpr int kSmemBytes = kUsedBytes > 120 * 1024 ? kUsedBytes : 120 * 1024;
 };
+
+// Barrier numbers (8 bytes each from the start of the barrier block); [2] = one per query tile or per stage.
+enum : unsigned { kBarQ = 0, kBarKFull = 2, kBarKEmpty = 4, kBarVFull = 6, kBarVEmpty = 8, kBarS = 10, kBarP = 12, kBarO = 14, kBarCount = 16 };
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -185,27 +207,30 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
     extern __shared__ unsigned char smemRaw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + Plan::kOffBars);
-    // bars: 0 Q loaded; 1-2 K/V stage loaded; 3-4 K/V stage read; 5 S ready; 6 P ready (and S read); 7 O updated
-    unsigned* tmemSlot = reinterpret_cast<unsigned*>(bars + 8);
+    unsigned* tmemSlot = reinterpret_cast<unsigned*>(bars + kBarCount);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const unsigned base = smemAddr(smem);
-    const unsigned barQ = smemAddr(bars), barKvFull = barQ + 8, barKvEmpty = barQ + 24, barS = barQ + 40, barP = barQ + 48, barO = barQ + 56;
-    const int q0 = blockIdx.x * kTileQ, head = blockIdx.y, batch = blockIdx.z;
+    const unsigned bar0 = smemAddr(bars);
+    const auto bar = [&](unsigned which, int index) { return bar0 + 8 * (which + unsigned(index)); };
+    const int q0 = blockIdx.x * kQueriesPerCta, head = blockIdx.y, batch = blockIdx.z;
     const int kvHead = head / g.kvGroup;
     // keys a query may see: index <= query + diag
     const int diag = g.mask == 2 ? g.numK - g.numQ : 0;
-    const int lastQuery = min(q0 + kTileQ, g.numQ) - 1;
-    const int keysInReach = g.mask ? max(0, min(g.numK, lastQuery + diag + 1)) : g.numK;
-    const int tiles = (keysInReach + kTileK - 1) / kTileK;
+    // key tiles that hold a key some query of query tile t may see
+    const auto keyTilesOf = [&](int t) {
+        const int first = q0 + t * kTileQ;
+        if (first >= g.numQ) return 0;
+        const int lastQuery = min(first + kTileQ, g.numQ) - 1;
+        const int reach = g.mask ? max(0, min(g.numK, lastQuery + diag + 1)) : g.numK;
+        return (reach + kTileK - 1) / kTileK;
+    };
+    const int tiles[2] = {keyTilesOf(0), keyTilesOf(1)};
+    const int steps = max(tiles[0], tiles[1]);
 
     if (threadIdx.x == 0) {
-        mbarInit(barQ, 1);
-        for (int s = 0; s < 2; ++s) mbarInit(barKvFull + 8 * s, 1), mbarInit(barKvEmpty + 8 * s, 1);
-        mbarInit(barS, 1);
-        mbarInit(barP, 4);  // one arrival per softmax warp
-        mbarInit(barO, 1);
+        for (unsigned b = 0; b < kBarCount; ++b) mbarInit(bar0 + 8 * b, b == kBarP || b == kBarP + 1 ? 4 : 1);  // P: one arrival per softmax warp
         *abortFlag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fenceAsyncShared();
@@ -218,136 +243,185 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
     __syncthreads();
     tcgen05FenceAfter();
     const unsigned tmemBase = *tmemSlot;
-    const unsigned tmemS = tmemBase, tmemO = tmemBase + 128;
+    // columns: S of query tile 0 | S of tile 1 | O of tile 0 | O of tile 1; P of a tile overlays the first 64 columns of its S
 
     if (warp == 0) {
         // ---- TMA producer ----
-        if (lane == 0 && tiles > 0) {
-            mbarArriveExpectTx(barQ, Plan::kQBytes);
-            for (int a = 0; a < kAtoms; ++a) tmaLoad4d(base + a * kAtomBytes, &mapQ, barQ, 64 * a, q0, head, batch);
-            for (int j = 0; j < tiles; ++j) {
+        if (lane == 0 && steps > 0) {
+            for (int t = 0; t < 2; ++t) {
+                if (!tiles[t]) continue;
+                mbarArriveExpectTx(bar(kBarQ, t), Plan::kTileBytes);
+                for (int a = 0; a < kAtoms; ++a) tmaLoad4d(base + t * Plan::kTileBytes + a * kAtomBytes, &mapQ, bar(kBarQ, t), 64 * a, q0 + t * kTileQ, head, batch);
+            }
+            for (int j = 0; j < steps; ++j) {
                 const int stage = j & 1;
-                if (!mbarWait(barKvEmpty + 8 * stage, ((j >> 1) & 1) ^ 1, abortFlag, kAttnProducerWait)) break;
-                const unsigned bar = barKvFull + 8 * stage;
-                mbarArriveExpectTx(bar, Plan::kKBytes + Plan::kVBytes);
-                const unsigned dstK = base + Plan::kOffK + stage * Plan::kKBytes, dstV = base + Plan::kOffV + stage * Plan::kVBytes;
+                const unsigned freed = ((j >> 1) & 1) ^ 1;
                 const int k0 = j * kTileK;
-                for (int a = 0; a < kAtoms; ++a) tmaLoad4d(dstK + a * kAtomBytes, &mapK, bar, 64 * a, k0, kvHead, batch);
+                if (!mbarWait(bar(kBarKEmpty, stage), freed, abortFlag, kAttnProducerWait)) break;
+                mbarArriveExpectTx(bar(kBarKFull, stage), Plan::kTileBytes);
+                for (int a = 0; a < kAtoms; ++a)
+                    tmaLoad4d(base + Plan::kOffK + stage * Plan::kTileBytes + a * kAtomBytes, &mapK, bar(kBarKFull, stage), 64 * a, k0, kvHead, batch);
+                if (!mbarWait(bar(kBarVEmpty, stage), freed, abortFlag, kAttnProducerWait)) break;
+                mbarArriveExpectTx(bar(kBarVFull, stage), Plan::kVBytes);
                 for (int half = 0; half < 2; ++half)
                     for (int c = 0; c < kAtoms; ++c)
-                        tmaLoad4d(dstV + (half * kAtoms + c) * kVBoxBytes, &mapV, bar, 64 * c, k0 + 64 * half, kvHead, batch);
+                        tmaLoad4d(base + Plan::kOffV + stage * Plan::kVBytes + (half * kAtoms + c) * kVBoxBytes, &mapV, bar(kBarVFull, stage), 64 * c,
+                                  k0 + 64 * half, kvHead, batch);
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         // ---- MMA issuer ----
+        // The tensor cores run what this lane issues in order, so S_t of the next key tile may be issued right behind the
+        // P V of this one although both use the same columns. Per key tile and query tile: wait for the probabilities, issue
+        // O_t += P_t V, issue S_t of the next key tile. While the softmax warps of one query tile work, the tensor cores run
+        // the other tile's products.
         // shared-memory descriptors: stride offset 1024 bytes (8 rows of 128 bytes), version 1, 128-byte swizzle; the leading
         // offset is unused for K-major operands (1) and the distance between 64-value chunks for V
         const unsigned long long hi = static_cast<unsigned long long>((1024u >> 4) | 1u << 14 | 2u << 29) << 32;
         const auto desc = [&](unsigned addr, unsigned lbo) { return hi | (((addr & 0x3FFFFu) >> 4) | lbo << 16); };
         // the whole warp takes every decision together: a wait that gave up in one lane ends the loop for all
-        const auto waitAll = [&](unsigned bar, unsigned parity) { return __all_sync(0xFFFFFFFFu, mbarWait(bar, parity, abortFlag, kAttnMmaWait)) != 0; };
-        bool ok = tiles == 0 || waitAll(barQ, 0);
-        for (int j = 0; ok && j < tiles; ++j) {
+        const auto waitAll = [&](unsigned b, unsigned parity) { return __all_sync(0xFFFFFFFFu, mbarWait(b, parity, abortFlag, kAttnMmaWait)) != 0; };
+        const auto issueS = [&](int t, int j) {  // S_t = Q_t K_j^T, 16 values of the head dimension per instruction
             const int stage = j & 1;
-            if (!(ok = waitAll(barKvFull + 8 * stage, (j >> 1) & 1))) break;
-            tcgen05FenceAfter();
-            if (electOne()) {
-                // S = Q K^T: the previous tile's probabilities were announced, so S has been read
 #pragma unroll
-                for (int a = 0; a < kAtoms; ++a) {
-                    const unsigned long long dq = desc(base + a * kAtomBytes, 1), dk = desc(base + Plan::kOffK + stage * Plan::kKBytes + a * kAtomBytes, 1);
+            for (int a = 0; a < kAtoms; ++a) {
+                const unsigned long long dq = desc(base + t * Plan::kTileBytes + a * kAtomBytes, 1);
+                const unsigned long long dk = desc(base + Plan::kOffK + stage * Plan::kTileBytes + a * kAtomBytes, 1);
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) mmaF16(tmemS, dq + 2 * q, dk + 2 * q, g.idescS, (a | q) ? 1u : 0u);
-                }
-                tcgen05Commit(barS);
+                for (int q = 0; q < 4; ++q) mmaF16(tmemBase + 128 * t, dq + 2 * q, dk + 2 * q, g.idescS, (a | q) ? 1u : 0u);
             }
-            __syncwarp();
-            if (!(ok = waitAll(barP, j & 1))) break;
+            tcgen05Commit(bar(kBarS, t));
+        };
+        const auto issuePV = [&](int t, int j) {  // O_t += P_t V_j, 16 keys per instruction: 8 columns of P (two values each)
+            const int stage = j & 1;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const unsigned long long dv = desc(base + Plan::kOffV + stage * Plan::kVBytes + half * kAtoms * kVBoxBytes, kVBoxBytes >> 4);
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    mmaF16FromTmem(tmemBase + 256 + 128 * t, tmemBase + 128 * t + 8 * (4 * half + q), dv + q * (2048 >> 4), g.idescO, (j | half | q) ? 1u : 0u);
+            }
+            tcgen05Commit(bar(kBarO, t));
+        };
+        bool ok = steps == 0 || waitAll(bar(kBarKFull, 0), 0);
+        for (int t = 0; ok && t < 2; ++t) {
+            if (!tiles[t]) continue;
+            if (!(ok = waitAll(bar(kBarQ, t), 0))) break;
             tcgen05FenceAfter();
-            if (electOne()) {
-                // O += P V: 16 keys per instruction, 64 keys per atom of P and per half of the V stage
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const unsigned long long dp = desc(base + Plan::kOffP + half * kAtomBytes, 1);
-                    const unsigned long long dv = desc(base + Plan::kOffV + stage * Plan::kVBytes + half * kAtoms * kVBoxBytes, kVBoxBytes >> 4);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) mmaF16(tmemO, dp + 2 * q, dv + q * (2048 >> 4), g.idescO, (j | half | q) ? 1u : 0u);
+            if (electOne()) issueS(t, 0);
+            __syncwarp();
+        }
+        if (ok && steps > 0 && electOne()) tcgen05Commit(bar(kBarKEmpty, 0));  // K tile 0 has no reader left once these products are done
+        __syncwarp();
+        for (int j = 0; ok && j < steps; ++j) {
+            const int stage = j & 1, next = stage ^ 1;
+            if (!(ok = waitAll(bar(kBarVFull, stage), (j >> 1) & 1))) break;
+            if (j + 1 < steps && !(ok = waitAll(bar(kBarKFull, next), ((j + 1) >> 1) & 1))) break;
+            for (int t = 0; ok && t < 2; ++t) {
+                if (j >= tiles[t]) continue;
+                if (!(ok = waitAll(bar(kBarP, t), j & 1))) break;
+                tcgen05FenceAfter();
+                if (electOne()) {
+                    issuePV(t, j);
+                    if (j + 1 < tiles[t]) issueS(t, j + 1);
                 }
-                tcgen05Commit(barKvEmpty + 8 * stage);
-                tcgen05Commit(barO);
+                __syncwarp();
+            }
+            if (ok && electOne()) {
+                tcgen05Commit(bar(kBarVEmpty, stage));                      // every P V of this key tile has been issued
+                if (j + 1 < steps) tcgen05Commit(bar(kBarKEmpty, next));    // and every S of the next one
             }
             __syncwarp();
         }
     } else {
-        // ---- softmax and output: one thread per query ----
+        // ---- softmax and output: four warps per query tile, one thread per query ----
+        const int t = (warp - 2) / 4;
         const int quarter = warp % 4;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31
-        const int rowInTile = quarter * 32 + lane, query = q0 + rowInTile;
+        const int rowInTile = quarter * 32 + lane, query = q0 + t * kTileQ + rowInTile;
         const unsigned laneBits = unsigned(quarter * 32) << 16;
+        const unsigned tmemS = tmemBase + 128 * t + laneBits, tmemO = tmemBase + 256 + 128 * t + laneBits;
         const int visible = g.mask ? max(0, min(g.numK, query + diag + 1)) : g.numK;  // keys [0, visible) count for this row
+        const int myTiles = tiles[t];
         const float c = g.scaleLog2;
         float runMax = -INFINITY, runSum = 0.f;
-        unsigned char* sP = smem + Plan::kOffP;
         // tcgen05.ld and .st are warp-wide: the warp takes every decision together
-        const auto waitAll = [&](unsigned bar, unsigned parity) { return __all_sync(0xFFFFFFFFu, mbarWait(bar, parity, abortFlag, kAttnSoftmaxWait)) != 0; };
+        const auto waitAll = [&](unsigned b, unsigned parity) { return __all_sync(0xFFFFFFFFu, mbarWait(b, parity, abortFlag, kAttnSoftmaxWait)) != 0; };
         bool ok = true;
-        for (int j = 0; j < tiles; ++j) {
-            if (!(ok = waitAll(barS, j & 1))) break;
+        for (int j = 0; j < myTiles; ++j) {
+            // S_t of this key tile is complete, and with it everything issued before it: the previous P V has read P and updated O
+            if (!(ok = waitAll(bar(kBarS, t), j & 1))) break;
             tcgen05FenceAfter();
             const int limit = visible - j * kTileK;  // columns [0, limit) of this tile count
+            // the same code path for the whole warp (tcgen05.ld and .st must not sit in a branch that lanes take differently)
+            const bool allCount = __all_sync(0xFFFFFFFFu, limit >= kTileK) != 0;
             unsigned v[32];
             float tileMax = -INFINITY;
+            if (allCount && c >= 0.f) {
+                // every column counts: the maximum of the raw scores, scaled once
 #pragma unroll
-            for (int chunk = 0; chunk < 4; ++chunk) {
-                tmemLoad32(tmemS + laneBits + 32 * chunk, v);
+                for (int chunk = 0; chunk < 4; ++chunk) {
+                    tmemLoad32(tmemS + 32 * chunk, v);
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (chunk * 32 + i < limit) tileMax = fmaxf(tileMax, __uint_as_float(v[i]) * c);
+                    for (int i = 0; i < 32; ++i) tileMax = fmaxf(tileMax, __uint_as_float(v[i]));
+                }
+                tileMax *= c;
+            } else {
+#pragma unroll
+                for (int chunk = 0; chunk < 4; ++chunk) {
+                    tmemLoad32(tmemS + 32 * chunk, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (chunk * 32 + i < limit) tileMax = fmaxf(tileMax, __uint_as_float(v[i]) * c);
+                }
             }
-            const float newMax = fmaxf(runMax, tileMax);
+            // The reference point of the exponentials moves only when the maximum has grown by more than 2^8: until then the
+            // probabilities are at most 256 (exact enough in 16 bits, far from overflow in the sums) and the row of O needs
+            // no rescaling. The final division by the sum, taken against the same reference point, makes the result the same.
+            const float newMax = runMax == -INFINITY || tileMax > runMax + 8.f ? tileMax : runMax;
             const float shift = newMax == -INFINITY ? 0.f : newMax;  // a row that has seen no key yet
-            const float correction = exp2Approx(runMax - shift);     // 0 for the first keys of a row
+            const float correction = newMax == runMax ? 1.f : exp2Approx(runMax - shift);  // 0 for the first keys of a row
             runMax = newMax;
-            // the previous tile's P V has read P and updated O
-            if (j > 0 && !(ok = waitAll(barO, (j - 1) & 1))) break;
-            tcgen05FenceAfter();
             float tileSum = 0.f;
 #pragma unroll
             for (int chunk = 0; chunk < 4; ++chunk) {
-                tmemLoad32(tmemS + laneBits + 32 * chunk, v);
+                tmemLoad32(tmemS + 32 * chunk, v);
                 unsigned packed[16];
+                if (allCount) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int col = chunk * 32 + 2 * i;
-                    const float p0 = col < limit ? exp2Approx(fmaf(__uint_as_float(v[2 * i]), c, -shift)) : 0.f;
-                    const float p1 = col + 1 < limit ? exp2Approx(fmaf(__uint_as_float(v[2 * i + 1]), c, -shift)) : 0.f;
-                    tileSum += p0 + p1;
-                    packed[i] = packPair<BF16>(p0, p1);
-                }
-                // 16-byte pieces of this row: piece (4 chunk + t) of 16 sits in atom (piece / 8), at position (piece % 8) ^ (row % 8)
+                    for (int i = 0; i < 16; ++i) {
+                        const float p0 = exp2Approx(fmaf(__uint_as_float(v[2 * i]), c, -shift)), p1 = exp2Approx(fmaf(__uint_as_float(v[2 * i + 1]), c, -shift));
+                        tileSum += p0 + p1;
+                        packed[i] = packPair<BF16>(p0, p1);
+                    }
+                } else {
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const int piece = 4 * chunk + t;
-                    uint4* dst = reinterpret_cast<uint4*>(sP + (piece / 8) * kAtomBytes + rowInTile * 128 + (((piece % 8) ^ (rowInTile & 7)) * 16));
-                    *dst = make_uint4(packed[4 * t], packed[4 * t + 1], packed[4 * t + 2], packed[4 * t + 3]);
+                    for (int i = 0; i < 16; ++i) {
+                        const int col = chunk * 32 + 2 * i;
+                        const float p0 = col < limit ? exp2Approx(fmaf(__uint_as_float(v[2 * i]), c, -shift)) : 0.f;
+                        const float p1 = col + 1 < limit ? exp2Approx(fmaf(__uint_as_float(v[2 * i + 1]), c, -shift)) : 0.f;
+                        tileSum += p0 + p1;
+                        packed[i] = packPair<BF16>(p0, p1);
+                    }
                 }
+                // P overlays S: columns 16 chunk .. + 15 hold what was read from columns 32 chunk .. + 31, always behind the reads
+                tmemStore16(tmemS + 16 * chunk, packed);
             }
             runSum = runSum * correction + tileSum;
-            if (j > 0 && !__all_sync(0xFFFFFFFFu, correction == 1.f)) {
+            if (j > 0 && __any_sync(0xFFFFFFFFu, correction != 1.f)) {
 #pragma unroll
                 for (int chunk = 0; chunk < D / 32; ++chunk) {
-                    tmemLoad32(tmemO + laneBits + 32 * chunk, v);
+                    tmemLoad32(tmemO + 32 * chunk, v);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * correction);
-                    tmemStore32(tmemO + laneBits + 32 * chunk, v);
+                    tmemStore32(tmemO + 32 * chunk, v);
                 }
             }
             tcgen05FenceBefore();
-            fenceAsyncShared();
             __syncwarp();
-            if (lane == 0) mbarArrive(barP);
+            if (lane == 0) mbarArrive(bar(kBarP, t));
         }
-        if (ok && tiles > 0) ok = waitAll(barO, (tiles - 1) & 1);
+        if (ok && myTiles > 0) ok = waitAll(bar(kBarO, t), (myTiles - 1) & 1);
         tcgen05FenceAfter();
         if (ok) {
             using Elem = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
@@ -356,19 +430,19 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
 #pragma unroll
             for (int chunk = 0; chunk < D / 32; ++chunk) {
                 unsigned v[32];
-                if (tiles > 0) {
-                    tmemLoad32(tmemO + laneBits + 32 * chunk, v);
+                if (myTiles > 0) {
+                    tmemLoad32(tmemO + 32 * chunk, v);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0u;
                 }
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {
+                for (int piece = 0; piece < 4; ++piece) {
                     unsigned w[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        w[i] = packPair<BF16>(__uint_as_float(v[8 * t + 2 * i]) * inverse, __uint_as_float(v[8 * t + 2 * i + 1]) * inverse);
-                    if (query < g.numQ) *reinterpret_cast<uint4*>(out + chunk * 32 + t * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        w[i] = packPair<BF16>(__uint_as_float(v[8 * piece + 2 * i]) * inverse, __uint_as_float(v[8 * piece + 2 * i + 1]) * inverse);
+                    if (query < g.numQ) *reinterpret_cast<uint4*>(out + chunk * 32 + piece * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
             if (g.logSumExp && query < g.numQ)  // natural logarithm of the sum of exp(score); 0 for a row without visible keys
@@ -473,7 +547,7 @@ extern "C" __attribute__((visibility("default"))) int vkzbAttentionForward(cudaS
     // accumulate in f32; A and B in `format`; M = 128; S: N = 128 keys, both operands K-major; O: N = head dimension, B (V) N-major
     g.idescS = 1u << 4 | format << 7 | format << 10 | unsigned(kTileK >> 3) << 17 | unsigned(kTileQ >> 4) << 24;
     g.idescO = 1u << 4 | format << 7 | format << 10 | 1u << 16 | unsigned(a->headDim >> 3) << 17 | unsigned(kTileQ >> 4) << 24;
-    const dim3 grid(unsigned((a->numQ + kTileQ - 1) / kTileQ), unsigned(a->heads), unsigned(a->batches));
+    const dim3 grid(unsigned((a->numQ + kQueriesPerCta - 1) / kQueriesPerCta), unsigned(a->heads), unsigned(a->batches));
     cudaError_t e;
     if (a->headDim == 128) e = bf16 ? launchAttention<128, true>(g, mq, mk, mv, grid, stream) : launchAttention<128, false>(g, mq, mk, mv, grid, stream);
     else e = bf16 ? launchAttention<64, true>(g, mq, mk, mv, grid, stream) : launchAttention<64, false>(g, mq, mk, mv, grid, stream);
