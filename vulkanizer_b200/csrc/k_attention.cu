@@ -24,6 +24,7 @@
 #include <cuda_runtime.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <cstdint>
 #include <mutex>
 #include <type_traits>
@@ -54,7 +55,15 @@ struct AttentionArgs {
     long long oRow, oHead, oBatch;
     float* logSumExp;    // [batch][head][numQ], or null
     unsigned idescS, idescO;
+#ifdef VKZB_ATTN_TRACE
+    long long* trace;
+#endif
 };
+#ifdef VKZB_ATTN_TRACE
+#define TRACE(slot) do { if (g.trace && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) g.trace[(slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot) do {} while (0)
+#endif
 
 // ---- PTX wrappers (the same instructions as in k_umma.cu; this file is a translation unit of its own) -----------------
 
@@ -152,19 +161,57 @@ __device__ __forceinline__ void tmemStore32(unsigned taddr, const unsigned (&r)[
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void tmemStore16(unsigned taddr, const unsigned (&r)[16]) {
+__device__ __forceinline__ void tmemLoad32Issue(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmemWaitLoads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmemStore16Issue(unsigned taddr, const unsigned (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
         "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
         "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmemWaitStores() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// sm_100's three-input maximum
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 __device__ __forceinline__ float exp2Approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// 2^x for x <= 8 without the special-function unit (the split into integer and fraction of Cody and Waite, a cubic for the
+// fraction with the coefficients FlashAttention-4 uses: relative error about 1e-4, below the rounding of a 16-bit result).
+#ifndef VKZB_ATTN_POLY_EVERY
+#define VKZB_ATTN_POLY_EVERY 0
+#endif
+#ifndef VKZB_ATTN_TURNS
+#define VKZB_ATTN_TURNS 0
+#endif
+constexpr bool kTakeTurns = VKZB_ATTN_TURNS != 0;
+constexpr int kPolyEvery = VKZB_ATTN_POLY_EVERY;  // one exponential in this many takes the polynomial (0: none; even values)
+__device__ __forceinline__ float exp2Poly(float x) {
+    x = fmaxf(x, -127.f);
+    const float biased = __fadd_rd(x, 12582912.f);   // 1.5 * 2^23: the low mantissa bits now hold floor(x)
+    const float fraction = x - (biased - 12582912.f);  // in [0, 1)
+    float p = fmaf(fraction, 0.077119089663028717041015625f, 0.227564394474029541015625f);
+    p = fmaf(p, fraction, 0.695146143436431884765625f);
+    p = fmaf(p, fraction, 1.f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(biased) << 23));  // times 2^floor(x), through the exponent field
 }
 template <bool BF16>
 __device__ __forceinline__ unsigned packPair(float lo, float hi) {
@@ -196,7 +243,7 @@ struct AttnPlan {
 };
 
 // Barrier numbers (8 bytes each from the start of the barrier block); [2] = one per query tile or per stage.
-enum : unsigned { kBarQ = 0, kBarKFull = 2, kBarKEmpty = 4, kBarVFull = 6, kBarVEmpty = 8, kBarS = 10, kBarP = 12, kBarO = 14, kBarCount = 16 };
+enum : unsigned { kBarQ = 0, kBarKFull = 2, kBarKEmpty = 4, kBarVFull = 6, kBarVEmpty = 8, kBarS = 10, kBarP = 12, kBarO = 14, kBarTurn = 16, kBarCount = 18 };
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -230,7 +277,7 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
     const int steps = max(tiles[0], tiles[1]);
 
     if (threadIdx.x == 0) {
-        for (unsigned b = 0; b < kBarCount; ++b) mbarInit(bar0 + 8 * b, b == kBarP || b == kBarP + 1 ? 4 : 1);  // P: one arrival per softmax warp
+        for (unsigned b = 0; b < kBarCount; ++b) mbarInit(bar0 + 8 * b, b >= kBarTurn || b == kBarP || b == kBarP + 1 ? 4 : 1);  // P and the turns: one arrival per softmax warp
         *abortFlag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fenceAsyncShared();
@@ -322,11 +369,13 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
                 if (j >= tiles[t]) continue;
                 if (!(ok = waitAll(bar(kBarP, t), j & 1))) break;
                 tcgen05FenceAfter();
+                TRACE(2000 + 1000 * t + 16 * j + 0);
                 if (electOne()) {
                     issuePV(t, j);
                     if (j + 1 < tiles[t]) issueS(t, j + 1);
                 }
                 __syncwarp();
+                TRACE(2000 + 1000 * t + 16 * j + 1);
             }
             if (ok && electOne()) {
                 tcgen05Commit(bar(kBarVEmpty, stage));                      // every P V of this key tile has been issued
@@ -352,74 +401,101 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
             // S_t of this key tile is complete, and with it everything issued before it: the previous P V has read P and updated O
             if (!(ok = waitAll(bar(kBarS, t), j & 1))) break;
             tcgen05FenceAfter();
+            if (quarter == 0) TRACE(1000 * t + 16 * j + 0);
             const int limit = visible - j * kTileK;  // columns [0, limit) of this tile count
             // the same code path for the whole warp (tcgen05.ld and .st must not sit in a branch that lanes take differently)
             const bool allCount = __all_sync(0xFFFFFFFFu, limit >= kTileK) != 0;
-            unsigned v[32];
+            // the whole row of S in registers: four loads in flight, one wait
+            unsigned v[kTileK];
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk) tmemLoad32Issue(tmemS + 32 * chunk, *reinterpret_cast<unsigned(*)[32]>(v + 32 * chunk));
+            tmemWaitLoads();
+            if (quarter == 0) TRACE(1000 * t + 16 * j + 1);
             float tileMax = -INFINITY;
             if (allCount && c >= 0.f) {
-                // every column counts: the maximum of the raw scores, scaled once
+                // every column counts: the maximum of the raw scores (three at a time), scaled once
+                float m[8];
 #pragma unroll
-                for (int chunk = 0; chunk < 4; ++chunk) {
-                    tmemLoad32(tmemS + 32 * chunk, v);
+                for (int i = 0; i < 8; ++i) m[i] = fmaxf(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) tileMax = fmaxf(tileMax, __uint_as_float(v[i]));
-                }
-                tileMax *= c;
+                for (int i = 16; i < kTileK; i += 16)
+#pragma unroll
+                    for (int a = 0; a < 8; ++a) m[a] = max3(m[a], __uint_as_float(v[i + 2 * a]), __uint_as_float(v[i + 2 * a + 1]));
+                tileMax = max3(max3(m[0], m[1], m[2]), max3(m[3], m[4], m[5]), fmaxf(m[6], m[7])) * c;
             } else {
 #pragma unroll
-                for (int chunk = 0; chunk < 4; ++chunk) {
-                    tmemLoad32(tmemS + 32 * chunk, v);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (chunk * 32 + i < limit) tileMax = fmaxf(tileMax, __uint_as_float(v[i]) * c);
-                }
+                for (int i = 0; i < kTileK; ++i)
+                    if (i < limit) tileMax = fmaxf(tileMax, __uint_as_float(v[i]) * c);
             }
             // The reference point of the exponentials moves only when the maximum has grown by more than 2^8: until then the
             // probabilities are at most 256 (exact enough in 16 bits, far from overflow in the sums) and the row of O needs
             // no rescaling. The final division by the sum, taken against the same reference point, makes the result the same.
+            if (quarter == 0) TRACE(1000 * t + 16 * j + 2);
             const float newMax = runMax == -INFINITY || tileMax > runMax + 8.f ? tileMax : runMax;
             const float shift = newMax == -INFINITY ? 0.f : newMax;  // a row that has seen no key yet
             const float correction = newMax == runMax ? 1.f : exp2Approx(runMax - shift);  // 0 for the first keys of a row
             runMax = newMax;
-            float tileSum = 0.f;
-#pragma unroll
-            for (int chunk = 0; chunk < 4; ++chunk) {
-                tmemLoad32(tmemS + 32 * chunk, v);
-                unsigned packed[16];
-                if (allCount) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float p0 = exp2Approx(fmaf(__uint_as_float(v[2 * i]), c, -shift)), p1 = exp2Approx(fmaf(__uint_as_float(v[2 * i + 1]), c, -shift));
-                        tileSum += p0 + p1;
-                        packed[i] = packPair<BF16>(p0, p1);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int col = chunk * 32 + 2 * i;
-                        const float p0 = col < limit ? exp2Approx(fmaf(__uint_as_float(v[2 * i]), c, -shift)) : 0.f;
-                        const float p1 = col + 1 < limit ? exp2Approx(fmaf(__uint_as_float(v[2 * i + 1]), c, -shift)) : 0.f;
-                        tileSum += p0 + p1;
-                        packed[i] = packPair<BF16>(p0, p1);
-                    }
-                }
-                // P overlays S: columns 16 chunk .. + 15 hold what was read from columns 32 chunk .. + 31, always behind the reads
-                tmemStore16(tmemS + 16 * chunk, packed);
+            // The exponentials of the two query tiles take turns: the special-function unit is what bounds them, and two warps
+            // of a scheduler that want it at once only slow each other down, while taking turns leaves one tile's loads,
+            // maximum and hand-over to run beside the other's exponentials. Tile 0 goes first in every step; a tile waits
+            // only for a step the other tile really has.
+            if (kTakeTurns && (t == 1 ? j < tiles[0] : (j > 0 && j - 1 < tiles[1]))) {
+                if (!(ok = waitAll(bar(kBarTurn, t), (t == 1 ? j : j - 1) & 1))) break;
             }
+            // exp2(c s - shift): most on the special-function unit (16 results per clock and SM, which is what bounds this
+            // loop), one in kPolyEvery by a polynomial on the FMA pipe, which would otherwise idle
+            const float negShift = -shift;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            // The row is read a second time, 32 columns at a time with the next 32 already on their way: holding all 128 scores
+            // through this loop leaves the compiler too few registers to keep enough exponentials in flight.
+            unsigned ping[32], pong[32];
+            const auto exponentials = [&](const unsigned (&s32)[32], int chunk) {
+                unsigned packed[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int col = chunk * 32 + 2 * i;
+                    const float x0 = fmaf(__uint_as_float(s32[2 * i]), c, negShift), x1 = fmaf(__uint_as_float(s32[2 * i + 1]), c, negShift);
+                    float p0 = exp2Approx(x0);
+                    float p1 = kPolyEvery && (i % (kPolyEvery / 2 > 0 ? kPolyEvery / 2 : 1)) == 0 ? exp2Poly(x1) : exp2Approx(x1);
+                    if (!allCount) p0 = col < limit ? p0 : 0.f, p1 = col + 1 < limit ? p1 : 0.f;
+                    sum[i & 3] += p0 + p1;
+                    packed[i] = packPair<BF16>(p0, p1);
+                }
+                // P overlays S: columns 16 chunk .. + 15 of the row, behind everything still to be read
+                tmemStore16Issue(tmemS + 16 * chunk, packed);
+            };
+            tmemLoad32Issue(tmemS, ping);
+            tmemWaitLoads();
+            tmemLoad32Issue(tmemS + 32, pong);
+            exponentials(ping, 0);
+            tmemWaitLoads();
+            tmemLoad32Issue(tmemS + 64, ping);
+            exponentials(pong, 1);
+            tmemWaitLoads();
+            tmemLoad32Issue(tmemS + 96, pong);
+            exponentials(ping, 2);
+            tmemWaitLoads();
+            exponentials(pong, 3);
+            const float tileSum = (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            __syncwarp();
+            if (kTakeTurns && lane == 0) mbarArrive(bar(kBarTurn, t ^ 1));
+            tmemWaitStores();
+            if (quarter == 0) TRACE(1000 * t + 16 * j + 3);
             runSum = runSum * correction + tileSum;
             if (j > 0 && __any_sync(0xFFFFFFFFu, correction != 1.f)) {
 #pragma unroll
                 for (int chunk = 0; chunk < D / 32; ++chunk) {
-                    tmemLoad32(tmemO + 32 * chunk, v);
+                    unsigned o[32];
+                    tmemLoad32(tmemO + 32 * chunk, o);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * correction);
-                    tmemStore32(tmemO + 32 * chunk, v);
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * correction);
+                    tmemStore32(tmemO + 32 * chunk, o);
                 }
             }
             tcgen05FenceBefore();
             __syncwarp();
             if (lane == 0) mbarArrive(bar(kBarP, t));
+            if (quarter == 0) TRACE(1000 * t + 16 * j + 4);
         }
         if (ok && myTiles > 0) ok = waitAll(bar(kBarO, t), (myTiles - 1) & 1);
         tcgen05FenceAfter();
@@ -543,6 +619,9 @@ extern "C" __attribute__((visibility("default"))) int vkzbAttentionForward(cudaS
     g.scaleLog2 = a->scale * 1.4426950408889634f;
     g.o = a->o, g.oRow = a->oRow, g.oHead = a->oHead, g.oBatch = a->oBatch;
     g.logSumExp = a->logSumExp;
+#ifdef VKZB_ATTN_TRACE
+    g.trace = getenv("VKZB_ATTN_TRACE_PTR") ? reinterpret_cast<long long*>(strtoull(getenv("VKZB_ATTN_TRACE_PTR"), nullptr, 0)) : nullptr;
+#endif
     const unsigned format = bf16 ? 1u : 0u;
     // accumulate in f32; A and B in `format`; M = 128; S: N = 128 keys, both operands K-major; O: N = head dimension, B (V) N-major
     g.idescS = 1u << 4 | format << 7 | format << 10 | unsigned(kTileK >> 3) << 17 | unsigned(kTileQ >> 4) << 24;
