@@ -51,8 +51,6 @@ struct AttentionArgs {
     int numQ, numK, heads, kvGroup;
     int mask;            // 0 none, 1 causal from the top left, 2 from the bottom right
     float scaleLog2;     // scale * log2(e): the exponentials are taken in base 2
-    void* o;
-    long long oRow, oHead, oBatch;
     float* logSumExp;    // [batch][head][numQ], or null
     unsigned idescS, idescO;
 #ifdef VKZB_ATTN_TRACE
@@ -111,6 +109,12 @@ __device__ __forceinline__ bool mbarWait(unsigned bar, unsigned parity, volatile
 __device__ __forceinline__ void tmaLoad4d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                  ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+// Shared memory -> global, asynchronous; rows outside the tensor are clipped by the hardware.
+__device__ __forceinline__ void tmaStore4d(const CUtensorMap* map, unsigned src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(reinterpret_cast<unsigned long long>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                  : "memory");
 }
 __device__ __forceinline__ bool electOne() {
@@ -248,7 +252,7 @@ enum : unsigned { kBarQ = 0, kBarKFull = 2, kBarKEmpty = 4, kBarVFull = 6, kBarV
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                const __grid_constant__ CUtensorMap mapV) {
+                const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO) {
     using Plan = AttnPlan<D>;
     constexpr int kAtoms = Plan::kAtoms;
     extern __shared__ unsigned char smemRaw[];
@@ -499,10 +503,11 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
         }
         if (ok && myTiles > 0) ok = waitAll(bar(kBarO, t), (myTiles - 1) & 1);
         tcgen05FenceAfter();
+        // The rows of O leave through the query tile's shared memory (free once the last S has been computed) and two bulk
+        // tensor stores: a thread holds a whole row, so direct stores would touch 32 rows with every instruction.
         if (ok) {
-            using Elem = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-            Elem* out = reinterpret_cast<Elem*>(g.o) + (size_t(batch) * g.oBatch + size_t(head) * g.oHead + size_t(query) * g.oRow);
             const float inverse = runSum > 0.f ? 1.f / runSum : 0.f;
+            unsigned char* rowBase = smem + t * Plan::kTileBytes + rowInTile * 128;
 #pragma unroll
             for (int chunk = 0; chunk < D / 32; ++chunk) {
                 unsigned v[32];
@@ -518,11 +523,22 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
                         w[i] = packPair<BF16>(__uint_as_float(v[8 * piece + 2 * i]) * inverse, __uint_as_float(v[8 * piece + 2 * i + 1]) * inverse);
-                    if (query < g.numQ) *reinterpret_cast<uint4*>(out + chunk * 32 + piece * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    // 16-byte piece (4 chunk + piece) of the row: atom (index / 8), position (index % 8) ^ (row % 8), as TMA expects it
+                    const int index = 4 * chunk + piece;
+                    *reinterpret_cast<uint4*>(rowBase + (index / 8) * kAtomBytes + (((index % 8) ^ (rowInTile & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
             if (g.logSumExp && query < g.numQ)  // natural logarithm of the sum of exp(score); 0 for a row without visible keys
                 g.logSumExp[(size_t(batch) * g.heads + head) * g.numQ + query] = runSum > 0.f ? (runMax + log2f(runSum)) * 0.6931471805599453f : 0.f;
+        }
+        // every warp of the tile comes here, whatever happened before: the barrier must not wait for a warp that gave up
+        fenceAsyncShared();
+        if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+        else asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (rowInTile == 0 && *abortFlag == 0 && q0 + t * kTileQ < g.numQ) {
+            for (int a = 0; a < kAtoms; ++a) tmaStore4d(&mapO, base + t * Plan::kTileBytes + a * kAtomBytes, 64 * a, q0 + t * kTileQ, head, batch);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the shared memory is read before the CTA may end
         }
     }
 
@@ -565,7 +581,8 @@ bool encodeSequence(CUtensorMap* map, const void* base, bool bf16, int headDim, 
 }
 
 template <int D, bool BF16>
-cudaError_t launchAttention(const AttentionArgs& g, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, dim3 grid, cudaStream_t stream) {
+cudaError_t launchAttention(const AttentionArgs& g, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, dim3 grid,
+                            cudaStream_t stream) {
     static std::mutex mutex;
     static bool attributeSet[64] = {};
     int device = 0;
@@ -579,7 +596,7 @@ cudaError_t launchAttention(const AttentionArgs& g, const CUtensorMap& mq, const
             attributeSet[device] = true;
         }
     }
-    attentionKernel<D, BF16><<<grid, kAttnThreads, AttnPlan<D>::kSmemBytes, stream>>>(g, mq, mk, mv);
+    attentionKernel<D, BF16><<<grid, kAttnThreads, AttnPlan<D>::kSmemBytes, stream>>>(g, mq, mk, mv, mo);
     countLaunch();
     return cudaGetLastError();
 }
@@ -607,17 +624,17 @@ extern "C" __attribute__((visibility("default"))) int vkzbAttentionForward(cudaS
     if (!encodeTiled()) return kNotInitialized;
     const bool bf16 = a->dataType == 14;
     const int numK = a->numK;
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq, mk, mv, mo;
     // with no keys the kernel loads nothing; the maps still have to describe some memory, so they get extent 1
     if (!encodeSequence(&mq, a->q, bf16, a->headDim, a->numQ, a->heads, a->batches, a->qRow, a->qHead, a->qBatch, kTileQ) ||
         !encodeSequence(&mk, a->k, bf16, a->headDim, numK > 0 ? numK : 1, a->kvHeads, a->batches, a->kRow, a->kHead, a->kBatch, kTileK) ||
-        !encodeSequence(&mv, a->v, bf16, a->headDim, numK > 0 ? numK : 1, a->kvHeads, a->batches, a->vRow, a->vHead, a->vBatch, 64))
+        !encodeSequence(&mv, a->v, bf16, a->headDim, numK > 0 ? numK : 1, a->kvHeads, a->batches, a->vRow, a->vHead, a->vBatch, 64) ||
+        !encodeSequence(&mo, a->o, bf16, a->headDim, a->numQ, a->heads, a->batches, a->oRow, a->oHead, a->oBatch, kTileQ))
         return kNotSupported;
     AttentionArgs g{};
     g.numQ = a->numQ, g.numK = numK, g.heads = a->heads, g.kvGroup = a->heads / a->kvHeads;
     g.mask = a->mask;
     g.scaleLog2 = a->scale * 1.4426950408889634f;
-    g.o = a->o, g.oRow = a->oRow, g.oHead = a->oHead, g.oBatch = a->oBatch;
     g.logSumExp = a->logSumExp;
 #ifdef VKZB_ATTN_TRACE
     g.trace = getenv("VKZB_ATTN_TRACE_PTR") ? reinterpret_cast<long long*>(strtoull(getenv("VKZB_ATTN_TRACE_PTR"), nullptr, 0)) : nullptr;
@@ -628,8 +645,8 @@ extern "C" __attribute__((visibility("default"))) int vkzbAttentionForward(cudaS
     g.idescO = 1u << 4 | format << 7 | format << 10 | 1u << 16 | unsigned(a->headDim >> 3) << 17 | unsigned(kTileQ >> 4) << 24;
     const dim3 grid(unsigned((a->numQ + kQueriesPerCta - 1) / kQueriesPerCta), unsigned(a->heads), unsigned(a->batches));
     cudaError_t e;
-    if (a->headDim == 128) e = bf16 ? launchAttention<128, true>(g, mq, mk, mv, grid, stream) : launchAttention<128, false>(g, mq, mk, mv, grid, stream);
-    else e = bf16 ? launchAttention<64, true>(g, mq, mk, mv, grid, stream) : launchAttention<64, false>(g, mq, mk, mv, grid, stream);
+    if (a->headDim == 128) e = bf16 ? launchAttention<128, true>(g, mq, mk, mv, mo, grid, stream) : launchAttention<128, false>(g, mq, mk, mv, mo, grid, stream);
+    else e = bf16 ? launchAttention<64, true>(g, mq, mk, mv, mo, grid, stream) : launchAttention<64, false>(g, mq, mk, mv, mo, grid, stream);
     return e == cudaSuccess ? kSuccess : kExecutionFailed;
 }
 
