@@ -265,7 +265,8 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
     const unsigned base = smemAddr(smem);
     const unsigned bar0 = smemAddr(bars);
     const auto bar = [&](unsigned which, int index) { return bar0 + 8 * (which + unsigned(index)); };
-    const int q0 = blockIdx.x * kQueriesPerCta, head = blockIdx.y, batch = blockIdx.z;
+    // under a causal mask the later queries have more keys to visit: their CTAs start first, so the short ones fill the tail
+    const int q0 = int(g.mask ? gridDim.x - 1 - blockIdx.x : blockIdx.x) * kQueriesPerCta, head = blockIdx.y, batch = blockIdx.z;
     const int kvHead = head / g.kvGroup;
     // keys a query may see: index <= query + diag
     const int diag = g.mask == 2 ? g.numK - g.numQ : 0;
@@ -280,11 +281,38 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
     const int tiles[2] = {keyTilesOf(0), keyTilesOf(1)};
     const int steps = max(tiles[0], tiles[1]);
 
+    const auto loadQ = [&](int t) {
+        mbarArriveExpectTx(bar(kBarQ, t), Plan::kTileBytes);
+        for (int a = 0; a < kAtoms; ++a) tmaLoad4d(base + t * Plan::kTileBytes + a * kAtomBytes, &mapQ, bar(kBarQ, t), 64 * a, q0 + t * kTileQ, head, batch);
+    };
+    const auto loadK = [&](int j) {
+        const int stage = j & 1;
+        mbarArriveExpectTx(bar(kBarKFull, stage), Plan::kTileBytes);
+        for (int a = 0; a < kAtoms; ++a)
+            tmaLoad4d(base + Plan::kOffK + stage * Plan::kTileBytes + a * kAtomBytes, &mapK, bar(kBarKFull, stage), 64 * a, j * kTileK, kvHead, batch);
+    };
+    const auto loadV = [&](int j) {
+        const int stage = j & 1;
+        mbarArriveExpectTx(bar(kBarVFull, stage), Plan::kVBytes);
+        for (int half = 0; half < 2; ++half)
+            for (int c = 0; c < kAtoms; ++c)
+                tmaLoad4d(base + Plan::kOffV + stage * Plan::kVBytes + (half * kAtoms + c) * kVBoxBytes, &mapV, bar(kBarVFull, stage), 64 * c,
+                          j * kTileK + 64 * half, kvHead, batch);
+    };
     if (threadIdx.x == 0) {
         for (unsigned b = 0; b < kBarCount; ++b) mbarInit(bar0 + 8 * b, b >= kBarTurn || b == kBarP || b == kBarP + 1 ? 4 : 1);  // P and the turns: one arrival per softmax warp
         *abortFlag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fenceAsyncShared();
+        // This thread is also the loader: the first tiles are on their way while the tensor memory is still being
+        // allocated, in the order the first products need them (both stages are free, so nothing to wait for).
+        if (steps > 0) {
+            if (tiles[0]) loadQ(0);
+            loadK(0);
+            if (tiles[1]) loadQ(1);
+            loadV(0);
+            if (steps > 1) loadK(1), loadV(1);
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(tmemSlot)), "r"(kTmemColumns) : "memory");
@@ -298,26 +326,14 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
 
     if (warp == 0) {
         // ---- TMA producer ----
-        if (lane == 0 && steps > 0) {
-            for (int t = 0; t < 2; ++t) {
-                if (!tiles[t]) continue;
-                mbarArriveExpectTx(bar(kBarQ, t), Plan::kTileBytes);
-                for (int a = 0; a < kAtoms; ++a) tmaLoad4d(base + t * Plan::kTileBytes + a * kAtomBytes, &mapQ, bar(kBarQ, t), 64 * a, q0 + t * kTileQ, head, batch);
-            }
-            for (int j = 0; j < steps; ++j) {
+        if (lane == 0) {
+            for (int j = 2; j < steps; ++j) {  // tiles 0 and 1 were requested during set-up
                 const int stage = j & 1;
                 const unsigned freed = ((j >> 1) & 1) ^ 1;
-                const int k0 = j * kTileK;
                 if (!mbarWait(bar(kBarKEmpty, stage), freed, abortFlag, kAttnProducerWait)) break;
-                mbarArriveExpectTx(bar(kBarKFull, stage), Plan::kTileBytes);
-                for (int a = 0; a < kAtoms; ++a)
-                    tmaLoad4d(base + Plan::kOffK + stage * Plan::kTileBytes + a * kAtomBytes, &mapK, bar(kBarKFull, stage), 64 * a, k0, kvHead, batch);
+                loadK(j);
                 if (!mbarWait(bar(kBarVEmpty, stage), freed, abortFlag, kAttnProducerWait)) break;
-                mbarArriveExpectTx(bar(kBarVFull, stage), Plan::kVBytes);
-                for (int half = 0; half < 2; ++half)
-                    for (int c = 0; c < kAtoms; ++c)
-                        tmaLoad4d(base + Plan::kOffV + stage * Plan::kVBytes + (half * kAtoms + c) * kVBoxBytes, &mapV, bar(kBarVFull, stage), 64 * c,
-                                  k0 + 64 * half, kvHead, batch);
+                loadV(j);
             }
         }
         __syncwarp();
