@@ -15,7 +15,12 @@
 //   warps 2-5 and 6-9   query tile 0 and 1, one thread per query row: read the row of S, keep the running maximum and sum
 //               (the online softmax of Milakov and Gimelshein, as used by FlashAttention), write P as 16-bit pairs over the
 //               columns of S already read, rescale the row of O when the maximum moved far, and at the end divide by the
-//               sum and store the row.
+//               sum and put the row into the query tile's shared memory, from where a bulk tensor store takes the tile.
+// What was measured and dropped (256 heads of 1024 x 1024 x 128, f16): steps of 64 keys with S, P and O in columns of their
+// own, so that no product waits for the exponentials (S products of 64 columns read Q from shared memory again for half the
+// work: 186 us against 155); two exponentials per special-function instruction in 16 bits (three times slower); a cubic
+// on the FMA pipe for a quarter of the exponentials (the loop is bound by issue slots, not by that unit: slower); CTAs that
+// walk several work items, statically dealt or drawn from a counter (149 - 166 us, and worse under a causal mask).
 // Every wait is bounded: a wait that runs out records a code in g_attentionStatus, raises the CTA's abort flag and all
 // roles leave through the common exit, which frees the tensor memory.
 #include <cuda.h>
@@ -24,7 +29,6 @@
 #include <cuda_runtime.h>
 
 #include <cmath>
-#include <cstdlib>
 #include <cstdint>
 #include <mutex>
 #include <type_traits>
@@ -53,15 +57,7 @@ struct AttentionArgs {
     float scaleLog2;     // scale * log2(e): the exponentials are taken in base 2
     float* logSumExp;    // [batch][head][numQ], or null
     unsigned idescS, idescO;
-#ifdef VKZB_ATTN_TRACE
-    long long* trace;
-#endif
 };
-#ifdef VKZB_ATTN_TRACE
-#define TRACE(slot) do { if (g.trace && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) g.trace[(slot)] = clock64(); } while (0)
-#else
-#define TRACE(slot) do {} while (0)
-#endif
 
 // ---- PTX wrappers (the same instructions as in k_umma.cu; this file is a translation unit of its own) -----------------
 
@@ -198,25 +194,6 @@ __device__ __forceinline__ float exp2Approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// 2^x for x <= 8 without the special-function unit (the split into integer and fraction of Cody and Waite, a cubic for the
-// fraction with the coefficients FlashAttention-4 uses: relative error about 1e-4, below the rounding of a 16-bit result).
-#ifndef VKZB_ATTN_POLY_EVERY
-#define VKZB_ATTN_POLY_EVERY 0
-#endif
-#ifndef VKZB_ATTN_TURNS
-#define VKZB_ATTN_TURNS 0
-#endif
-constexpr bool kTakeTurns = VKZB_ATTN_TURNS != 0;
-constexpr int kPolyEvery = VKZB_ATTN_POLY_EVERY;  // one exponential in this many takes the polynomial (0: none; even values)
-__device__ __forceinline__ float exp2Poly(float x) {
-    x = fmaxf(x, -127.f);
-    const float biased = __fadd_rd(x, 12582912.f);   // 1.5 * 2^23: the low mantissa bits now hold floor(x)
-    const float fraction = x - (biased - 12582912.f);  // in [0, 1)
-    float p = fmaf(fraction, 0.077119089663028717041015625f, 0.227564394474029541015625f);
-    p = fmaf(p, fraction, 0.695146143436431884765625f);
-    p = fmaf(p, fraction, 1.f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(biased) << 23));  // times 2^floor(x), through the exponent field
-}
 template <bool BF16>
 __device__ __forceinline__ unsigned packPair(float lo, float hi) {
     if constexpr (BF16) {
@@ -247,7 +224,7 @@ struct AttnPlan {
 };
 
 // Barrier numbers (8 bytes each from the start of the barrier block); [2] = one per query tile or per stage.
-enum : unsigned { kBarQ = 0, kBarKFull = 2, kBarKEmpty = 4, kBarVFull = 6, kBarVEmpty = 8, kBarS = 10, kBarP = 12, kBarO = 14, kBarTurn = 16, kBarCount = 18 };
+enum : unsigned { kBarQ = 0, kBarKFull = 2, kBarKEmpty = 4, kBarVFull = 6, kBarVEmpty = 8, kBarS = 10, kBarP = 12, kBarO = 14, kBarCount = 16 };
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -300,7 +277,7 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
                           j * kTileK + 64 * half, kvHead, batch);
     };
     if (threadIdx.x == 0) {
-        for (unsigned b = 0; b < kBarCount; ++b) mbarInit(bar0 + 8 * b, b >= kBarTurn || b == kBarP || b == kBarP + 1 ? 4 : 1);  // P and the turns: one arrival per softmax warp
+        for (unsigned b = 0; b < kBarCount; ++b) mbarInit(bar0 + 8 * b, b == kBarP || b == kBarP + 1 ? 4 : 1);  // P: one arrival per softmax warp
         *abortFlag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fenceAsyncShared();
@@ -389,13 +366,11 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
                 if (j >= tiles[t]) continue;
                 if (!(ok = waitAll(bar(kBarP, t), j & 1))) break;
                 tcgen05FenceAfter();
-                TRACE(2000 + 1000 * t + 16 * j + 0);
                 if (electOne()) {
                     issuePV(t, j);
                     if (j + 1 < tiles[t]) issueS(t, j + 1);
                 }
                 __syncwarp();
-                TRACE(2000 + 1000 * t + 16 * j + 1);
             }
             if (ok && electOne()) {
                 tcgen05Commit(bar(kBarVEmpty, stage));                      // every P V of this key tile has been issued
@@ -421,7 +396,6 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
             // S_t of this key tile is complete, and with it everything issued before it: the previous P V has read P and updated O
             if (!(ok = waitAll(bar(kBarS, t), j & 1))) break;
             tcgen05FenceAfter();
-            if (quarter == 0) TRACE(1000 * t + 16 * j + 0);
             const int limit = visible - j * kTileK;  // columns [0, limit) of this tile count
             // the same code path for the whole warp (tcgen05.ld and .st must not sit in a branch that lanes take differently)
             const bool allCount = __all_sync(0xFFFFFFFFu, limit >= kTileK) != 0;
@@ -430,7 +404,6 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
 #pragma unroll
             for (int chunk = 0; chunk < 4; ++chunk) tmemLoad32Issue(tmemS + 32 * chunk, *reinterpret_cast<unsigned(*)[32]>(v + 32 * chunk));
             tmemWaitLoads();
-            if (quarter == 0) TRACE(1000 * t + 16 * j + 1);
             float tileMax = -INFINITY;
             if (allCount && c >= 0.f) {
                 // every column counts: the maximum of the raw scores (three at a time), scaled once
@@ -450,20 +423,11 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
             // The reference point of the exponentials moves only when the maximum has grown by more than 2^8: until then the
             // probabilities are at most 256 (exact enough in 16 bits, far from overflow in the sums) and the row of O needs
             // no rescaling. The final division by the sum, taken against the same reference point, makes the result the same.
-            if (quarter == 0) TRACE(1000 * t + 16 * j + 2);
             const float newMax = runMax == -INFINITY || tileMax > runMax + 8.f ? tileMax : runMax;
             const float shift = newMax == -INFINITY ? 0.f : newMax;  // a row that has seen no key yet
             const float correction = newMax == runMax ? 1.f : exp2Approx(runMax - shift);  // 0 for the first keys of a row
             runMax = newMax;
-            // The exponentials of the two query tiles take turns: the special-function unit is what bounds them, and two warps
-            // of a scheduler that want it at once only slow each other down, while taking turns leaves one tile's loads,
-            // maximum and hand-over to run beside the other's exponentials. Tile 0 goes first in every step; a tile waits
-            // only for a step the other tile really has.
-            if (kTakeTurns && (t == 1 ? j < tiles[0] : (j > 0 && j - 1 < tiles[1]))) {
-                if (!(ok = waitAll(bar(kBarTurn, t), (t == 1 ? j : j - 1) & 1))) break;
-            }
-            // exp2(c s - shift): most on the special-function unit (16 results per clock and SM, which is what bounds this
-            // loop), one in kPolyEvery by a polynomial on the FMA pipe, which would otherwise idle
+            // exp2(c s - shift) on the special-function unit (16 results per clock and SM)
             const float negShift = -shift;
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
             // The row is read a second time, 32 columns at a time with the next 32 already on their way: holding all 128 scores
@@ -475,8 +439,7 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
                 for (int i = 0; i < 16; ++i) {
                     const int col = chunk * 32 + 2 * i;
                     const float x0 = fmaf(__uint_as_float(s32[2 * i]), c, negShift), x1 = fmaf(__uint_as_float(s32[2 * i + 1]), c, negShift);
-                    float p0 = exp2Approx(x0);
-                    float p1 = kPolyEvery && (i % (kPolyEvery / 2 > 0 ? kPolyEvery / 2 : 1)) == 0 ? exp2Poly(x1) : exp2Approx(x1);
+                    float p0 = exp2Approx(x0), p1 = exp2Approx(x1);
                     if (!allCount) p0 = col < limit ? p0 : 0.f, p1 = col + 1 < limit ? p1 : 0.f;
                     sum[i & 3] += p0 + p1;
                     packed[i] = packPair<BF16>(p0, p1);
@@ -497,10 +460,7 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
             tmemWaitLoads();
             exponentials(pong, 3);
             const float tileSum = (sum[0] + sum[1]) + (sum[2] + sum[3]);
-            __syncwarp();
-            if (kTakeTurns && lane == 0) mbarArrive(bar(kBarTurn, t ^ 1));
             tmemWaitStores();
-            if (quarter == 0) TRACE(1000 * t + 16 * j + 3);
             runSum = runSum * correction + tileSum;
             if (j > 0 && __any_sync(0xFFFFFFFFu, correction != 1.f)) {
 #pragma unroll
@@ -515,7 +475,6 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
             tcgen05FenceBefore();
             __syncwarp();
             if (lane == 0) mbarArrive(bar(kBarP, t));
-            if (quarter == 0) TRACE(1000 * t + 16 * j + 4);
         }
         if (ok && myTiles > 0) ok = waitAll(bar(kBarO, t), (myTiles - 1) & 1);
         tcgen05FenceAfter();
@@ -652,9 +611,6 @@ extern "C" __attribute__((visibility("default"))) int vkzbAttentionForward(cudaS
     g.mask = a->mask;
     g.scaleLog2 = a->scale * 1.4426950408889634f;
     g.logSumExp = a->logSumExp;
-#ifdef VKZB_ATTN_TRACE
-    g.trace = getenv("VKZB_ATTN_TRACE_PTR") ? reinterpret_cast<long long*>(strtoull(getenv("VKZB_ATTN_TRACE_PTR"), nullptr, 0)) : nullptr;
-#endif
     const unsigned format = bf16 ? 1u : 0u;
     // accumulate in f32; A and B in `format`; M = 128; S: N = 128 keys, both operands K-major; O: N = head dimension, B (V) N-major
     g.idescS = 1u << 4 | format << 7 | format << 10 | unsigned(kTileK >> 3) << 17 | unsigned(kTileQ >> 4) << 24;
