@@ -10,12 +10,13 @@ multiplied; A (2 GiB) is replicated, every rank ends with the whole of D. This i
 `partOf(g, rows=false, first, count)` (src/cublas/cublas.cpp:542-546) applied across GPUs, with the exchange step its
 libnccl surface provides (src/nccl/nccl.cpp:691-695). Strong scaling: the total work is fixed.
 
-Two ways of getting every rank's columns everywhere are built. "Fused" (2 and 4 GPUs): each rank multiplies its column
+Two ways of getting every rank's columns everywhere are built. "Pipelined" (what runs by default): the block-cyclic,
+chunk-pipelined products + ncclAllGather described above. "Fused" (--gather fused): each rank multiplies its column
 block with cublasLtMatmul calls whose epilogue stores every finished tile not only to its own D but, through peer-mapped
 addresses (vkzbNcclExchangeBuffer + vkzbSetOutputMirrors), to the other ranks' D as well, so the NVLink traffic is spread
-over the whole product and nothing is left to gather; barriers of libnccl.so.2 order the ranks around the step.
-"Pipelined" (8 GPUs, where NVLink is busy for most of the step): the block-cyclic, chunk-pipelined products + ncclAllGather
-described above.
+over the whole product and nothing is left to gather; barriers of libnccl.so.2 order the ranks around the step. It measures
+slower at every rank count (the remote stores hold up the epilogue: 28.1 / 17.3 / 9.1 ms at 2 / 4 / 8 GPUs against
+26.9 / 14.5 / 8.3), and is kept as the form in which one kernel does the product and the exchange.
 
 Operands are the seeded synthetic ones of vulkanizer_b200/synth.py (seed 5; element i of A^T's storage is value i of the
 stream, element i of B's value m * k + i), made on the GPU by the torch form of that generator. After the timed region every
@@ -45,9 +46,10 @@ def round_widths(n: int, ranks: int, forced: int = 0):
 def default_round_widths(n: int, ranks: int):
     """Chunk widths (columns per rank) of the successive rounds: uniform, 1024 columns where the share allows four rounds.
     1024 columns are 512 tile pairs of 256 x 256, 6.9 waves over 74 CTA pairs, so almost no SM idles at the end of a
-    chunk; and with equal chunks the gather of round j (about 0.8 of a chunk's product time over NVLink) always hides
-    behind the product of round j + 1. Only the last round's gather is exposed. (Rounds that shrink towards the end were
-    measured slower: a wide round's gather outlasts the narrower product after it.)"""
+    chunk; and with equal chunks the gather of round j always hides behind the product of round j + 1. Only the last round's
+    gather is exposed. (Rounds that shrink towards the end were measured slower, at 8 ranks, where a wide round's gather
+    outlasts the narrower product after it, and at 4 ranks, where the gather takes under half a product's time: 14.5 ms with
+    equal rounds, 14.8 - 15.0 with the last round cut into halves, 14.6 into a half and two quarters.)"""
     per_rank = n // ranks
     assert n % ranks == 0 and per_rank % 256 == 0, "the column count must be a multiple of 256 x ranks"
     if ranks == 1:
@@ -211,13 +213,11 @@ def run(args):
     size = 32768
     m = n = k = size
     # fused: products whose tiles go straight to every rank's D; pipelined: chunked products + ncclAllGather.
-    # Which of the two runs depends on how much of the step NVLink needs: every rank receives (G - 1) / G of D,
-    # 4 m n (G - 1) / G bytes at about 770 GB/s, against 2 m n k / G flop at about 1.45 PFLOP/s. Mirrored bulk stores reach
-    # about 640 GB/s and push back into the epilogue when the link is busy most of the step (8 GPUs: 4.9 ms of traffic in a
-    # 6.0 ms product, measured 9.1 ms fused against 8.3 ms chunk-pipelined), while the copy engines behind ncclAllGather
-    # reach 700 GB/s; below that (2 and 4 GPUs) the fused form wins because nothing is left over at the end of the step.
-    link_share = (4.0 * m * n * (world - 1) / world / 770e9) / (2.0 * m * n * k / world / 1.45e15) if world > 1 else 0.0
-    fused = world > 1 and (args.gather == "fused" or (args.gather == "auto" and link_share < 0.6))
+    # Measured, 32768^3: 2 GPUs 28.1 ms fused / 26.9 pipelined, 4 GPUs 17.3 / 14.5, 8 GPUs 9.1 / 8.3. The
+    # mirrored bulk stores push back into the epilogue (every tile waits for seven or three or one remote copies of itself),
+    # while a gather behind the next round's product costs the product nothing; so the pipelined form is what runs unless
+    # the fused one is asked for.
+    fused = world > 1 and args.gather == "fused"
     # (fused: 2048 columns per call. One call over a rank's whole share ran a quarter slower at 2 GPUs: over tens of
     # milliseconds the CTAs of one persistent kernel drift apart along k and stop finding each other's operand slices in L2.)
     rounds = column_chunks(n, world, round_widths(n, world, getattr(args, "chunk_columns", 0)))

@@ -44,6 +44,7 @@ def test_rounds_are_uniform_so_each_gather_hides_behind_the_next_product():
     assert round_widths(32768, 2) == [1024] * 16
     assert round_widths(32768, 1) == [2048] * 16
     assert round_widths(8192, 8) == [256] * 4
+    assert round_widths(32768, 4, 2048) == [2048] * 4
 
 
 def test_uneven_split_is_refused():

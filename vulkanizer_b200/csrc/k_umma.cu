@@ -1041,6 +1041,13 @@ DeviceInfo& deviceInfo() {
 
 int elemSizeOf(int type) { return type == kF32 ? 4 : type == kS8 ? 1 : 2; }
 
+// How much L2 fetches around each line an operand load asks for.
+CUtensorMapL2promotion operandPromotion() {
+    static const int forced = measureKnob("VKZB_UMMA_L2_PROMOTION", 3);  // 0 none, 1 64 bytes, 2 128 bytes, 3 256 bytes
+    return forced == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : forced == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+         : forced == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+}
+
 // A 3-d map over one operand: (contiguous dimension, strided dimension, batch entry).
 bool encodeOperand(CUtensorMap* map, const void* base, int type, long long inner, long long outer, long long ld,
                    long long batch, long long batchStride, unsigned boxInner, unsigned boxOuter) {
@@ -1055,8 +1062,7 @@ bool encodeOperand(CUtensorMap* map, const void* base, int type, long long inner
     const cuuint32_t box[3] = {boxInner, boxOuter, 1};
     const cuuint32_t elemStrides[3] = {1, 1, 1};
     return encodeTiled()(map, dt, 3, const_cast<void*>(base), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+                         CU_TENSOR_MAP_SWIZZLE_128B, operandPromotion(), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // A 4-d map over an operand that is contiguous along m or n (`inner`), for extents that are whole chunks of 128 bytes:
@@ -1261,6 +1267,7 @@ cudaError_t launchUmma(const Problem& p) {
     g.m = p.m, g.n = p.n, g.k = p.k, g.batch = p.batch;
     g.tilesM = plan.tilesM, g.tilesN = plan.tilesN;
     g.groupM = pair ? 8 : 16;  // about as many tile rows as tile columns among the tiles in flight
+    if (const int forcedGroup = measureKnob("VKZB_UMMA_GROUP_M", 0)) g.groupM = forcedGroup;
     g.totalTiles = plan.totalTiles;
     g.splits = splits;
     g.totalUnits = g.totalTiles * splits;
