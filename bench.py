@@ -642,7 +642,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, help="one of the names in WORKLOADS or ATTENTION_WORKLOADS (default: the headline configuration)")
     ap.add_argument("--chunk-columns", type=int, default=0, help="sharded run: columns per rank and round of the pipelined gather (default: chosen by rank count)")
-    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "pipelined"], help="sharded run: how the column blocks reach every rank")
+    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "pipelined", "hybrid"], help="sharded run: how the column blocks reach every rank")
     ap.add_argument("--timeline", action="store_true", help="sharded run: device time of every round's product and gather of one extra step, on stderr")
     args = ap.parse_args()
     if args.impl == "reference":

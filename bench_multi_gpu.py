@@ -218,6 +218,9 @@ def run(args):
     # while a gather behind the next round's product costs the product nothing; so the pipelined form is what runs unless
     # the fused one is asked for.
     fused = world > 1 and args.gather == "fused"
+    # hybrid: pipelined, except that the last round's product stores its tiles to every rank itself, so that no gather is left
+    # over when the last product ends (the price: that one product's epilogue waits for the remote copies)
+    hybrid = world > 1 and args.gather == "hybrid"
     # (fused: 2048 columns per call. One call over a rank's whole share ran a quarter slower at 2 GPUs: over tens of
     # milliseconds the CTAs of one persistent kernel drift apart along k and stop finding each other's operand slices in L2.)
     rounds = column_chunks(n, world, round_widths(n, world, getattr(args, "chunk_columns", 0)))
@@ -255,25 +258,35 @@ def run(args):
     bf16, f32 = capi.CUDA_R_16BF, capi.CUDA_R_32F
     events = [torch.cuda.Event() for _ in rounds]
 
-    if fused:
+    mirrors = []
+    if fused or hybrid:
         peers = comm.exchange_buffer(D.data_ptr())
-        lt.set_output_mirrors(D.data_ptr(), D.numel() * 4, [peers[p] for p in range(world) if p != rank])
+        mirrors = [peers[p] for p in range(world) if p != rank]
+    if fused:
+        lt.set_output_mirrors(D.data_ptr(), D.numel() * 4, mirrors)
 
     def step():
         if fused:
             comm.barrier(compute.cuda_stream)  # nobody still reads the D this step overwrites
         for j, w, round_first, firsts in rounds:
             mine = D.data_ptr() + 4 * firsts[rank] * m
+            stored_everywhere = hybrid and j == len(rounds) - 1
+            if stored_everywhere:
+                lt.set_output_mirrors(D.data_ptr(), D.numel() * 4, mirrors)
             lt.matmul(capi.OP_T, capi.OP_N, m, w, k, 1.0, A.data_ptr(), bf16, k, Bmine.data_ptr() + 2 * b_offset[j], bf16, k, 0.0,
                       mine, f32, m, mine, f32, m, stream=compute.cuda_stream)
-            if world > 1 and not fused:
+            if stored_everywhere:
+                lt.set_output_mirrors(0, 0, [])
+            elif world > 1 and not fused:
                 events[j].record(compute)
                 gather.wait_event(events[j])
                 comm.all_gather(mine, D.data_ptr() + 4 * round_first * m, w * m, "float32", gather.cuda_stream)
-        if fused:
-            comm.barrier(compute.cuda_stream)  # every rank's product is finished, so every tile has landed here
-        elif world > 1:
+        if world > 1 and not fused:
             compute.wait_stream(gather)  # the step ends when every rank's columns have arrived
+        if fused or hybrid:
+            # every rank's (last) product is finished, so every tile it stored has landed here; behind the gathers, because a
+            # communicator's operations run one after another, whatever stream they were given
+            comm.barrier(compute.cuda_stream)
 
     for _ in range(max(3, args.warmup)):
         step()
@@ -411,7 +424,7 @@ def run(args):
             "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": "cfg5b_bf16_32768_nsharded", "call": "cublasLtMatmul with output mirrors (tiles stored to every rank over NVLink)" if fused else "cublasLtMatmul + ncclAllGather", "opA": "T", "opB": "N", "m": m, "n": n,
-                       "k": k, "a_b_type": "bf16", "c_type": "f32", "alpha": 1, "beta": 0, "seed": 5, "parallelism": f"n-sharded x{world}", "gather": "fused into the GEMM epilogue" if fused else ("none" if world == 1 else "ncclAllGather, chunk-pipelined"),
+                       "k": k, "a_b_type": "bf16", "c_type": "f32", "alpha": 1, "beta": 0, "seed": 5, "parallelism": f"n-sharded x{world}", "gather": "fused into the GEMM epilogue" if fused else ("none" if world == 1 else "ncclAllGather, chunk-pipelined" + ("; the last round stored to every rank by the GEMM epilogue" if hybrid else "")),
                        "chunk_columns": [w for _, w, _, _ in rounds], "rounds": len(rounds),
                        "l2": "operands of one step hold 8 GiB > L2, no flush", "timing": "CUDA events on the compute stream, maximum over ranks"},
             "roofline": {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak, "traffic": None,
