@@ -483,25 +483,24 @@ attentionKernel(const AttentionArgs g, const __grid_constant__ CUtensorMap mapQ,
         if (ok) {
             const float inverse = runSum > 0.f ? 1.f / runSum : 0.f;
             unsigned char* rowBase = smem + t * Plan::kTileBytes + rowInTile * 128;
+            // the whole row at once: all the loads in flight, one wait (nothing else is alive in registers by now)
+            unsigned v[D];
+            if (myTiles > 0) {
 #pragma unroll
-            for (int chunk = 0; chunk < D / 32; ++chunk) {
-                unsigned v[32];
-                if (myTiles > 0) {
-                    tmemLoad32(tmemO + 32 * chunk, v);
-                } else {
+                for (int chunk = 0; chunk < D / 32; ++chunk) tmemLoad32Issue(tmemO + 32 * chunk, *reinterpret_cast<unsigned(*)[32]>(v + 32 * chunk));
+                tmemWaitLoads();
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = 0u;
-                }
+                for (int i = 0; i < D; ++i) v[i] = 0u;
+            }
 #pragma unroll
-                for (int piece = 0; piece < 4; ++piece) {
-                    unsigned w[4];
+            for (int index = 0; index < D / 8; ++index) {
+                unsigned w[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        w[i] = packPair<BF16>(__uint_as_float(v[8 * piece + 2 * i]) * inverse, __uint_as_float(v[8 * piece + 2 * i + 1]) * inverse);
-                    // 16-byte piece (4 chunk + piece) of the row: atom (index / 8), position (index % 8) ^ (row % 8), as TMA expects it
-                    const int index = 4 * chunk + piece;
-                    *reinterpret_cast<uint4*>(rowBase + (index / 8) * kAtomBytes + (((index % 8) ^ (rowInTile & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
-                }
+                for (int i = 0; i < 4; ++i)
+                    w[i] = packPair<BF16>(__uint_as_float(v[8 * index + 2 * i]) * inverse, __uint_as_float(v[8 * index + 2 * i + 1]) * inverse);
+                // 16-byte piece `index` of the row: atom (index / 8), position (index % 8) ^ (row % 8), as TMA expects it
+                *reinterpret_cast<uint4*>(rowBase + (index / 8) * kAtomBytes + (((index % 8) ^ (rowInTile & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
             if (g.logSumExp && query < g.numQ)  // natural logarithm of the sum of exp(score); 0 for a row without visible keys
                 g.logSumExp[(size_t(batch) * g.heads + head) * g.numQ + query] = runSum > 0.f ? (runMax + log2f(runSum)) * 0.6931471805599453f : 0.f;
