@@ -23,7 +23,9 @@
 // walk several work items, statically dealt or drawn from a counter (149 - 166 us, and worse under a causal mask); P through
 // shared memory instead of tensor memory, so that a tile's next scores are computed before its P V and its softmax warps
 // start half a product earlier (188 us: both products then read both operands from shared memory, which the softmax warps'
-// stores and the loads also use).
+// stores and the loads also use); the maximum taken inside the exponential pass against the row's previous reference point,
+// with a second pass only when it moved by more than 2^8 (163 us: that loop is the bottleneck, and the extra maxima and the
+// held-back probabilities cost it more than the separate pass did).
 // Every wait is bounded: a wait that runs out records a code in g_attentionStatus, raises the CTA's abort flag and all
 // roles leave through the common exit, which frees the tensor memory.
 #include <cuda.h>
