@@ -393,9 +393,18 @@ def run_single_gpu(args):
     # j - 1 is multiplied and block j - 2 of C travels back, on three streams, so both directions of the host link stay busy.
     blocks = 8 if (batch == 1 and n >= 2048 and n % 8 == 0 and spec["call"] == "gemmex" and spec["tb"] == "N") else 1
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
-    in_done = [torch.cuda.Event() for _ in range(blocks + 1)]
-    out_ready = [torch.cuda.Event() for _ in range(blocks)]
-    step_done = torch.cuda.Event()
+    # Two sets of device buffers take turns, so that the operands of step s + 1 travel while step s is still being multiplied
+    # and its result is still on its way back: the link to the host, not the GPU, bounds this figure, and it is busy in both
+    # directions the whole time.
+    sets = 2 if blocks > 1 else 1
+    eA = [dAs[0]] + [torch.empty_like(dAs[0]) for _ in range(sets - 1)]
+    eB = [dBs[0]] + [torch.empty_like(dBs[0]) for _ in range(sets - 1)]
+    eC = [dCs[0]] + [torch.empty_like(dCs[0]) for _ in range(sets - 1)]
+    in_done = [[torch.cuda.Event() for _ in range(blocks + 1)] for _ in range(sets)]
+    out_ready = [[torch.cuda.Event() for _ in range(blocks)] for _ in range(sets)]
+    out_done = [[torch.cuda.Event() for _ in range(blocks)] for _ in range(sets)]
+    step_done = [torch.cuda.Event() for _ in range(sets)]
+    e2e_count = [0]
 
     def step_e2e():
         if blocks == 1:
@@ -404,29 +413,38 @@ def run_single_gpu(args):
             call(0)
             hostC.copy_(dCs[0], non_blocking=True)
             return
+        b = e2e_count[0] % sets
+        e2e_count[0] += 1
+        A_d, B_d, C_d = eA[b], eB[b], eC[b]
         cols = n // blocks
-        copy_in.wait_event(step_done)  # the previous step's products have read A and B
+        copy_in.wait_event(step_done[b])  # the products of the step that last used this set have read its A and B
         with torch.cuda.stream(copy_in):
-            dAs[0].copy_(hostA, non_blocking=True)
-            in_done[blocks].record(copy_in)
+            A_d.copy_(hostA, non_blocking=True)
+            in_done[b][blocks].record(copy_in)
             for j in range(blocks):
-                dBs[0][j * cols * ldb:(j + 1) * cols * ldb].copy_(hostB[j * cols * ldb:(j + 1) * cols * ldb], non_blocking=True)
-                in_done[j].record(copy_in)
-        stream.wait_event(in_done[blocks])
+                B_d[j * cols * ldb:(j + 1) * cols * ldb].copy_(hostB[j * cols * ldb:(j + 1) * cols * ldb], non_blocking=True)
+                in_done[b][j].record(copy_in)
+        stream.wait_event(in_done[b][blocks])
         for j in range(blocks):
-            stream.wait_event(in_done[j])
-            blas.gemm_ex(ta, tb, m, cols, k, spec["alpha"], dAs[0].data_ptr(), cuda_type[ab], lda, dBs[0].data_ptr() + j * cols * ldb * ELEM[ab],
-                         cuda_type[ab], ldb, spec["beta"], dCs[0].data_ptr() + j * cols * ldc * ELEM[ct], cuda_type[ct], ldc, compute,
+            stream.wait_event(in_done[b][j])
+            stream.wait_event(out_done[b][j])  # this block of C has left for the host (the step before last wrote it)
+            blas.gemm_ex(ta, tb, m, cols, k, spec["alpha"], A_d.data_ptr(), cuda_type[ab], lda, B_d.data_ptr() + j * cols * ldb * ELEM[ab],
+                         cuda_type[ab], ldb, spec["beta"], C_d.data_ptr() + j * cols * ldc * ELEM[ct], cuda_type[ct], ldc, compute,
                          capi.GEMM_DEFAULT_TENSOR_OP)
-            out_ready[j].record(stream)
-            copy_out.wait_event(out_ready[j])
+            out_ready[b][j].record(stream)
+            copy_out.wait_event(out_ready[b][j])
             with torch.cuda.stream(copy_out):
-                hostC[j * cols * ldc:(j + 1) * cols * ldc].copy_(dCs[0][j * cols * ldc:(j + 1) * cols * ldc], non_blocking=True)
-        step_done.record(stream)
+                hostC[j * cols * ldc:(j + 1) * cols * ldc].copy_(C_d[j * cols * ldc:(j + 1) * cols * ldc], non_blocking=True)
+                out_done[b][j].record(copy_out)
+        step_done[b].record(stream)
 
     with torch.cuda.stream(stream):
-        step_done.record(stream)
-        for _ in range(2):
+        for e in step_done:
+            e.record(stream)
+        for per_set in out_done:
+            for e in per_set:
+                e.record(stream)
+        for _ in range(2 * sets):
             step_e2e()
         stream.wait_stream(copy_out)
         stream.synchronize()
@@ -484,7 +502,7 @@ def run_single_gpu(args):
                      "algorithmic_bytes": algorithmic_bytes, "algorithmic_flop": flops},
         "roofline_sustained": sustained,
         "e2e": {"value": e2e_tf, "unit": "TFLOP/s", "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out,
-                "how": (f"{blocks} column blocks: copy in, cublasGemmEx and copy out overlap on three streams" if blocks > 1 else
+                "how": (f"{blocks} column blocks: copy in, cublasGemmEx and copy out overlap on three streams, two sets of device buffers in turn" if blocks > 1 else
                         "copy in, one call, copy out, on one stream")},
         "gpu_launches": launches, "clocks": clocks,
     }
