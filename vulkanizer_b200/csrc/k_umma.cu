@@ -85,6 +85,7 @@ struct UmmaArgs {
     const CUtensorMap* entryMaps;
     const unsigned* entryFlag;
     unsigned entrySerial;           // *entryFlag == entrySerial: stand down (the word needs no clearing between launches)
+    int serpentine;                 // alternate units of a CTA walk the k slices in opposite directions
     int tmaStore;                   // D is 16-byte aligned in every dimension: results leave through shared memory and TMA
     int mirrorCount;                // every bulk store of D is repeated into this many other buffers (peer GPUs)
     // Split along k: a unit of work is (tile, split); the splits of a tile run on different CTAs at the same time, each
@@ -696,7 +697,8 @@ __device__ __forceinline__ void producerLoop(const UmmaArgs& g, const CUtensorMa
     const int slices = g.numKSlices, sliceElems = g.sliceElems;
     int stage = 0;
     unsigned phase = 0;
-    for (long long unit = firstUnit; unit < g.totalUnits; unit += unitStride) {
+    bool backwards = false;
+    for (long long unit = firstUnit; unit < g.totalUnits; unit += unitStride, backwards = !backwards) {
         const int split = int(unit % g.splits);
         const TileCoord t = tileCoord(g, unit / g.splits);
         const int row0 = t.row * kTileRows + int(ctaRank) * kBM, col0 = t.col * BN + int(ctaRank) * Plan::kCtaB;
@@ -705,8 +707,11 @@ __device__ __forceinline__ void producerLoop(const UmmaArgs& g, const CUtensorMa
         const CUtensorMap* mapB = g.entryMaps ? g.entryMaps + 3 * t.batch + 1 : launchMapB;
         if (g.entryMaps) tensorMapAcquire(mapA), tensorMapAcquire(mapB);
         const int batchA = g.entryMaps ? 0 : t.batch * g.batchMulA, batchB = g.entryMaps ? 0 : t.batch * g.batchMulB;
-        const int ksEnd = int((long long)slices * (split + 1) / g.splits);
-        for (int ks = int((long long)slices * split / g.splits); ks < ksEnd; ++ks) {
+        // Every other unit of a CTA walks k from the far end: the CTAs of a wave move along k together, so the slices they all
+        // used last are the ones the next wave's tiles in the same rows find in L2 first.
+        const int ksFirst = int((long long)slices * split / g.splits), ksEnd = int((long long)slices * (split + 1) / g.splits);
+        for (int step = ksFirst; step < ksEnd; ++step) {
+            const int ks = g.serpentine && backwards ? ksEnd - 1 - (step - ksFirst) : step;
             if (!mbarWait(emptyBar + 8 * stage, phase ^ 1, abortFlag, kStatusProducerWait)) return;
             const unsigned bar = fullBarLeader + 8 * stage;
             if (leader) mbarArriveExpectTx(fullBar + 8 * stage, unsigned(Plan::kStageBytes) * (PAIR ? 2u : 1u));
@@ -1268,6 +1273,7 @@ cudaError_t launchUmma(const Problem& p) {
     g.tilesM = plan.tilesM, g.tilesN = plan.tilesN;
     g.groupM = pair ? 8 : 16;  // about as many tile rows as tile columns among the tiles in flight
     if (const int forcedGroup = measureKnob("VKZB_UMMA_GROUP_M", 0)) g.groupM = forcedGroup;
+    g.serpentine = measureKnob("VKZB_UMMA_SERPENTINE", 1);  // measured on 8192^3 f16: 0.806 -> 0.796 ms
     g.totalTiles = plan.totalTiles;
     g.splits = splits;
     g.totalUnits = g.totalTiles * splits;
