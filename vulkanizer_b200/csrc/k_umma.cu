@@ -1271,9 +1271,18 @@ cudaError_t launchUmma(const Problem& p) {
     UmmaArgs g{};
     g.m = p.m, g.n = p.n, g.k = p.k, g.batch = p.batch;
     g.tilesM = plan.tilesM, g.tilesN = plan.tilesN;
-    g.groupM = pair ? 8 : 16;  // about as many tile rows as tile columns among the tiles in flight
+    // Raster. By default groups of 8 rows of pair tiles (16 of single ones): about as many tile rows as tile columns among the
+    // tiles in flight. Products that are many groups tall AND many tiles wide (8192^3: 32 x 32 pair tiles) do better with the k
+    // direction alternating between a CTA's units (producerLoop), which lets the A panels of a group survive in L2 from wave
+    // to wave, and then with taller groups, so that every B panel is fetched once per group and there are half as many groups
+    // (8192^3 f16: on one box 0.806 ms forward, 0.796 alternating; on another, alternating, 8 rows 0.857 ms, 12 rows 0.853,
+    // 16 rows 0.846, 24 rows 0.86, 32 rows 0.88). Tall, narrow products with a long k lose by both (32768^3 in calls of
+    // 2048 columns: 57.4 ms against 59.4 - 59.6), so they keep the default.
+    const bool wideRaster = pair && plan.tilesM >= 32 && plan.tilesN >= 16;
+    g.groupM = pair ? (wideRaster ? 16 : 8) : 16;
+    g.serpentine = wideRaster;
     if (const int forcedGroup = measureKnob("VKZB_UMMA_GROUP_M", 0)) g.groupM = forcedGroup;
-    g.serpentine = measureKnob("VKZB_UMMA_SERPENTINE", 1);  // measured on 8192^3 f16: 0.806 -> 0.796 ms
+    if (const int forcedDirection = measureKnob("VKZB_UMMA_SERPENTINE", -1); forcedDirection >= 0) g.serpentine = forcedDirection;
     g.totalTiles = plan.totalTiles;
     g.splits = splits;
     g.totalUnits = g.totalTiles * splits;
