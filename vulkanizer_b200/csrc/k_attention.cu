@@ -19,7 +19,8 @@
 // What was measured and dropped (256 heads of 1024 x 1024 x 128, f16): steps of 64 keys with S, P and O in columns of their
 // own, so that no product waits for the exponentials (S products of 64 columns read Q from shared memory again for half the
 // work: 186 us against 155); two exponentials per special-function instruction in 16 bits (three times slower); a cubic
-// on the FMA pipe for a quarter of the exponentials (the loop is bound by issue slots, not by that unit: slower); CTAs that
+// on the FMA pipe for a quarter of the exponentials (slower), fp32 arithmetic on pairs in that loop (no change), the two tiles
+// taking turns at the special-function unit (slightly slower); CTAs that
 // walk several work items, statically dealt or drawn from a counter (149 - 166 us, and worse under a causal mask); P through
 // shared memory instead of tensor memory, so that a tile's next scores are computed before its P V and its softmax warps
 // start half a product earlier (188 us: both products then read both operands from shared memory, which the softmax warps'
